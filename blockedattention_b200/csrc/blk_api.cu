@@ -1,0 +1,388 @@
+// C ABI of libblkattn: plan life cycle and the run entry points declared in
+// include/blkattn.h.  Thin by design -- argument checks, one upload of the
+// schedule at plan creation, kernel launches on the caller's stream.
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "blk_internal.h"
+#include "blk_kernels.h"
+
+namespace {
+
+int cuda_fail(const char* what, cudaError_t e) {
+    blk_set_error(std::string(what) + ": " + cudaGetErrorString(e));
+    return BLK_ERR_CUDA;
+}
+
+template <typename T>
+int upload(const std::vector<T>& v, T** dptr, const char* what) {
+    *dptr = nullptr;
+    if (v.empty()) return BLK_OK;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(dptr), v.size() * sizeof(T));
+    if (e != cudaSuccess) return cuda_fail(what, e);
+    e = cudaMemcpy(*dptr, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return cuda_fail(what, e);
+    return BLK_OK;
+}
+
+struct DeviceScope {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceScope(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+        if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+        target = dev;
+    }
+    ~DeviceScope() {
+        if (ok && prev >= 0 && prev != target) cudaSetDevice(prev);
+    }
+    int target = -1;
+};
+
+int upload_plan(blk_plan* p) {
+    if (p->device < 0) return BLK_OK;
+    DeviceScope scope(p->device);
+    if (!scope.ok) {
+        blk_set_error("cannot select CUDA device " + std::to_string(p->device));
+        return BLK_ERR_CUDA;
+    }
+    int rc;
+    if ((rc = upload(p->segs, &p->d_segs, "upload segments")) != BLK_OK) return rc;
+    if ((rc = upload(p->tile_items, &p->d_tile_items, "upload tile items")) != BLK_OK) return rc;
+    if ((rc = upload(p->simt_items, &p->d_simt_items, "upload simt items")) != BLK_OK) return rc;
+    if ((rc = upload(p->small_items, &p->d_small_items, "upload small items")) != BLK_OK) return rc;
+    if ((rc = upload(p->umma_items, &p->d_umma_items, "upload umma items")) != BLK_OK) return rc;
+    if ((rc = upload(p->smx_chunks, &p->d_smx_chunks, "upload softmax chunks")) != BLK_OK) return rc;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&p->d_status), 2 * sizeof(int));
+    if (e != cudaSuccess) return cuda_fail("allocate status word", e);
+    e = cudaMemset(p->d_status, 0, 2 * sizeof(int));
+    if (e != cudaSuccess) return cuda_fail("clear status word", e);
+    p->d_counter = p->d_status + 1;
+    return BLK_OK;
+}
+
+bool grid_ok(int64_t items, int64_t H, const char* what) {
+    if (items * H > 0x7fffffffLL) {
+        blk_set_error(std::string(what) + ": work items x heads exceeds 2^31-1 CTAs");
+        return false;
+    }
+    return true;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+extern "C" int blk_gemm_plan_create(blk_plan_t** plan, const int64_t* M, const int64_t* N, const int64_t* K,
+                                    const int64_t* accum1, const int64_t* accum2, const int64_t* accumOut, int64_t S,
+                                    int64_t H, int dtype_in, int dtype_out, int transpose1, int transpose2,
+                                    int epilogue, int device) {
+    if (!plan) {
+        blk_set_error("blk_gemm_plan_create: plan is null");
+        return BLK_ERR_INVALID;
+    }
+    *plan = nullptr;
+    if (S < 0 || H < 0 || (S > 0 && (!M || !N || !K))) {
+        blk_set_error("blk_gemm_plan_create: negative count or null list");
+        return BLK_ERR_INVALID;
+    }
+    const int given = (accum1 != nullptr) + (accum2 != nullptr) + (accumOut != nullptr);
+    if (given != 0 && given != 3) {
+        blk_set_error("blk_gemm_plan_create: give all three offset arrays or none");
+        return BLK_ERR_INVALID;
+    }
+    if (dtype_in < BLK_F16 || dtype_in > BLK_F32 || dtype_out < BLK_F16 || dtype_out > BLK_F32 ||
+        (dtype_in == BLK_F32 && dtype_out != BLK_F32) ||
+        (dtype_in != BLK_F32 && dtype_out != BLK_F32 && dtype_out != dtype_in)) {
+        blk_set_error("blk_gemm_plan_create: unsupported dtype combination (out must be the input dtype or fp32)");
+        return BLK_ERR_UNSUPPORTED;
+    }
+    if (epilogue != BLK_EPI_SCORES && epilogue != BLK_EPI_SOFTMAX) {
+        blk_set_error("blk_gemm_plan_create: unknown epilogue");
+        return BLK_ERR_INVALID;
+    }
+    blk_plan* p = new (std::nothrow) blk_plan();
+    if (!p) return BLK_ERR_NOMEM;
+    p->kind = 0;
+    p->S = S;
+    p->H = H;
+    p->dtype_in = dtype_in;
+    p->dtype_out = dtype_out;
+    p->ta = transpose1 ? 1 : 0;
+    p->tb = transpose2 ? 1 : 0;
+    p->epi = epilogue;
+    p->device = device;
+    p->M.assign(M, M + S);
+    p->N.assign(N, N + S);
+    p->K.assign(K, K + S);
+    p->a1.resize(S + 1);
+    p->a2.resize(S + 1);
+    p->ao.resize(S + 1);
+    int rc;
+    if (given == 3) {
+        std::memcpy(p->a1.data(), accum1, (S + 1) * sizeof(int64_t));
+        std::memcpy(p->a2.data(), accum2, (S + 1) * sizeof(int64_t));
+        std::memcpy(p->ao.data(), accumOut, (S + 1) * sizeof(int64_t));
+        rc = BLK_OK;
+    } else {
+        rc = blk_offsets_from_lists(M, N, K, S, p->a1.data(), p->a2.data(), p->ao.data());
+    }
+    if (rc == BLK_OK) rc = blk_build_gemm_schedule(p);
+    if (rc == BLK_OK && !(grid_ok((int64_t)p->tile_items.size(), H, "gemm plan") &&
+                          grid_ok((int64_t)p->simt_items.size(), H, "gemm plan") &&
+                          grid_ok((int64_t)p->smx_chunks.size(), H, "gemm plan") &&
+                          grid_ok((int64_t)p->small_items.size(), H, "gemm plan")))
+        rc = BLK_ERR_UNSUPPORTED;
+    if (rc == BLK_OK) rc = upload_plan(p);
+    if (rc != BLK_OK) {
+        blk_plan_destroy(p);
+        return rc;
+    }
+    *plan = p;
+    return BLK_OK;
+}
+
+extern "C" int blk_softmax_plan_create(blk_plan_t** plan, const int64_t* rows, const int64_t* cols,
+                                       const int64_t* accum, int64_t S, int64_t H, int dtype, int device) {
+    if (!plan) {
+        blk_set_error("blk_softmax_plan_create: plan is null");
+        return BLK_ERR_INVALID;
+    }
+    *plan = nullptr;
+    if (S < 0 || H < 0 || (S > 0 && (!rows || !cols))) {
+        blk_set_error("blk_softmax_plan_create: negative count or null list");
+        return BLK_ERR_INVALID;
+    }
+    if (dtype < BLK_F16 || dtype > BLK_F32) {
+        blk_set_error("blk_softmax_plan_create: unsupported dtype");
+        return BLK_ERR_UNSUPPORTED;
+    }
+    blk_plan* p = new (std::nothrow) blk_plan();
+    if (!p) return BLK_ERR_NOMEM;
+    p->kind = 1;
+    p->S = S;
+    p->H = H;
+    p->dtype_in = p->dtype_out = dtype;
+    p->device = device;
+    p->M.assign(rows, rows + S);
+    p->N.assign(cols, cols + S);
+    p->a1.resize(S + 1);
+    int rc;
+    if (accum) {
+        std::memcpy(p->a1.data(), accum, (S + 1) * sizeof(int64_t));
+        rc = BLK_OK;
+    } else {
+        rc = blk_softmax_offsets(rows, cols, S, p->a1.data());
+    }
+    if (rc == BLK_OK) rc = blk_build_softmax_schedule(p);
+    if (rc == BLK_OK && !grid_ok((int64_t)p->smx_chunks.size(), H, "softmax plan")) rc = BLK_ERR_UNSUPPORTED;
+    if (rc == BLK_OK) rc = upload_plan(p);
+    if (rc != BLK_OK) {
+        blk_plan_destroy(p);
+        return rc;
+    }
+    p->ao = p->a1;
+    *plan = p;
+    return BLK_OK;
+}
+
+extern "C" void blk_plan_destroy(blk_plan_t* p) {
+    if (!p) return;
+    if (p->device >= 0) {
+        DeviceScope scope(p->device);
+        cudaFree(p->d_segs);
+        cudaFree(p->d_tile_items);
+        cudaFree(p->d_simt_items);
+        cudaFree(p->d_small_items);
+        cudaFree(p->d_umma_items);
+        cudaFree(p->d_smx_chunks);
+        cudaFree(p->d_status);
+    }
+    delete p;
+}
+
+extern "C" int blk_plan_extents(const blk_plan_t* p, int64_t* Dm1, int64_t* Dm2, int64_t* Dout) {
+    if (!p) {
+        blk_set_error("blk_plan_extents: plan is null");
+        return BLK_ERR_INVALID;
+    }
+    if (Dm1) *Dm1 = p->Dm1;
+    if (Dm2) *Dm2 = p->Dm2;
+    if (Dout) *Dout = p->Dout;
+    return BLK_OK;
+}
+
+extern "C" int blk_plan_offsets(const blk_plan_t* p, int64_t* a1, int64_t* a2, int64_t* ao) {
+    if (!p) {
+        blk_set_error("blk_plan_offsets: plan is null");
+        return BLK_ERR_INVALID;
+    }
+    const size_t n = (size_t)(p->S + 1) * sizeof(int64_t);
+    if (a1) std::memcpy(a1, p->a1.data(), n);
+    if (a2 && p->kind == 0) std::memcpy(a2, p->a2.data(), n);
+    if (ao) std::memcpy(ao, p->ao.data(), n);
+    return BLK_OK;
+}
+
+static int launches_per_run(const blk_plan* p) {
+    return (!p->tile_items.empty()) + (!p->simt_items.empty()) + (!p->small_items.empty()) +
+           (!p->umma_items.empty()) + (!p->smx_chunks.empty());
+}
+
+extern "C" int blk_plan_summary(const blk_plan_t* p, int64_t counts[8]) {
+    if (!p || !counts) {
+        blk_set_error("blk_plan_summary: null argument");
+        return BLK_ERR_INVALID;
+    }
+    counts[0] = p->S;
+    counts[1] = (int64_t)p->small_items.size();
+    counts[2] = (int64_t)p->tile_items.size();
+    counts[3] = (int64_t)p->umma_items.size();
+    counts[4] = (int64_t)p->smx_chunks.size();
+    counts[5] = p->H > 0 ? launches_per_run(p) : 0;
+    counts[6] = (int64_t)p->simt_items.size();
+    counts[7] = 0;
+    return BLK_OK;
+}
+
+extern "C" int blk_plan_work(const blk_plan_t* p, double* flops, double* bytes) {
+    if (!p) {
+        blk_set_error("blk_plan_work: plan is null");
+        return BLK_ERR_INVALID;
+    }
+    if (flops) *flops = p->flops;
+    if (bytes) *bytes = p->bytes;
+    return BLK_OK;
+}
+
+extern "C" int blk_plan_check(const blk_plan_t* p, void* cuda_stream) {
+    if (!p || p->device < 0) {
+        blk_set_error("blk_plan_check: plan has no device");
+        return BLK_ERR_INVALID;
+    }
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail("blk_plan_check: synchronize", e);
+    int status = 0;
+    e = cudaMemcpy(&status, p->d_status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail("blk_plan_check: read status", e);
+    if (status != 0) {
+        blk_set_error("a device-side bounded wait gave up (status " + std::to_string(status) + ")");
+        cudaMemset(p->d_status, 0, sizeof(int));
+        return BLK_ERR_TIMEOUT;
+    }
+    return BLK_OK;
+}
+
+extern "C" int blk_gemm_run(const blk_plan_t* p, const void* mat1, const void* mat2, void* out, float scale,
+                            void* cuda_stream) {
+    if (!p || p->kind != 0) {
+        blk_set_error("blk_gemm_run: not a GEMM plan");
+        return BLK_ERR_INVALID;
+    }
+    if (p->device < 0) {
+        blk_set_error("blk_gemm_run: the plan was created without a device");
+        return BLK_ERR_INVALID;
+    }
+    if (p->S == 0 || p->H == 0 || p->Dout == 0) return BLK_OK;
+    if (!out || (!mat1 && p->Dm1 > 0) || (!mat2 && p->Dm2 > 0)) {
+        blk_set_error("blk_gemm_run: null buffer");
+        return BLK_ERR_INVALID;
+    }
+    if (!aligned16(mat1) || !aligned16(mat2) || !aligned16(out)) {
+        blk_set_error("blk_gemm_run: device pointers must be 16-byte aligned");
+        return BLK_ERR_UNALIGNED;
+    }
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    cudaError_t e;
+    if (!p->simt_items.empty()) {
+        BlkSimtParams sp{};
+        sp.A = reinterpret_cast<const float*>(mat1);
+        sp.B = reinterpret_cast<const float*>(mat2);
+        sp.C = reinterpret_cast<float*>(out);
+        sp.segs = p->d_segs;
+        sp.items = p->d_simt_items;
+        sp.Dm1 = p->Dm1; sp.Dm2 = p->Dm2; sp.Dout = p->Dout;
+        sp.num_items = (int)p->simt_items.size();
+        sp.H = (int)p->H;
+        sp.ta = p->ta; sp.tb = p->tb;
+        sp.scale = scale;
+        if ((e = blk_launch_gemm_simt(sp, st)) != cudaSuccess) return cuda_fail("fp32 GEMM launch", e);
+        if (!p->smx_chunks.empty()) {
+            BlkSmxParams xp{};
+            xp.src = out; xp.dst = out;
+            xp.chunks = p->d_smx_chunks;
+            xp.D = p->Dout;
+            xp.num_chunks = (int)p->smx_chunks.size();
+            xp.H = (int)p->H;
+            xp.scale = 1.f;
+            if ((e = blk_launch_softmax(xp, BLK_F32, st)) != cudaSuccess) return cuda_fail("softmax launch", e);
+        }
+    }
+    if (!p->small_items.empty()) {
+        BlkSmallParams mp{};
+        mp.A = reinterpret_cast<const uint16_t*>(mat1);
+        mp.B = reinterpret_cast<const uint16_t*>(mat2);
+        mp.C = out;
+        mp.items = p->d_small_items;
+        mp.Dm1 = p->Dm1; mp.Dm2 = p->Dm2; mp.Dout = p->Dout;
+        mp.num_items = (int)p->small_items.size();
+        mp.H = (int)p->H;
+        mp.out_f32 = p->dtype_out == BLK_F32;
+        mp.epi = p->epi;
+        mp.scale = scale;
+        if ((e = blk_launch_scores_small(mp, p->dtype_in, p->small_K, st)) != cudaSuccess)
+            return cuda_fail("small-segment launch", e);
+    }
+    if (!p->tile_items.empty()) {
+        BlkGemmParams gp{};
+        gp.A = reinterpret_cast<const uint16_t*>(mat1);
+        gp.B = reinterpret_cast<const uint16_t*>(mat2);
+        gp.C = out;
+        gp.segs = p->d_segs;
+        gp.items = p->d_tile_items;
+        gp.Dm1 = p->Dm1; gp.Dm2 = p->Dm2; gp.Dout = p->Dout;
+        gp.num_items = (int)p->tile_items.size();
+        gp.H = (int)p->H;
+        gp.out_f32 = p->dtype_out == BLK_F32;
+        gp.epi = p->epi;
+        gp.scale = scale;
+        if ((e = blk_launch_gemm_tile(gp, p->dtype_in, p->ta, p->tb, st)) != cudaSuccess)
+            return cuda_fail("tile GEMM launch", e);
+    }
+    return BLK_OK;
+}
+
+extern "C" int blk_softmax_run(const blk_plan_t* p, const void* src, void* out, float scale, void* cuda_stream) {
+    if (!p || p->kind != 1) {
+        blk_set_error("blk_softmax_run: not a softmax plan");
+        return BLK_ERR_INVALID;
+    }
+    if (p->device < 0) {
+        blk_set_error("blk_softmax_run: the plan was created without a device");
+        return BLK_ERR_INVALID;
+    }
+    if (p->smx_chunks.empty() || p->H == 0) return BLK_OK;
+    if (!src || !out) {
+        blk_set_error("blk_softmax_run: null buffer");
+        return BLK_ERR_INVALID;
+    }
+    if (!aligned16(src) || !aligned16(out)) {
+        blk_set_error("blk_softmax_run: device pointers must be 16-byte aligned");
+        return BLK_ERR_UNALIGNED;
+    }
+    BlkSmxParams xp{};
+    xp.src = src;
+    xp.dst = out;
+    xp.chunks = p->d_smx_chunks;
+    xp.D = p->Dm1;
+    xp.num_chunks = (int)p->smx_chunks.size();
+    xp.H = (int)p->H;
+    xp.scale = scale;
+    cudaError_t e = blk_launch_softmax(xp, p->dtype_in, reinterpret_cast<cudaStream_t>(cuda_stream));
+    if (e != cudaSuccess) return cuda_fail("softmax launch", e);
+    return BLK_OK;
+}

@@ -1,0 +1,362 @@
+// Host side of libblkattn that needs no CUDA: error text, index helpers,
+// multi-GPU partitioners and the segment scheduler that bins segments onto the
+// kernels.  Everything here runs (and is tested) on a machine without a GPU.
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <numeric>
+#include <queue>
+#include <string>
+
+#include "blk_internal.h"
+
+static thread_local std::string g_last_error;
+
+void blk_set_error(const std::string& msg) { g_last_error = msg; }
+
+bool blk_env_flag(const char* name) {
+    const char* v = std::getenv(name);
+    return v && v[0] && std::strcmp(v, "0") != 0;
+}
+
+extern "C" const char* blk_last_error(void) { return g_last_error.c_str(); }
+extern "C" const char* blk_version(void) { return "blkattn-b200 0.1 (sm_100a)"; }
+
+// ---------------------------------------------------------------------------
+// index helpers
+// ---------------------------------------------------------------------------
+static bool mul_ok(int64_t a, int64_t b, int64_t* out) {
+    return !__builtin_mul_overflow(a, b, out);
+}
+
+extern "C" int blk_offsets_from_lists(const int64_t* M, const int64_t* N, const int64_t* K,
+                                      int64_t S, int64_t* a1, int64_t* a2, int64_t* ao) {
+    if (S < 0 || (S > 0 && (!M || !N || !K)) || !a1 || !a2 || !ao) {
+        blk_set_error("blk_offsets_from_lists: null argument");
+        return BLK_ERR_INVALID;
+    }
+    a1[0] = a2[0] = ao[0] = 0;
+    for (int64_t s = 0; s < S; ++s) {
+        int64_t mk, nk, mn;
+        if (M[s] < 0 || N[s] < 0 || K[s] < 0 || !mul_ok(M[s], K[s], &mk) || !mul_ok(N[s], K[s], &nk) ||
+            !mul_ok(M[s], N[s], &mn) || __builtin_add_overflow(a1[s], mk, &a1[s + 1]) ||
+            __builtin_add_overflow(a2[s], nk, &a2[s + 1]) || __builtin_add_overflow(ao[s], mn, &ao[s + 1])) {
+            blk_set_error("blk_offsets_from_lists: negative extent or int64 overflow at segment " + std::to_string(s));
+            return BLK_ERR_INVALID;
+        }
+    }
+    return BLK_OK;
+}
+
+extern "C" int blk_softmax_offsets(const int64_t* rows, const int64_t* cols, int64_t S, int64_t* acc) {
+    if (S < 0 || (S > 0 && (!rows || !cols)) || !acc) {
+        blk_set_error("blk_softmax_offsets: null argument");
+        return BLK_ERR_INVALID;
+    }
+    acc[0] = 0;
+    for (int64_t s = 0; s < S; ++s) {
+        int64_t rc;
+        if (rows[s] < 0 || cols[s] < 0 || !mul_ok(rows[s], cols[s], &rc) ||
+            __builtin_add_overflow(acc[s], rc, &acc[s + 1])) {
+            blk_set_error("blk_softmax_offsets: negative extent or int64 overflow at segment " + std::to_string(s));
+            return BLK_ERR_INVALID;
+        }
+    }
+    return BLK_OK;
+}
+
+static uint64_t isqrt_u128(unsigned __int128 v) {
+    if (v == 0) return 0;
+    long double approx = std::sqrt((long double)v);
+    uint64_t r = (uint64_t)approx;
+    while ((unsigned __int128)r * r > v) --r;
+    while ((unsigned __int128)(r + 1) * (r + 1) <= v) ++r;
+    return r;
+}
+
+extern "C" int blk_lists_from_offsets(const int64_t* a1, const int64_t* a2, const int64_t* ao, int64_t S,
+                                      int64_t* M, int64_t* N, int64_t* K) {
+    if (S < 0 || (S > 0 && (!a1 || !a2 || !ao || !M || !N || !K))) {
+        blk_set_error("blk_lists_from_offsets: null argument");
+        return BLK_ERR_INVALID;
+    }
+    for (int64_t s = 0; s < S; ++s) {
+        const int64_t mk = a1[s + 1] - a1[s], nk = a2[s + 1] - a2[s], mn = ao[s + 1] - ao[s];
+        if (mk <= 0 || nk <= 0 || mn <= 0) {
+            blk_set_error("blk_lists_from_offsets: segment " + std::to_string(s) +
+                          " has an empty extent; (M,N,K) cannot be recovered from offsets");
+            return BLK_ERR_INVALID;
+        }
+        const unsigned __int128 num = (unsigned __int128)mk * (unsigned __int128)mn;
+        bool ok = (num % (unsigned __int128)nk) == 0;
+        uint64_t m = 0;
+        if (ok) {
+            const unsigned __int128 m2 = num / (unsigned __int128)nk;
+            m = isqrt_u128(m2);
+            ok = m > 0 && (unsigned __int128)m * m == m2 && mn % (int64_t)m == 0 && mk % (int64_t)m == 0 &&
+                 (unsigned __int128)(mn / (int64_t)m) * (unsigned __int128)(mk / (int64_t)m) == (unsigned __int128)nk;
+        }
+        if (!ok) {
+            blk_set_error("blk_lists_from_offsets: offsets of segment " + std::to_string(s) +
+                          " are not those of an (M,N,K) segment");
+            return BLK_ERR_INVALID;
+        }
+        M[s] = (int64_t)m;
+        N[s] = mn / (int64_t)m;
+        K[s] = mk / (int64_t)m;
+    }
+    return BLK_OK;
+}
+
+// ---------------------------------------------------------------------------
+// partitioning
+// ---------------------------------------------------------------------------
+extern "C" int blk_segment_cost(const int64_t* M, const int64_t* N, const int64_t* K, int64_t S, int64_t H,
+                                int in_bytes, int out_bytes, double flops_per_s, double bytes_per_s,
+                                double* cost) {
+    if (S < 0 || (S > 0 && (!M || !N || !K || !cost)) || flops_per_s <= 0 || bytes_per_s <= 0 || H < 0) {
+        blk_set_error("blk_segment_cost: bad argument");
+        return BLK_ERR_INVALID;
+    }
+    for (int64_t s = 0; s < S; ++s) {
+        const double m = (double)M[s], n = (double)N[s], k = (double)K[s];
+        const double fl = 2.0 * m * n * k;
+        const double by = (m + n) * k * in_bytes + m * n * out_bytes;
+        cost[s] = (double)H * std::max(fl / flops_per_s, by / bytes_per_s);
+    }
+    return BLK_OK;
+}
+
+// Number of ranges a greedy left-to-right fill needs when no range may exceed cap.
+static int64_t ranges_needed(const double* cost, int64_t S, double cap) {
+    int64_t cnt = 1;
+    double cur = 0;
+    for (int64_t s = 0; s < S; ++s) {
+        if (cost[s] > cap) return INT64_MAX;
+        if (cur + cost[s] > cap) {
+            ++cnt;
+            cur = 0;
+        }
+        cur += cost[s];
+    }
+    return cnt;
+}
+
+extern "C" int blk_partition_contiguous(const double* cost, int64_t S, int R, int64_t* bounds) {
+    if (S < 0 || R < 1 || !bounds || (S > 0 && !cost)) {
+        blk_set_error("blk_partition_contiguous: bad argument");
+        return BLK_ERR_INVALID;
+    }
+    double total = 0, mx = 0;
+    for (int64_t s = 0; s < S; ++s) {
+        if (!(cost[s] >= 0)) {
+            blk_set_error("blk_partition_contiguous: negative or NaN cost");
+            return BLK_ERR_INVALID;
+        }
+        total += cost[s];
+        mx = std::max(mx, cost[s]);
+    }
+    // bisection on the bottleneck value
+    double lo = std::max(mx, total / R), hi = total;
+    if (ranges_needed(cost, S, lo) <= R) hi = lo;
+    for (int it = 0; it < 100 && hi - lo > 1e-10 * hi; ++it) {
+        const double mid = 0.5 * (lo + hi);
+        if (ranges_needed(cost, S, mid) <= R) hi = mid; else lo = mid;
+    }
+    // materialise the split for cap = hi: greedy fill, then spread empty tail ranges
+    std::vector<int64_t> b(R + 1, S);
+    b[0] = 0;
+    {
+        int r = 0;
+        double cur = 0;
+        int64_t start = 0;
+        const double cap = hi * (1 + 1e-12);
+        for (int64_t s = 0; s < S; ++s) {
+            if (cur + cost[s] > cap && s > start && r + 1 < R) {  // s > start: never emit an empty range
+                b[++r] = s;
+                cur = 0;
+                start = s;
+            }
+            cur += cost[s];
+        }
+        for (int q = r + 1; q <= R; ++q) b[q] = S;
+    }
+    for (int r = 0; r <= R; ++r) bounds[r] = b[r];
+    return BLK_OK;
+}
+
+extern "C" int blk_partition_lpt(const double* cost, int64_t S, int R, int32_t* owner) {
+    if (S < 0 || R < 1 || (S > 0 && (!cost || !owner))) {
+        blk_set_error("blk_partition_lpt: bad argument");
+        return BLK_ERR_INVALID;
+    }
+    std::vector<int64_t> order(S);
+    std::iota(order.begin(), order.end(), 0);
+    std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return cost[a] > cost[b]; });
+    typedef std::pair<double, int> Load;  // (load, rank); smallest load first, ties to the lowest rank
+    std::priority_queue<Load, std::vector<Load>, std::greater<Load>> pq;
+    for (int r = 0; r < R; ++r) pq.push(Load(0.0, r));
+    for (int64_t i = 0; i < S; ++i) {
+        Load l = pq.top();
+        pq.pop();
+        owner[order[i]] = l.second;
+        l.first += cost[order[i]];
+        pq.push(l);
+    }
+    return BLK_OK;
+}
+
+// ---------------------------------------------------------------------------
+// scheduler
+// ---------------------------------------------------------------------------
+static int elem_bytes(int dtype) { return dtype == BLK_F32 ? 4 : 2; }
+
+// Widest access class usable at `off` with row pitch `pitch` on every head of
+// a (H, D) buffer of es-byte elements: 2 -> 16 bytes, 1 -> 4 bytes (a pair of
+// 16-bit elements; one fp32 element), 0 -> one element.
+static int access_class(int64_t H, int64_t D, int64_t off, int64_t pitch, int es) {
+    const int64_t v16 = 16 / es, v4 = es == 2 ? 2 : 1;
+    auto ok = [&](int64_t v) { return (H <= 1 || D % v == 0) && off % v == 0 && pitch % v == 0; };
+    if (ok(v16)) return 2;
+    if (ok(v4)) return 1;
+    return 0;
+}
+
+static int validate_offsets(const char* what, const std::vector<int64_t>& acc, const std::vector<int64_t>& need,
+                            int64_t S) {
+    if (acc[0] < 0) {
+        blk_set_error(std::string(what) + ": first offset is negative");
+        return BLK_ERR_INVALID;
+    }
+    for (int64_t s = 0; s < S; ++s) {
+        if (acc[s + 1] < acc[s] || acc[s + 1] - acc[s] < need[s]) {
+            blk_set_error(std::string(what) + ": offsets of segment " + std::to_string(s) +
+                          " do not leave room for its extents (need " + std::to_string(need[s]) + " elements, have " +
+                          std::to_string(acc[s + 1] - acc[s]) + ")");
+            return BLK_ERR_INVALID;
+        }
+    }
+    return BLK_OK;
+}
+
+int blk_build_gemm_schedule(blk_plan* p) {
+    const int64_t S = p->S;
+    const int es_in = elem_bytes(p->dtype_in), es_out = elem_bytes(p->dtype_out);
+    std::vector<int64_t> needA(S), needB(S), needC(S);
+    for (int64_t s = 0; s < S; ++s) {
+        const int64_t m = p->M[s], n = p->N[s], k = p->K[s];
+        if (m < 0 || n < 0 || k < 0 || m > INT32_MAX / 2 || n > INT32_MAX / 2 || k > INT32_MAX / 2) {
+            blk_set_error("gemm plan: extent of segment " + std::to_string(s) + " is negative or exceeds 2^30");
+            return BLK_ERR_INVALID;
+        }
+        if (!mul_ok(m, k, &needA[s]) || !mul_ok(n, k, &needB[s]) || !mul_ok(m, n, &needC[s])) {
+            blk_set_error("gemm plan: int64 overflow");
+            return BLK_ERR_INVALID;
+        }
+    }
+    int rc;
+    if ((rc = validate_offsets("gemm plan: mat1Accum", p->a1, needA, S)) != BLK_OK) return rc;
+    if ((rc = validate_offsets("gemm plan: mat2Accum", p->a2, needB, S)) != BLK_OK) return rc;
+    if ((rc = validate_offsets("gemm plan: outAccum", p->ao, needC, S)) != BLK_OK) return rc;
+    p->Dm1 = p->a1[S];
+    p->Dm2 = p->a2[S];
+    p->Dout = p->ao[S];
+
+    const bool allow_small = !blk_env_flag("BLK_DISABLE_SMALL");
+    p->segs.resize(S);
+    p->flops = p->bytes = 0;
+    for (int64_t s = 0; s < S; ++s) {
+        const int64_t m = p->M[s], n = p->N[s], k = p->K[s];
+        BlkSeg& sd = p->segs[s];
+        sd.offA = p->a1[s];
+        sd.offB = p->a2[s];
+        sd.offC = p->ao[s];
+        sd.M = (int32_t)m;
+        sd.N = (int32_t)n;
+        sd.K = (int32_t)k;
+        const int cA = access_class(p->H, p->Dm1, sd.offA, p->ta ? m : k, es_in);
+        const int cB = access_class(p->H, p->Dm2, sd.offB, p->tb ? n : k, es_in);
+        sd.clsIn = (uint8_t)std::min(cA, cB);
+        sd.clsOut = (uint8_t)access_class(p->H, p->Dout, sd.offC, n, es_out);
+        sd.pad[0] = sd.pad[1] = 0;
+        p->flops += 2.0 * (double)p->H * (double)m * (double)n * (double)k;
+        p->bytes += (double)p->H * ((double)(m + n) * (double)k * es_in + (double)m * (double)n * es_out);
+        if (m == 0 || n == 0) continue;
+
+        if (p->dtype_in == BLK_F32) {
+            const int32_t tms = (int32_t)((m + BLK_SIMT_BM - 1) / BLK_SIMT_BM);
+            const int32_t tns = (int32_t)((n + BLK_SIMT_BN - 1) / BLK_SIMT_BN);
+            for (int32_t tm = 0; tm < tms; ++tm)
+                for (int32_t tn = 0; tn < tns; ++tn) p->simt_items.push_back(BlkTileItem{(int32_t)s, tm, tn, 1});
+            continue;
+        }
+        // Packed small-segment kernel: one warp per (segment, head).
+        const bool small_ok = allow_small && !p->ta && !p->tb && n <= BLK_SMALL_MAXN && m <= 4 * BLK_SMALL_MAXN &&
+                              (k == 32 || k == 64) && sd.clsIn == 2 &&
+                              (p->small_K == 0 || p->small_K == (int)k);
+        if (small_ok) {
+            p->small_K = (int)k;
+            p->small_items.push_back(BlkSmallItem{sd.offA, sd.offB, sd.offC, (int32_t)m, (int32_t)n});
+            continue;
+        }
+        const int32_t tms = (int32_t)((m + BLK_TILE_BM - 1) / BLK_TILE_BM);
+        const int32_t tns = (int32_t)((n + BLK_TILE_BN - 1) / BLK_TILE_BN);
+        for (int32_t tm = 0; tm < tms; ++tm) {
+            if (p->epi == BLK_EPI_SOFTMAX) {
+                p->tile_items.push_back(BlkTileItem{(int32_t)s, tm, 0, tns});
+            } else {
+                for (int32_t tn = 0; tn < tns; ++tn) p->tile_items.push_back(BlkTileItem{(int32_t)s, tm, tn, 1});
+            }
+        }
+    }
+    // fp32 inputs with the softmax epilogue: SIMT GEMM, then the softmax kernel in place.
+    if (p->dtype_in == BLK_F32 && p->epi == BLK_EPI_SOFTMAX) {
+        blk_plan tmp;
+        tmp.kind = 1;
+        tmp.S = S;
+        tmp.H = p->H;
+        tmp.dtype_in = tmp.dtype_out = BLK_F32;
+        tmp.M = p->M;
+        tmp.N = p->N;
+        tmp.a1 = p->ao;
+        if ((rc = blk_build_softmax_schedule(&tmp)) != BLK_OK) return rc;
+        p->smx_chunks.swap(tmp.smx_chunks);
+    }
+    return BLK_OK;
+}
+
+int blk_build_softmax_schedule(blk_plan* p) {
+    const int64_t S = p->S;
+    const int es = elem_bytes(p->dtype_in);
+    std::vector<int64_t> need(S);
+    for (int64_t s = 0; s < S; ++s) {
+        if (p->M[s] < 0 || p->N[s] < 0 || p->M[s] > INT32_MAX / 2 || p->N[s] > INT32_MAX / 2 ||
+            !mul_ok(p->M[s], p->N[s], &need[s])) {
+            blk_set_error("softmax plan: extent of segment " + std::to_string(s) + " is negative or too large");
+            return BLK_ERR_INVALID;
+        }
+    }
+    int rc;
+    if ((rc = validate_offsets("softmax plan: srcAccum", p->a1, need, S)) != BLK_OK) return rc;
+    p->Dm1 = p->Dout = p->a1[S];
+    p->Dm2 = 0;
+    p->flops = 0;
+    p->bytes = 0;
+    const int64_t window = BLK_SMX_WINDOW_BYTES / es;  // elements
+    for (int64_t s = 0; s < S; ++s) {
+        const int64_t rows = p->M[s], cols = p->N[s];
+        p->bytes += 2.0 * (double)p->H * (double)rows * (double)cols * es;
+        if (rows == 0 || cols == 0) continue;
+        if (cols > window) {
+            for (int64_t r = 0; r < rows; ++r)
+                p->smx_chunks.push_back(BlkSmxChunk{p->a1[s] + r * cols, 1, (int32_t)cols});
+        } else {
+            const int64_t rpc = window / cols;
+            for (int64_t r = 0; r < rows; r += rpc)
+                p->smx_chunks.push_back(
+                    BlkSmxChunk{p->a1[s] + r * cols, (int32_t)std::min(rpc, rows - r), (int32_t)cols});
+        }
+    }
+    return BLK_OK;
+}

@@ -1,0 +1,109 @@
+// Internal declarations shared by the host scheduler and the kernels of
+// libblkattn.  Not part of the public ABI (that is include/blkattn.h).
+#pragma once
+#include <stdint.h>
+#include <string>
+#include <vector>
+
+#include "blkattn.h"
+
+// ---- device-visible schedule records ---------------------------------------
+
+// One segment of the packed batch.  Offsets are in elements inside a head
+// strip.  cls is the widest access the kernels may use for this segment on
+// every head: 2 -> 16-byte vectors, 1 -> 4-byte pairs, 0 -> single elements.
+struct BlkSeg {
+    int64_t offA, offB, offC;
+    int32_t M, N, K;
+    uint8_t clsIn;   // min over both inputs
+    uint8_t clsOut;  // output
+    uint8_t pad[2];
+};
+static_assert(sizeof(BlkSeg) == 40, "BlkSeg layout");
+
+// One CTA of the staged mma.sync kernel: rows [tm*BM, ...) of segment seg and
+// column tiles tn .. tn+ntn-1 (ntn > 1 only when the softmax epilogue sweeps
+// the whole row).
+struct BlkTileItem {
+    int32_t seg;
+    int32_t tm;
+    int32_t tn;
+    int32_t ntn;
+};
+
+// One warp of the packed small-segment kernel: a whole (segment, head) score
+// block with N <= 64, K a multiple of 32, everything 16-byte aligned.
+struct BlkSmallItem {
+    int64_t offA, offB, offC;
+    int32_t M, N;
+};
+static_assert(sizeof(BlkSmallItem) == 32, "BlkSmallItem layout");
+
+// One CTA of the softmax kernel: `rows` consecutive rows of `cols` elements
+// starting at element `off` of the head strip.  rows*cols fits the CTA's
+// shared-memory window, or rows == 1 for a row longer than the window.
+struct BlkSmxChunk {
+    int64_t off;
+    int32_t rows;
+    int32_t cols;
+};
+
+// Per-CTA tile of the tcgen05 kernel (filled in by blk_gemm_umma.cu's planner).
+struct BlkUmmaItem {
+    int32_t seg;
+    int32_t tm;       // 128-row block inside the segment
+    int32_t rowA;     // first row of that block in the [sum M, K] operand view
+    int32_t rowB;     // first row of the segment in the [sum N, K] operand view
+    int64_t offC;     // element offset of the segment's output block
+    int32_t M, N;
+};
+
+// ---- kernel geometry constants the scheduler must agree with ----------------
+constexpr int BLK_TILE_BM = 64;
+constexpr int BLK_TILE_BN = 128;
+constexpr int BLK_TILE_BK = 32;
+constexpr int BLK_SIMT_BM = 64;
+constexpr int BLK_SIMT_BN = 64;
+constexpr int BLK_SMALL_MAXN = 64;
+constexpr int BLK_SMALL_WARPS = 4;
+constexpr int BLK_SMX_WINDOW_BYTES = 16384;
+constexpr int BLK_UMMA_BM = 128;
+
+// ---- the plan ----------------------------------------------------------------
+struct blk_plan {
+    int kind = 0;  // 0 GEMM, 1 softmax
+    int64_t S = 0, H = 0;
+    int dtype_in = 0, dtype_out = 0, ta = 0, tb = 0, epi = 0, device = -1;
+    std::vector<int64_t> M, N, K, a1, a2, ao;
+    int64_t Dm1 = 0, Dm2 = 0, Dout = 0;
+    double flops = 0, bytes = 0;
+
+    std::vector<BlkSeg> segs;
+    std::vector<BlkTileItem> tile_items;    // staged mma.sync kernel (16-bit inputs)
+    std::vector<BlkTileItem> simt_items;    // fp32 SIMT kernel
+    std::vector<BlkSmallItem> small_items;  // packed small-segment kernel
+    std::vector<BlkUmmaItem> umma_items;    // tcgen05 kernel
+    std::vector<BlkSmxChunk> smx_chunks;    // softmax kernel (also second pass of fp32 scores)
+    int umma_K = 0;                         // uniform K of the tcgen05 bin
+    int small_K = 0;                        // uniform K of the small bin
+
+    // device copies
+    BlkSeg* d_segs = nullptr;
+    BlkTileItem* d_tile_items = nullptr;
+    BlkTileItem* d_simt_items = nullptr;
+    BlkSmallItem* d_small_items = nullptr;
+    BlkUmmaItem* d_umma_items = nullptr;
+    BlkSmxChunk* d_smx_chunks = nullptr;
+    int* d_status = nullptr;
+    int* d_counter = nullptr;  // persistent-kernel tile counter
+};
+
+void blk_set_error(const std::string& msg);
+
+// Host scheduling (blk_host.cpp) -- no CUDA calls.
+int blk_build_gemm_schedule(blk_plan* p);
+int blk_build_softmax_schedule(blk_plan* p);
+
+// Environment overrides used by the benchmark harness to force a path:
+// BLK_DISABLE_SMALL=1, BLK_DISABLE_UMMA=1.
+bool blk_env_flag(const char* name);

@@ -1,0 +1,61 @@
+// Kernel parameter blocks and launcher prototypes (internal).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "blk_internal.h"
+
+struct BlkGemmParams {
+    const uint16_t* A;
+    const uint16_t* B;
+    void* C;
+    const BlkSeg* segs;
+    const BlkTileItem* items;
+    int64_t Dm1, Dm2, Dout;
+    int num_items;
+    int H;
+    int out_f32;
+    int epi;
+    float scale;
+};
+
+struct BlkSimtParams {
+    const float* A;
+    const float* B;
+    float* C;
+    const BlkSeg* segs;
+    const BlkTileItem* items;
+    int64_t Dm1, Dm2, Dout;
+    int num_items;
+    int H;
+    int ta, tb;
+    float scale;
+};
+
+struct BlkSmallParams {
+    const uint16_t* A;
+    const uint16_t* B;
+    void* C;
+    const BlkSmallItem* items;
+    int64_t Dm1, Dm2, Dout;
+    int num_items;
+    int H;
+    int out_f32;
+    int epi;
+    float scale;
+};
+
+struct BlkSmxParams {
+    const void* src;
+    void* dst;
+    const BlkSmxChunk* chunks;
+    int64_t D;
+    int num_chunks;
+    int H;
+    float scale;
+};
+
+cudaError_t blk_launch_gemm_tile(const BlkGemmParams& p, int dtype_in, int ta, int tb, cudaStream_t st);
+cudaError_t blk_launch_gemm_simt(const BlkSimtParams& p, cudaStream_t st);
+cudaError_t blk_launch_scores_small(const BlkSmallParams& p, int dtype_in, int K, cudaStream_t st);
+cudaError_t blk_launch_softmax(const BlkSmxParams& p, int dtype, cudaStream_t st);

@@ -1,0 +1,202 @@
+"""Plan objects: the host-built segment schedule of one varlen problem, uploaded
+once and reused by every call on the same lists.
+
+A plan is what replaces the per-call host work of the upstream launchers
+(``csrc/cuda/spBlkGEMM.cu:943-1006``: seven device->host syncs, a host loop over
+tiles and an upload per GEMM call; ``csrc/cuda/spBlkSoftmax.cu:358-396``: a
+per-row table).  Lists are taken on the host; running a plan launches kernels
+on torch's current stream and does not synchronise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib as L
+
+_DTYPES = {torch.float16: L.BLK_F16, torch.bfloat16: L.BLK_BF16, torch.float32: L.BLK_F32}
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPES[dt]
+    except KeyError:
+        raise RuntimeError(f"blockedattention_b200: dtype {dt} is not supported (float16, bfloat16, float32)")
+
+
+def _host_i64(x) -> Optional[np.ndarray]:
+    if x is None:
+        return None
+    if isinstance(x, torch.Tensor):
+        x = x.detach().to("cpu", torch.int64).numpy()
+    return np.ascontiguousarray(np.asarray(x, dtype=np.int64))
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class _Plan:
+    def __init__(self):
+        self._h = C.c_void_p()
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h:
+            L.lib.blk_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def extents(self):
+        a, b, c = C.c_int64(), C.c_int64(), C.c_int64()
+        L.check(L.lib.blk_plan_extents(self._h, C.byref(a), C.byref(b), C.byref(c)))
+        return a.value, b.value, c.value
+
+    @property
+    def summary(self) -> dict:
+        arr = (C.c_int64 * 8)()
+        L.check(L.lib.blk_plan_summary(self._h, arr))
+        keys = ["segments", "small_items", "tile_items", "umma_items", "softmax_chunks", "launches", "simt_items"]
+        return {k: int(arr[i]) for i, k in enumerate(keys)}
+
+    @property
+    def work(self):
+        """(algorithmic flops, algorithmic bytes) of one run over all heads."""
+        f, b = C.c_double(), C.c_double()
+        L.check(L.lib.blk_plan_work(self._h, C.byref(f), C.byref(b)))
+        return f.value, b.value
+
+    def check(self):
+        """Synchronises the current stream and raises if a kernel reported a timed-out wait."""
+        L.check(L.lib.blk_plan_check(self._h, C.c_void_p(_stream_ptr(self.device))))
+
+
+class GemmPlan(_Plan):
+    """Schedule for ``out_s = epilogue(scale * A_s B_s^T)`` over S segments and H heads.
+
+    ``MList/NList/KList``: host sequences (or tensors, copied to the host once).
+    ``accum``: optional ``(mat1Accum, mat2Accum, outAccum)`` triple; default is
+    the packed offsets ``cumsum([0, M*K])`` etc. (upstream
+    ``csrc/sparseBlockedAttention.cpp:22-29``).  ``device=None`` builds the
+    schedule only (no GPU needed).
+    """
+
+    def __init__(self, MList, NList, KList, H: int, dtype_in: torch.dtype, dtype_out: Optional[torch.dtype] = None,
+                 transpose1: bool = False, transpose2: bool = False, softmax: bool = False,
+                 accum: Optional[Sequence] = None, device=None):
+        super().__init__()
+        self.M, self.N, self.K = _host_i64(MList), _host_i64(NList), _host_i64(KList)
+        if not (len(self.M) == len(self.N) == len(self.K)):
+            raise RuntimeError("MList, NList and KList must have the same length")
+        self.S, self.H = len(self.M), int(H)
+        self.dtype_in = dtype_in
+        self.dtype_out = dtype_out if dtype_out is not None else dtype_in
+        self.softmax = bool(softmax)
+        self.device = torch.device(device) if device is not None else None
+        a1 = a2 = ao = None
+        if accum is not None:
+            a1, a2, ao = (_host_i64(a) for a in accum)
+            for a in (a1, a2, ao):
+                if len(a) != self.S + 1:
+                    raise RuntimeError("offset arrays must have one more entry than the lists")
+        dev = -1 if self.device is None else (self.device.index if self.device.index is not None
+                                               else torch.cuda.current_device())
+        L.check(L.lib.blk_gemm_plan_create(
+            C.byref(self._h), L.i64(self.M), L.i64(self.N), L.i64(self.K), L.i64(a1), L.i64(a2), L.i64(ao),
+            self.S, self.H, dtype_code(self.dtype_in), dtype_code(self.dtype_out), int(transpose1), int(transpose2),
+            L.BLK_EPI_SOFTMAX if softmax else L.BLK_EPI_SCORES, dev))
+        self.Dm1, self.Dm2, self.Dout = self.extents
+
+    @property
+    def offsets(self):
+        a1 = np.empty(self.S + 1, np.int64); a2 = np.empty_like(a1); ao = np.empty_like(a1)
+        L.check(L.lib.blk_plan_offsets(self._h, L.i64(a1), L.i64(a2), L.i64(ao)))
+        return a1, a2, ao
+
+    def run(self, mat1: torch.Tensor, mat2: torch.Tensor, out: Optional[torch.Tensor] = None,
+            scale: float = 1.0) -> torch.Tensor:
+        if self.device is None:
+            raise RuntimeError("this plan was built without a device")
+        for name, t, D in (("mat1", mat1, self.Dm1), ("mat2", mat2, self.Dm2)):
+            if not t.is_cuda:
+                raise RuntimeError(f"{name} must be a CUDA tensor")
+            if not t.is_contiguous():
+                raise RuntimeError(f"{name} must be contiguous")
+            if t.dtype != self.dtype_in:
+                raise RuntimeError(f"{name} has dtype {t.dtype}, the plan was built for {self.dtype_in}")
+            if t.numel() != self.H * D:
+                raise RuntimeError(f"{name} has {t.numel()} elements, expected H*D = {self.H}*{D}")
+        if out is None:
+            out = torch.empty((self.H, self.Dout), dtype=self.dtype_out, device=mat1.device)
+        elif (not out.is_cuda or not out.is_contiguous() or out.dtype != self.dtype_out
+              or out.numel() != self.H * self.Dout):
+            raise RuntimeError("out must be a contiguous CUDA tensor of the plan's dtype with H*Dout elements")
+        if mat1.data_ptr() % 16:
+            mat1 = mat1.clone()
+        if mat2.data_ptr() % 16:
+            mat2 = mat2.clone()
+        if out.data_ptr() % 16:
+            raise RuntimeError("out must be 16-byte aligned")
+        with torch.cuda.device(mat1.device):
+            L.check(L.lib.blk_gemm_run(self._h, C.c_void_p(mat1.data_ptr()), C.c_void_p(mat2.data_ptr()),
+                                       C.c_void_p(out.data_ptr()), C.c_float(scale),
+                                       C.c_void_p(_stream_ptr(mat1.device))))
+        return out
+
+
+class SoftmaxPlan(_Plan):
+    """Schedule for the row softmax of S packed (rows_s, cols_s) blocks per head."""
+
+    def __init__(self, rowList, colList, H: int, dtype: torch.dtype, accum=None, device=None):
+        super().__init__()
+        self.rows, self.cols = _host_i64(rowList), _host_i64(colList)
+        if len(self.rows) != len(self.cols):
+            raise RuntimeError("rowList and colList must have the same length")
+        self.S, self.H, self.dtype = len(self.rows), int(H), dtype
+        self.device = torch.device(device) if device is not None else None
+        acc = _host_i64(accum)
+        if acc is not None and len(acc) != self.S + 1:
+            raise RuntimeError("srcAccum must have one more entry than the lists")
+        dev = -1 if self.device is None else (self.device.index if self.device.index is not None
+                                               else torch.cuda.current_device())
+        L.check(L.lib.blk_softmax_plan_create(C.byref(self._h), L.i64(self.rows), L.i64(self.cols), L.i64(acc),
+                                              self.S, self.H, dtype_code(dtype), dev))
+        self.D = self.extents[0]
+
+    @property
+    def offsets(self):
+        a = np.empty(self.S + 1, np.int64)
+        L.check(L.lib.blk_plan_offsets(self._h, L.i64(a), None, None))
+        return a
+
+    def run(self, src: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+        if self.device is None:
+            raise RuntimeError("this plan was built without a device")
+        if not src.is_cuda:
+            raise RuntimeError("src must be a CUDA tensor")
+        if not src.is_contiguous():
+            raise RuntimeError("src must be contiguous")
+        if src.dtype != self.dtype:
+            raise RuntimeError(f"src has dtype {src.dtype}, the plan was built for {self.dtype}")
+        if src.numel() != self.H * self.D:
+            raise RuntimeError(f"src has {src.numel()} elements, expected H*D = {self.H}*{self.D}")
+        if out is None:
+            out = torch.empty((self.H, self.D), dtype=self.dtype, device=src.device)
+        elif not out.is_cuda or not out.is_contiguous() or out.dtype != self.dtype or out.numel() != src.numel():
+            raise RuntimeError("out must be a contiguous CUDA tensor shaped like src")
+        if src.data_ptr() % 16:
+            src = src.clone()
+        if out.data_ptr() % 16:
+            raise RuntimeError("out must be 16-byte aligned")
+        with torch.cuda.device(src.device):
+            L.check(L.lib.blk_softmax_run(self._h, C.c_void_p(src.data_ptr()), C.c_void_p(out.data_ptr()),
+                                          C.c_float(scale), C.c_void_p(_stream_ptr(src.device))))
+        return out

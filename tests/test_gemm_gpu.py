@@ -1,0 +1,232 @@
+"""GPU parity of the varlen blocked GEMM (all kernels behind blk_gemm_run) with
+the CPU oracle, through the C ABI (GemmPlan -> ctypes -> libblkattn)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import O, assert_probs_close, assert_scores_close, packed_inputs
+from blockedattention_b200 import blockAttnScores, blockGEMM, blockSoftmax
+from blockedattention_b200 import _lib as L
+from blockedattention_b200.plan import GemmPlan
+from blockedattention_b200.synth import workload
+
+pytestmark = pytest.mark.gpu
+F16, BF16, F32 = torch.float16, torch.bfloat16, torch.float32
+
+
+def run_case(dev, M, N, K, H, dtype, ta=False, tb=False, softmax=False, scale=1.0, out_dtype=None, seed=0,
+             dist="normal", std=1.0, accum=None, env=None, what=""):
+    M = np.asarray(M, np.int64); N = np.asarray(N, np.int64); K = np.asarray(K, np.int64)
+    a1 = a2 = ao = None
+    if accum is not None:
+        a1, a2, ao = accum
+    A, B = packed_inputs(M, N, K, H, dtype, seed, dist, std, a1, a2)
+    ref = O.block_gemm(A, B, M, N, K, a1, a2, ao, ta, tb, scale)
+    if softmax:
+        ref = O.block_softmax(ref, M, N, ao)
+    old = {}
+    for k, v in (env or {}).items():
+        old[k] = os.environ.get(k); os.environ[k] = v
+    try:
+        plan = GemmPlan(M, N, K, H, dtype, out_dtype, ta, tb, softmax, accum=accum, device=dev)
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+    out = torch.full((H, plan.Dout), float("nan"), dtype=plan.dtype_out, device=dev)
+    plan.run(A.to(dev), B.to(dev), out=out, scale=scale)
+    torch.cuda.synchronize()
+    got = out.float().cpu()
+    if accum is not None:  # gaps between segments are not written: compare segment by segment
+        keep = torch.zeros(plan.Dout, dtype=torch.bool)
+        for s in range(len(M)):
+            keep[ao[s]:ao[s] + M[s] * N[s]] = True
+        assert torch.isnan(got[:, ~keep]).all(), f"{what}: wrote outside the segments"
+        got, ref = got[:, keep], ref[:, keep]
+    (assert_probs_close if softmax else assert_scores_close)(got, ref, what)
+    return plan
+
+
+def test_upstream_author_shapes(cuda_device):
+    # csrc/sparseBlockedAttention.cpp:170-199 (odd K), :216-255, :147-155; test/pytest.py:7-19
+    run_case(cuda_device, [33, 127], [33, 127], [61, 61], 8, F16, what="odd K fp16")
+    run_case(cuda_device, [33, 127], [33, 127], [61, 61], 8, BF16, what="odd K bf16")
+    run_case(cuda_device, [11], [13], [5], 1, F16, what="11x13x5")
+    run_case(cuda_device, [10, 5, 20, 5, 60], [10, 5, 20, 5, 60], [32] * 5, 8, F16, softmax=True,
+             scale=1 / np.sqrt(32), what="graph lengths d=32")
+    run_case(cuda_device, [33, 99, 64], [33, 99, 64], [64] * 3, 16, F32, what="script shapes fp32")
+    run_case(cuda_device, [33, 99, 64], [33, 99, 64], [64] * 3, 16, F16, softmax=True, what="script shapes fp16 fused")
+
+
+@pytest.mark.parametrize("dtype", [F16, BF16])
+@pytest.mark.parametrize("K", [1, 2, 3, 5, 8, 15, 16, 17, 31, 32, 33, 61, 64])
+def test_exhaustive_small_extents(cuda_device, dtype, K):
+    # every (M, N) in [1, 40]^2 as one packed batch: ragged tile edges, every alignment class
+    g = np.arange(1, 41)
+    M, N = [a.ravel() for a in np.meshgrid(g, g, indexing="ij")]
+    run_case(cuda_device, M, N, np.full(M.size, K), 2, dtype, seed=K, what=f"grid K={K}")
+
+
+@pytest.mark.parametrize("K", [32, 64])
+def test_exhaustive_small_fused_softmax(cuda_device, K):
+    g = np.arange(1, 41)
+    M, N = [a.ravel() for a in np.meshgrid(g, g, indexing="ij")]
+    for env in (None, {"BLK_DISABLE_SMALL": "1"}):
+        p = run_case(cuda_device, M, N, np.full(M.size, K), 2, F16, softmax=True, scale=0.3, seed=K, env=env,
+                     what=f"fused grid K={K} env={env}")
+        assert (p.summary["small_items"] > 0) == (env is None)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("dtype", [F16, BF16, F32])
+def test_transposes(cuda_device, dtype, ta, tb):
+    rs = np.random.RandomState(7)
+    M = rs.randint(1, 200, 24); N = rs.randint(1, 300, 24); K = rs.randint(1, 150, 24)
+    M[:4] = [8, 16, 64, 128]; N[:4] = [8, 24, 128, 256]; K[:4] = [8, 32, 64, 128]   # fully aligned ones too
+    run_case(cuda_device, M, N, K, 3, dtype, ta, tb, seed=11, what=f"transposes {ta},{tb}")
+
+
+@pytest.mark.parametrize("dtype", [F16, BF16])
+def test_fp32_output_and_scale(cuda_device, dtype):
+    rs = np.random.RandomState(9)
+    M = rs.randint(1, 257, 40); N = rs.randint(1, 257, 40); K = rs.choice([16, 32, 48, 64, 96, 128], 40)
+    run_case(cuda_device, M, N, K, 1, dtype, out_dtype=F32, scale=0.125, dist="uniform", what="fp32 out")
+
+
+@pytest.mark.parametrize("dtype", [F16, BF16, F32])
+def test_fused_softmax_long_rows(cuda_device, dtype):
+    # N > 128 takes the two-sweep path of the tile kernel; K uniform and ragged
+    M = [1, 130, 64, 300, 65, 7]; N = [129, 130, 1000, 257, 2049, 512]; K = [64, 64, 64, 40, 33, 128]
+    run_case(cuda_device, M, N, K, 2, dtype, softmax=True, scale=0.125, what="two-sweep softmax")
+    # large logits: the running max must do its job
+    run_case(cuda_device, M, N, K, 2, dtype, softmax=True, scale=4.0, seed=3, what="two-sweep softmax, hot")
+
+
+def test_degenerate_segments(cuda_device):
+    # empty segments, n = 1 graphs, K = 0 (a product over nothing is zero; its softmax is uniform)
+    M = [0, 1, 5, 0, 1, 3]; N = [4, 1, 0, 0, 7, 3]; K = [8, 64, 8, 0, 1, 0]
+    for sm in (False, True):
+        run_case(cuda_device, M, N, K, 3, F16, softmax=sm, what=f"degenerate softmax={sm}")
+        run_case(cuda_device, M, N, K, 3, F32, softmax=sm, what=f"degenerate fp32 softmax={sm}")
+    p = GemmPlan([], [], [], 4, F16, device=cuda_device)
+    out = p.run(torch.empty((4, 0), dtype=F16, device=cuda_device), torch.empty((4, 0), dtype=F16, device=cuda_device))
+    assert out.shape == (4, 0)
+
+
+def test_offsets_with_gaps_and_odd_strides(cuda_device):
+    M = np.array([5, 16, 33]); N = np.array([7, 16, 20]); K = np.array([9, 32, 64])
+    a1 = np.array([3, 60, 700, 3000]); a2 = np.array([0, 100, 800, 2500]); ao = np.array([1, 50, 400, 1201])
+    for dtype in (F16, F32):
+        run_case(cuda_device, M, N, K, 3, dtype, accum=(a1, a2, ao), what="gapped offsets")
+        run_case(cuda_device, M, N, K, 3, dtype, softmax=True, accum=(a1, a2, ao), what="gapped offsets fused")
+    # packed, but odd strip lengths: head 1 starts on an odd element
+    run_case(cuda_device, [3, 5], [5, 3], [7, 9], 5, BF16, what="odd strips")
+
+
+@pytest.mark.parametrize("name,segments", [("molecular", 512), ("general_gemm", 192), ("long_tail", 20)])
+def test_workload_shapes_reduced(cuda_device, name, segments):
+    w = workload(name, seed=1, segments=segments)
+    run_case(cuda_device, w.M, w.N, w.K, w.H, w.dtype, softmax=w.softmax, scale=w.scale, out_dtype=w.out_dtype,
+             dist=w.dist, std=w.std, what=name)
+
+
+def test_molecular_full_size_against_oracle(cuda_device):
+    # the headline configuration at its full size: the oracle still finishes in seconds
+    w = workload("molecular")
+    run_case(cuda_device, w.M, w.N, w.K, w.H, w.dtype, softmax=True, scale=w.scale, what="molecular full")
+
+
+def test_full_forward_reduced_p_then_pv(cuda_device):
+    # P = softmax(Q K^T / sqrt(d)) fused, then O = P @ V through the same GEMM with transpose2
+    rs = np.random.RandomState(5)
+    n = np.concatenate([rs.randint(64, 513, 6), np.ones(3, np.int64)])
+    H, d = 4, 128
+    dl = np.full_like(n, d)
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn((H, int(n.sum()) * d), generator=g).to(BF16) for _ in range(3))
+    Pref, Oref = O.block_attention(q, k, v, n, d, 1 / np.sqrt(d), p_dtype=BF16)
+    dev = cuda_device
+    P = blockAttnScores(q.to(dev), k.to(dev), n, n, dl, scale=1 / np.sqrt(d))
+    assert_probs_close(P, Pref, "P")
+    out = blockGEMM(P, v.to(dev), None, None, None, n, dl, n, False, True)
+    assert out.shape == (H, int(n.sum()) * d)
+    assert_scores_close(out, Oref, "O = P V")
+    # unfused chain gives the same probabilities within tolerance (scores rounded to bf16 in between)
+    S = blockGEMM(q.to(dev), k.to(dev), None, None, None, n, n, dl, out_dtype=F32, scale=1 / np.sqrt(d))
+    P2 = blockSoftmax(S, n, n)
+    assert_probs_close(P2, Pref, "unfused chain")
+
+
+def test_long_tail_full_size_properties(cuda_device):
+    # full size: rows sum to one, values in [0,1], sampled segments against the oracle
+    w = workload("long_tail")
+    dev = cuda_device
+    q, k = w.make_inputs(dev, seed=0)
+    P = blockAttnScores(q, k, w.M, w.N, w.K, scale=w.scale)
+    torch.cuda.synchronize()
+    assert P.shape == (w.H, w.Dout)
+    ao = O.offsets_from_lists(w.M, w.N, w.K)[2]
+    a1 = O.offsets_from_lists(w.M, w.N, w.K)[0]
+    worst = 0.0
+    for s in range(w.S):
+        blk = P[:, ao[s]:ao[s + 1]].reshape(w.H, w.M[s], w.N[s]).float()
+        worst = max(worst, float((blk.sum(-1) - 1).abs().max()))
+    assert worst < 2e-2, worst          # bf16 rounding of up to 2048 terms
+    assert float(P.float().min()) >= 0 and float(P.float().max()) <= 1.0
+    order = np.argsort(w.M)
+    for s in [order[0], order[len(order) // 2], order[-1]]:
+        n = int(w.M[s])
+        qs = q[:, a1[s]:a1[s + 1]].cpu(); ks = k[:, a1[s]:a1[s + 1]].cpu()
+        ref = O.block_scores(qs, ks, [n], [n], [64], scale=w.scale)
+        assert_probs_close(P[:, ao[s]:ao[s + 1]], ref, f"segment {s} (n={n})")
+
+
+def test_python_surface_matches_upstream_contract(cuda_device):
+    dev = cuda_device
+    M = torch.tensor([33, 99, 64], device=dev); K = torch.tensor([64, 64, 64], device=dev)
+    A, B = packed_inputs(M.cpu(), M.cpu(), K.cpu(), 6, F16, 1)
+    ref = O.block_gemm(A, B, M.cpu(), M.cpu(), K.cpu())
+    res = blockGEMM(A.to(dev), B.to(dev), None, None, None, M, M, K)
+    assert res.dtype == F16 and res.shape == (6, int((M * M).sum()))       # dtype = input dtype, 2-D (H, Dout)
+    assert_scores_close(res, ref)
+    # offsets only: lists are derived (upstream csrc/sparseBlockedAttention.cpp:30-40)
+    a1, a2, ao = (torch.from_numpy(a).to(dev) for a in O.offsets_from_lists(M.cpu(), M.cpu(), K.cpu()))
+    res2 = blockGEMM(A.to(dev), B.to(dev), a1, a2, ao)
+    assert torch.equal(res, res2)
+    # any leading shape flattens to H
+    res3 = blockGEMM(A.to(dev).reshape(2, 3, -1), B.to(dev).reshape(2, 3, -1), None, None, None, M, M, K)
+    assert torch.equal(res, res3)
+    # chained softmax, upstream test/pytest.py:36-38
+    sm = blockSoftmax(res, M, M)
+    assert_probs_close(sm, O.block_softmax(res.cpu(), M.cpu(), M.cpu()))
+    # error behaviour: RuntimeError like TORCH_CHECK
+    with pytest.raises(RuntimeError):
+        blockGEMM(A, B.to(dev), None, None, None, M, M, K)                 # CPU tensor
+    with pytest.raises(RuntimeError):
+        blockGEMM(A.to(dev).t(), B.to(dev), None, None, None, M, M, K)     # not contiguous
+    with pytest.raises(RuntimeError):
+        blockGEMM(A.to(dev), B.to(dev))                                    # neither lists nor offsets
+    with pytest.raises(RuntimeError):
+        blockGEMM(A.to(dev)[:, :-1].contiguous(), B.to(dev), None, None, None, M, M, K)
+
+
+def test_unaligned_pointer_is_handled(cuda_device):
+    dev = cuda_device
+    M = [5, 9]; N = [6, 4]; K = [8, 8]
+    A, B = packed_inputs(M, N, K, 1, F16, 2)
+    big = torch.zeros(A.numel() + 1, dtype=F16, device=dev)
+    big[1:] = A.to(dev).reshape(-1)
+    Au = big[1:].reshape(1, -1)            # data pointer off by two bytes
+    assert Au.data_ptr() % 16 != 0
+    plan = GemmPlan(M, N, K, 1, F16, device=dev)
+    out = plan.run(Au, B.to(dev))
+    assert_scores_close(out, O.block_gemm(A, B, M, N, K))
+    # the raw ABI refuses it rather than faulting
+    import ctypes as C
+    rc = L.lib.blk_gemm_run(plan._h, C.c_void_p(Au.data_ptr()), C.c_void_p(B.to(dev).data_ptr()),
+                            C.c_void_p(out.data_ptr()), C.c_float(1.0), None)
+    assert rc == L.BLK_ERR_UNALIGNED

@@ -1,0 +1,188 @@
+"""CPU: the C ABI loads and exports what include/blkattn.h declares; host-side
+index helpers are bit-exact with the oracle; scheduler and partitioners behave."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import O, ROOT
+from blockedattention_b200 import _lib as L
+from blockedattention_b200 import partition as P
+from blockedattention_b200.plan import GemmPlan, SoftmaxPlan
+from blockedattention_b200.synth import WORKLOADS, workload
+
+
+def declared_symbols():
+    src = open(os.path.join(ROOT, "include", "blkattn.h")).read()
+    return sorted(set(re.findall(r"BLK_API\s+[\w\s\*]+?\b(blk_\w+)\s*\(", src)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = declared_symbols()
+    assert len(names) >= 18
+    lib = C.CDLL(L.LIB_PATH)
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/blkattn.h but not exported"
+    assert set(names) == set(L.SIGNATURES), "ctypes table and header disagree"
+    assert b"sm_100a" in L.lib.blk_version()
+
+
+def _offsets(M, N, K):
+    M = np.ascontiguousarray(M, np.int64); N = np.ascontiguousarray(N, np.int64); K = np.ascontiguousarray(K, np.int64)
+    S = len(M)
+    a1 = np.empty(S + 1, np.int64); a2 = np.empty_like(a1); ao = np.empty_like(a1)
+    L.check(L.lib.blk_offsets_from_lists(L.i64(M), L.i64(N), L.i64(K), S, L.i64(a1), L.i64(a2), L.i64(ao)))
+    return a1, a2, ao
+
+
+@pytest.mark.parametrize("name", WORKLOADS)
+def test_offsets_bit_exact_on_every_workload(name):
+    w = workload(name)
+    a1, a2, ao = _offsets(w.M, w.N, w.K)
+    o1, o2, oo = O.offsets_from_lists(w.M, w.N, w.K)
+    assert np.array_equal(a1, o1) and np.array_equal(a2, o2) and np.array_equal(ao, oo)
+    # and the inverse recovers the lists exactly
+    S = w.S
+    M = np.empty(S, np.int64); N = np.empty(S, np.int64); K = np.empty(S, np.int64)
+    L.check(L.lib.blk_lists_from_offsets(L.i64(a1), L.i64(a2), L.i64(ao), S, L.i64(M), L.i64(N), L.i64(K)))
+    assert np.array_equal(M, w.M) and np.array_equal(N, w.N) and np.array_equal(K, w.K)
+
+
+def test_offsets_empty_and_overflow():
+    a1, a2, ao = _offsets([], [], [])
+    assert a1.tolist() == [0] and a2.tolist() == [0] and ao.tolist() == [0]
+    a1, a2, ao = _offsets([0, 3, 0], [4, 0, 0], [5, 6, 7])
+    assert a1.tolist() == [0, 0, 18, 18] and a2.tolist() == [0, 20, 20, 20] and ao.tolist() == [0, 0, 0, 0]
+    with pytest.raises(L.BlkError) as e:
+        _offsets([2 ** 40], [2 ** 40], [2 ** 40])
+    assert e.value.code == L.BLK_ERR_INVALID
+    with pytest.raises(L.BlkError):
+        _offsets([-1], [1], [1])
+
+
+def test_lists_from_offsets_agrees_with_upstream_formula_where_that_is_consistent():
+    rs = np.random.RandomState(1)
+    M = rs.randint(1, 3000, 500); N = rs.randint(1, 3000, 500); K = rs.randint(1, 300, 500)
+    a1, a2, ao = O.offsets_from_lists(M, N, K)
+    Mo = np.empty(500, np.int64); No = np.empty_like(Mo); Ko = np.empty_like(Mo)
+    L.check(L.lib.blk_lists_from_offsets(L.i64(a1), L.i64(a2), L.i64(ao), 500, L.i64(Mo), L.i64(No), L.i64(Ko)))
+    assert np.array_equal(Mo, M) and np.array_equal(No, N) and np.array_equal(Ko, K)
+    Mf, Nf, Kf = O.lists_from_offsets_float32(a1, a2, ao)
+    ok = (Mf * Kf == a1[1:] - a1[:-1]) & (Nf * Kf == a2[1:] - a2[:-1]) & (Mf * Nf == ao[1:] - ao[:-1])
+    assert ok.sum() > 100
+    assert np.array_equal(Mo[ok], Mf[ok]) and np.array_equal(No[ok], Nf[ok]) and np.array_equal(Ko[ok], Kf[ok])
+    bad = np.array([0, 6], np.int64), np.array([0, 6], np.int64), np.array([0, 5], np.int64)
+    with pytest.raises(L.BlkError):
+        L.check(L.lib.blk_lists_from_offsets(L.i64(bad[0]), L.i64(bad[1]), L.i64(bad[2]), 1, L.i64(Mo), L.i64(No), L.i64(Ko)))
+
+
+def test_softmax_offsets():
+    rows = np.array([127, 127, 127, 0, 3], np.int64); cols = np.array([2047, 2047, 2047, 9, 1], np.int64)
+    acc = np.empty(6, np.int64)
+    L.check(L.lib.blk_softmax_offsets(L.i64(rows), L.i64(cols), 5, L.i64(acc)))
+    assert np.array_equal(acc, O.softmax_offsets(rows, cols))
+
+
+# ---- scheduler ---------------------------------------------------------------
+def test_schedule_bins_and_work():
+    w = workload("molecular")
+    p = GemmPlan(w.M, w.N, w.K, w.H, w.dtype, softmax=True)
+    s = p.summary
+    assert s["segments"] == 4096 and s["small_items"] + s["tile_items"] > 0
+    assert s["small_items"] == int((w.N <= 64).sum())
+    fl, by = p.work
+    assert fl == pytest.approx(w.flops()) and by == pytest.approx(w.bytes())
+    assert p.extents == (w.Dm1, w.Dm2, w.Dout)
+
+    w = workload("long_tail")
+    p = GemmPlan(w.M, w.N, w.K, w.H, w.dtype, softmax=True)
+    s = p.summary
+    big = w.N > 64
+    assert s["tile_items"] + s["umma_items"] >= int(np.ceil(w.M[big] / 128).sum())
+
+    w = workload("general_gemm")
+    p = GemmPlan(w.M, w.N, w.K, w.H, w.dtype, torch.float32)
+    assert p.summary["launches"] >= 1 and p.work[0] == pytest.approx(w.flops())
+
+    w = workload("cpu_plumbing")
+    p = GemmPlan(w.M, w.N, w.K, w.H, torch.float32, softmax=True)
+    s = p.summary
+    assert s["simt_items"] == w.S and s["softmax_chunks"] >= 1 and s["launches"] == 2
+
+
+def test_schedule_rejects_bad_input():
+    with pytest.raises(L.BlkError) as e:
+        GemmPlan([4], [4], [8], 1, torch.float16, accum=([0, 31], [0, 32], [0, 16]))  # 4*8 = 32 > 31
+    assert e.value.code == L.BLK_ERR_INVALID
+    with pytest.raises(L.BlkError):
+        GemmPlan([4, 4], [4, 4], [8, 8], 1, torch.float16, accum=([0, 32, 30], [0, 32, 64], [0, 16, 32]))
+    with pytest.raises(L.BlkError) as e:
+        GemmPlan([4], [4], [8], 1, torch.float32, torch.float16)
+    assert e.value.code == L.BLK_ERR_UNSUPPORTED
+    with pytest.raises(L.BlkError):
+        GemmPlan([-1], [4], [8], 1, torch.float16)
+    with pytest.raises(RuntimeError):
+        GemmPlan([1, 2], [1], [1], 1, torch.float16)
+    p = GemmPlan([4], [4], [8], 1, torch.float16)      # no device: cannot run
+    with pytest.raises(RuntimeError):
+        p.run(torch.zeros(1, 32, dtype=torch.float16), torch.zeros(1, 32, dtype=torch.float16))
+
+
+def test_softmax_schedule_chunks():
+    p = SoftmaxPlan([127] * 3, [2047] * 3, 7, torch.float16)
+    assert p.summary["softmax_chunks"] == 3 * 32 and p.D == 3 * 127 * 2047
+    p = SoftmaxPlan([3, 0, 2], [20000, 5, 0], 1, torch.float32)   # rows longer than the window: one chunk per row
+    assert p.summary["softmax_chunks"] == 3
+    p = SoftmaxPlan([], [], 4, torch.bfloat16)
+    assert p.summary["softmax_chunks"] == 0 and p.D == 0
+    assert p.work[1] == 0
+
+
+# ---- partitioners --------------------------------------------------------------
+def brute_force_bottleneck(cost, R):
+    import itertools
+    S = len(cost)
+    best = float("inf")
+    for cuts in itertools.combinations_with_replacement(range(S + 1), R - 1):
+        b = (0,) + cuts + (S,)
+        best = min(best, max(sum(cost[b[i]:b[i + 1]]) for i in range(R)))
+    return best
+
+
+def test_partition_contiguous_is_optimal_on_small_cases():
+    rs = np.random.RandomState(0)
+    for trial in range(30):
+        S = rs.randint(1, 10); R = rs.randint(1, 5)
+        cost = rs.rand(S) ** 3
+        b = P.partition_contiguous(cost, R)
+        assert b[0] == 0 and b[-1] == S and (np.diff(b) >= 0).all()
+        got = max(cost[b[i]:b[i + 1]].sum() for i in range(R))
+        assert got <= brute_force_bottleneck(cost.tolist(), R) * (1 + 1e-6)
+
+
+@pytest.mark.parametrize("name", ["molecular", "long_tail", "full_forward"])
+def test_partition_balance_on_workloads(name):
+    w = workload(name)
+    cost = P.segment_cost(w.M, w.N, w.K, w.H)
+    assert (cost > 0).all()
+    for R in (1, 2, 4, 8):
+        b = P.partition_contiguous(cost, R)
+        assert P.imbalance(cost, b) < 1.06
+        owner = P.partition_lpt(cost, R)
+        loads = np.bincount(owner, weights=cost, minlength=R)
+        assert loads.max() / loads.mean() < 1.06
+        lo, hi = P.shard_range(w.M, w.N, w.K, w.H, R - 1, R)
+        assert (lo, hi) == (b[R - 1], b[R])
+
+
+def test_partition_edge_cases():
+    assert P.partition_contiguous([], 4).tolist() == [0, 0, 0, 0, 0]
+    b = P.partition_contiguous([5.0], 3)
+    assert b[0] == 0 and b[-1] == 1
+    with pytest.raises(L.BlkError):
+        P.partition_contiguous([1.0, -1.0], 2)
+    with pytest.raises(L.BlkError):
+        P.partition_contiguous([1.0], 0)
