@@ -53,7 +53,13 @@ int upload_plan(blk_plan* p) {
     if ((rc = upload(p->segs, &p->d_segs, "upload segments")) != BLK_OK) return rc;
     if ((rc = upload(p->tile_items, &p->d_tile_items, "upload tile items")) != BLK_OK) return rc;
     if ((rc = upload(p->simt_items, &p->d_simt_items, "upload simt items")) != BLK_OK) return rc;
-    if ((rc = upload(p->small_items, &p->d_small_items, "upload small items")) != BLK_OK) return rc;
+    for (int b = 0; b < BLK_SMALL_BUCKETS; ++b)
+        if ((rc = upload(p->small_items[b], &p->d_small_items[b], "upload small items")) != BLK_OK) return rc;
+    {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device) == cudaSuccess && sms > 0)
+            p->num_sms = sms;
+    }
     if ((rc = upload(p->umma_items, &p->d_umma_items, "upload umma items")) != BLK_OK) return rc;
     if ((rc = upload(p->smx_chunks, &p->d_smx_chunks, "upload softmax chunks")) != BLK_OK) return rc;
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&p->d_status), 2 * sizeof(int));
@@ -70,6 +76,12 @@ bool grid_ok(int64_t items, int64_t H, const char* what) {
         return false;
     }
     return true;
+}
+
+size_t small_count(const blk_plan* p) {
+    size_t n = 0;
+    for (const auto& v : p->small_items) n += v.size();
+    return n;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -134,7 +146,7 @@ extern "C" int blk_gemm_plan_create(blk_plan_t** plan, const int64_t* M, const i
     if (rc == BLK_OK && !(grid_ok((int64_t)p->tile_items.size(), H, "gemm plan") &&
                           grid_ok((int64_t)p->simt_items.size(), H, "gemm plan") &&
                           grid_ok((int64_t)p->smx_chunks.size(), H, "gemm plan") &&
-                          grid_ok((int64_t)p->small_items.size(), H, "gemm plan")))
+                          grid_ok((int64_t)small_count(p), H, "gemm plan")))
         rc = BLK_ERR_UNSUPPORTED;
     if (rc == BLK_OK) rc = upload_plan(p);
     if (rc != BLK_OK) {
@@ -196,7 +208,7 @@ extern "C" void blk_plan_destroy(blk_plan_t* p) {
         cudaFree(p->d_segs);
         cudaFree(p->d_tile_items);
         cudaFree(p->d_simt_items);
-        cudaFree(p->d_small_items);
+        for (int b = 0; b < BLK_SMALL_BUCKETS; ++b) cudaFree(p->d_small_items[b]);
         cudaFree(p->d_umma_items);
         cudaFree(p->d_smx_chunks);
         cudaFree(p->d_status);
@@ -228,8 +240,9 @@ extern "C" int blk_plan_offsets(const blk_plan_t* p, int64_t* a1, int64_t* a2, i
 }
 
 static int launches_per_run(const blk_plan* p) {
-    return (!p->tile_items.empty()) + (!p->simt_items.empty()) + (!p->small_items.empty()) +
-           (!p->umma_items.empty()) + (!p->smx_chunks.empty());
+    int n = (!p->tile_items.empty()) + (!p->simt_items.empty()) + (!p->umma_items.empty()) + (!p->smx_chunks.empty());
+    for (const auto& v : p->small_items) n += !v.empty();
+    return n;
 }
 
 extern "C" int blk_plan_summary(const blk_plan_t* p, int64_t counts[8]) {
@@ -238,7 +251,7 @@ extern "C" int blk_plan_summary(const blk_plan_t* p, int64_t counts[8]) {
         return BLK_ERR_INVALID;
     }
     counts[0] = p->S;
-    counts[1] = (int64_t)p->small_items.size();
+    counts[1] = (int64_t)small_count(p);
     counts[2] = (int64_t)p->tile_items.size();
     counts[3] = (int64_t)p->umma_items.size();
     counts[4] = (int64_t)p->smx_chunks.size();
@@ -322,19 +335,20 @@ extern "C" int blk_gemm_run(const blk_plan_t* p, const void* mat1, const void* m
             if ((e = blk_launch_softmax(xp, BLK_F32, st)) != cudaSuccess) return cuda_fail("softmax launch", e);
         }
     }
-    if (!p->small_items.empty()) {
+    for (int b = 0; b < BLK_SMALL_BUCKETS; ++b) {
+        if (p->small_items[b].empty()) continue;
         BlkSmallParams mp{};
         mp.A = reinterpret_cast<const uint16_t*>(mat1);
         mp.B = reinterpret_cast<const uint16_t*>(mat2);
         mp.C = out;
-        mp.items = p->d_small_items;
+        mp.items = p->d_small_items[b];
         mp.Dm1 = p->Dm1; mp.Dm2 = p->Dm2; mp.Dout = p->Dout;
-        mp.num_items = (int)p->small_items.size();
+        mp.num_items = (int)p->small_items[b].size();
         mp.H = (int)p->H;
         mp.out_f32 = p->dtype_out == BLK_F32;
         mp.epi = p->epi;
         mp.scale = scale;
-        if ((e = blk_launch_scores_small(mp, p->dtype_in, p->small_K, st)) != cudaSuccess)
+        if ((e = blk_launch_scores_small(mp, p->dtype_in, p->small_K, b, p->num_sms, st)) != cudaSuccess)
             return cuda_fail("small-segment launch", e);
     }
     if (!p->tile_items.empty()) {

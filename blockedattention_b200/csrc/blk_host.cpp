@@ -297,7 +297,8 @@ int blk_build_gemm_schedule(blk_plan* p) {
                               (p->small_K == 0 || p->small_K == (int)k);
         if (small_ok) {
             p->small_K = (int)k;
-            p->small_items.push_back(BlkSmallItem{sd.offA, sd.offB, sd.offC, (int32_t)m, (int32_t)n});
+            p->small_items[n <= 16 ? 0 : (n <= 32 ? 1 : 2)].push_back(
+                BlkSmallItem{sd.offA, sd.offB, sd.offC, (int32_t)m, (int32_t)n});
             continue;
         }
         const int32_t tms = (int32_t)((m + BLK_TILE_BM - 1) / BLK_TILE_BM);
@@ -310,6 +311,11 @@ int blk_build_gemm_schedule(blk_plan* p) {
             }
         }
     }
+    // Persistent warps take small items in list order with a fixed stride: heaviest first evens the tails.
+    for (auto& v : p->small_items)
+        std::stable_sort(v.begin(), v.end(), [](const BlkSmallItem& a, const BlkSmallItem& b) {
+            return (int64_t)a.M * a.N + (int64_t)(a.M + a.N) * 64 > (int64_t)b.M * b.N + (int64_t)(b.M + b.N) * 64;
+        });
     // fp32 inputs with the softmax epilogue: SIMT GEMM, then the softmax kernel in place.
     if (p->dtype_in == BLK_F32 && p->epi == BLK_EPI_SOFTMAX) {
         blk_plan tmp;

@@ -66,6 +66,7 @@ constexpr int BLK_SIMT_BM = 64;
 constexpr int BLK_SIMT_BN = 64;
 constexpr int BLK_SMALL_MAXN = 64;
 constexpr int BLK_SMALL_WARPS = 4;
+constexpr int BLK_SMALL_BUCKETS = 3;  // N <= 16, N <= 32, N <= 64
 constexpr int BLK_SMX_WINDOW_BYTES = 16384;
 constexpr int BLK_UMMA_BM = 128;
 
@@ -81,7 +82,7 @@ struct blk_plan {
     std::vector<BlkSeg> segs;
     std::vector<BlkTileItem> tile_items;    // staged mma.sync kernel (16-bit inputs)
     std::vector<BlkTileItem> simt_items;    // fp32 SIMT kernel
-    std::vector<BlkSmallItem> small_items;  // packed small-segment kernel
+    std::vector<BlkSmallItem> small_items[BLK_SMALL_BUCKETS];  // packed small-segment kernel, by column count
     std::vector<BlkUmmaItem> umma_items;    // tcgen05 kernel
     std::vector<BlkSmxChunk> smx_chunks;    // softmax kernel (also second pass of fp32 scores)
     int umma_K = 0;                         // uniform K of the tcgen05 bin
@@ -91,7 +92,8 @@ struct blk_plan {
     BlkSeg* d_segs = nullptr;
     BlkTileItem* d_tile_items = nullptr;
     BlkTileItem* d_simt_items = nullptr;
-    BlkSmallItem* d_small_items = nullptr;
+    BlkSmallItem* d_small_items[BLK_SMALL_BUCKETS] = {nullptr, nullptr, nullptr};
+    int num_sms = 148;
     BlkUmmaItem* d_umma_items = nullptr;
     BlkSmxChunk* d_smx_chunks = nullptr;
     int* d_status = nullptr;

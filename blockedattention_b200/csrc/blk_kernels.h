@@ -57,5 +57,6 @@ struct BlkSmxParams {
 
 cudaError_t blk_launch_gemm_tile(const BlkGemmParams& p, int dtype_in, int ta, int tb, cudaStream_t st);
 cudaError_t blk_launch_gemm_simt(const BlkSimtParams& p, cudaStream_t st);
-cudaError_t blk_launch_scores_small(const BlkSmallParams& p, int dtype_in, int K, cudaStream_t st);
+cudaError_t blk_launch_scores_small(const BlkSmallParams& p, int dtype_in, int K, int bucket, int sms,
+                                    cudaStream_t st);
 cudaError_t blk_launch_softmax(const BlkSmxParams& p, int dtype, cudaStream_t st);

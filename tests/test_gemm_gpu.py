@@ -154,7 +154,10 @@ def test_full_forward_reduced_p_then_pv(cuda_device):
     assert_probs_close(P, Pref, "P")
     out = blockGEMM(P, v.to(dev), None, None, None, n, dl, n, False, True)
     assert out.shape == (H, int(n.sum()) * d)
-    assert_scores_close(out, Oref, "O = P V")
+    # the second product is checked on the P it was given (a one-ulp difference in a bf16 probability
+    # is within the contract but moves O), then loosely against the all-oracle O
+    assert_scores_close(out, O.block_gemm(P.cpu(), v, n, dl, n, transpose2=True), "O = P V")
+    assert float((out.float().cpu() - Oref).abs().max()) < 1e-2 * float(Oref.abs().max())
     # unfused chain gives the same probabilities within tolerance (scores rounded to bf16 in between)
     S = blockGEMM(q.to(dev), k.to(dev), None, None, None, n, n, dl, out_dtype=F32, scale=1 / np.sqrt(d))
     P2 = blockSoftmax(S, n, n)
