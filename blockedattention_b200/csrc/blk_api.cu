@@ -311,6 +311,9 @@ extern "C" int blk_gemm_run(const blk_plan_t* p, const void* mat1, const void* m
     }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
     cudaError_t e;
+    // softmax(0 * S) is the uniform distribution; a denormal-free tiny scale gives exactly that and keeps
+    // the kernels' "-inf times scale" column masks well defined
+    if (p->epi == BLK_EPI_SOFTMAX && scale == 0.f) scale = 1.17549435e-38f;
     if (!p->simt_items.empty()) {
         BlkSimtParams sp{};
         sp.A = reinterpret_cast<const float*>(mat1);

@@ -93,6 +93,20 @@ __device__ __forceinline__ uint4 blk_ldg_stream16(const void* p) {
                  : "l"(p));
     return v;
 }
+// Shared-memory stores through 32-bit shared-window addresses.
+__device__ __forceinline__ void blk_sts_b32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(addr), "r"(v));
+}
+__device__ __forceinline__ void blk_sts_b16(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.b16 [%0], %1;\n" ::"r"(addr), "h"((uint16_t)v));
+}
+__device__ __forceinline__ void blk_sts_f32(uint32_t addr, float v) {
+    asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(addr), "f"(v));
+}
+__device__ __forceinline__ void blk_sts_f32x2(uint32_t addr, float x, float y) {
+    asm volatile("st.shared.v2.f32 [%0], {%1, %2};\n" ::"r"(addr), "f"(x), "f"(y));
+}
+
 __device__ __forceinline__ uint4 blk_ldg16(const void* p) {
     return __ldg(reinterpret_cast<const uint4*>(p));
 }

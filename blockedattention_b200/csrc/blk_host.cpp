@@ -292,12 +292,12 @@ int blk_build_gemm_schedule(blk_plan* p) {
             continue;
         }
         // Packed small-segment kernel: one warp per (segment, head).
-        const bool small_ok = allow_small && !p->ta && !p->tb && n <= BLK_SMALL_MAXN && m <= 4 * BLK_SMALL_MAXN &&
+        const bool small_ok = allow_small && !p->ta && !p->tb && n <= BLK_SMALL_MAXN && m <= BLK_SMALL_MAXM &&
                               (k == 32 || k == 64) && sd.clsIn == 2 &&
                               (p->small_K == 0 || p->small_K == (int)k);
         if (small_ok) {
             p->small_K = (int)k;
-            p->small_items[n <= 16 ? 0 : (n <= 32 ? 1 : 2)].push_back(
+            p->small_items[n <= 32 ? 0 : 1].push_back(
                 BlkSmallItem{sd.offA, sd.offB, sd.offC, (int32_t)m, (int32_t)n});
             continue;
         }

@@ -66,7 +66,8 @@ constexpr int BLK_SIMT_BM = 64;
 constexpr int BLK_SIMT_BN = 64;
 constexpr int BLK_SMALL_MAXN = 64;
 constexpr int BLK_SMALL_WARPS = 4;
-constexpr int BLK_SMALL_BUCKETS = 3;  // N <= 16, N <= 32, N <= 64
+constexpr int BLK_SMALL_MAXM = 64;
+constexpr int BLK_SMALL_BUCKETS = 2;  // N <= 32, N <= 64
 constexpr int BLK_SMX_WINDOW_BYTES = 16384;
 constexpr int BLK_UMMA_BM = 128;
 
@@ -92,7 +93,7 @@ struct blk_plan {
     BlkSeg* d_segs = nullptr;
     BlkTileItem* d_tile_items = nullptr;
     BlkTileItem* d_simt_items = nullptr;
-    BlkSmallItem* d_small_items[BLK_SMALL_BUCKETS] = {nullptr, nullptr, nullptr};
+    BlkSmallItem* d_small_items[BLK_SMALL_BUCKETS] = {nullptr, nullptr};
     int num_sms = 148;
     BlkUmmaItem* d_umma_items = nullptr;
     BlkSmxChunk* d_smx_chunks = nullptr;
