@@ -283,10 +283,19 @@ def main():
     kernel = max((("blk_scores_small_kernel", s["small_items"]), ("blk_gemm_tile_kernel", s["tile_items"]),
                   ("blk_gemm_umma_kernel", s["umma_items"]), ("blk_gemm_simt_kernel", s["simt_items"])),
                  key=lambda kv: kv[1])[0]
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                "kernel": kernel, "launches_per_step": launches_per_step,
-                "algorithmic_bytes_per_step": w.bytes()}
+    t_hbm = w.bytes() / (peaks["hbm_gbs"] * 1e9)
+    t_tc = w.flops() / (peaks["bf16_tflops"] * 1e12)
+    if t_tc > t_hbm:
+        ach_tf = w.flops() / (my_ms_per_step * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "achieved": ach_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": ach_tf / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"],
+                    "kernel": kernel, "launches_per_step": launches_per_step,
+                    "algorithmic_flops_per_step": w.flops()}
+    else:
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                    "kernel": kernel, "launches_per_step": launches_per_step,
+                    "algorithmic_bytes_per_step": w.bytes()}
 
     # ---- end to end through the public operator with host buffers ----------
     e2e = None

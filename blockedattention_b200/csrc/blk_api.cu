@@ -146,7 +146,8 @@ extern "C" int blk_gemm_plan_create(blk_plan_t** plan, const int64_t* M, const i
     if (rc == BLK_OK && !(grid_ok((int64_t)p->tile_items.size(), H, "gemm plan") &&
                           grid_ok((int64_t)p->simt_items.size(), H, "gemm plan") &&
                           grid_ok((int64_t)p->smx_chunks.size(), H, "gemm plan") &&
-                          grid_ok((int64_t)small_count(p), H, "gemm plan")))
+                          grid_ok((int64_t)small_count(p), H, "gemm plan") &&
+                          grid_ok((int64_t)p->umma_items.size(), H, "gemm plan")))
         rc = BLK_ERR_UNSUPPORTED;
     if (rc == BLK_OK) rc = upload_plan(p);
     if (rc != BLK_OK) {
@@ -353,6 +354,22 @@ extern "C" int blk_gemm_run(const blk_plan_t* p, const void* mat1, const void* m
         mp.scale = scale;
         if ((e = blk_launch_scores_small(mp, p->dtype_in, p->small_K, b, p->num_sms, st)) != cudaSuccess)
             return cuda_fail("small-segment launch", e);
+    }
+    if (!p->umma_items.empty()) {
+        BlkUmmaParams up{};
+        up.C = out;
+        up.items = p->d_umma_items;
+        up.Dout = p->Dout;
+        up.num_items = (int)p->umma_items.size();
+        up.H = (int)p->H;
+        up.K = p->umma_K;
+        up.bf16 = p->dtype_in == BLK_BF16;
+        up.out_f32 = p->dtype_out == BLK_F32;
+        up.epi = p->epi;
+        up.scale = scale;
+        up.status = p->d_status;
+        if ((e = blk_launch_gemm_umma(up, mat1, mat2, p->Dm1, p->Dm2, p->num_sms, st)) != cudaSuccess)
+            return cuda_fail("tcgen05 GEMM launch", e);
     }
     if (!p->tile_items.empty()) {
         BlkGemmParams gp{};

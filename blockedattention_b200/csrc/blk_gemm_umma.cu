@@ -1,0 +1,513 @@
+// Large-segment kernel of the varlen blocked GEMM on the 5th-generation tensor
+// cores: TMA-fed tcgen05.mma with the accumulator in tensor memory.
+//
+// A persistent CTA (one per SM, 6 warps) walks a static list of work items, an
+// item being a 128-row block of one segment of one head.  Roles:
+//   warp 0   producer: one lane issues 3-D tiled TMA loads (k, row, head) of a
+//            128 x 64 tile of the first operand and a 256 x 64 tile of the
+//            second into a 4-stage ring of 128-byte-swizzled shared memory;
+//   warp 1   MMA: allocates the 512 tensor-memory columns, and one lane issues
+//            tcgen05.mma (M = 128, N up to 256, K = 16 per instruction) into
+//            one of two 256-column accumulators; tcgen05.commit hands shared
+//            memory stages back to the producer and accumulators to the epilogue;
+//   warps 2-5 epilogue: each owns 32 accumulator lanes (= rows).  A thread
+//            reads its row 32 columns at a time (tcgen05.ld), applies the
+//            epilogue and the warp writes the piece out through a padded
+//            shared-memory strip so that lanes store consecutive addresses.
+//
+// Epilogues.  Scores: scale and round.  Softmax with N <= 512: both
+// accumulators hold the whole row; pass 1 takes the row maximum, pass 2 writes
+// exp2 back into tensor memory while summing, pass 3 normalises and stores, so
+// the exponential is evaluated once per element and the scores never leave the
+// SM.  Softmax with N > 512: the products are computed twice -- a first sweep
+// over the 256-column chunks keeps only a running (max, sum) per row, a second
+// sweep recomputes each chunk and stores normalised probabilities.
+//
+// Rows of the operand views past the end of a segment belong to its neighbour
+// (or are zero-filled past the end of the buffer); they only reach accumulator
+// rows/columns the epilogue never stores, and columns >= N are masked before
+// any row reduction.
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the kernel
+// records a status code, all roles leave their loops, tensor memory is
+// released and the kernel returns.
+//
+// Replaces upstream sparseBlockedHGEMM_half / _bf16 with the 128 x 128 x 16
+// WMMA tile (csrc/cuda/spBlkGEMM.cu:424-817, :866-868) and, fused, the softmax
+// kernels (csrc/cuda/spBlkSoftmax.cu:88-269).
+#include <cuda.h>
+
+#include "blk_device.cuh"
+#include "blk_kernels.h"
+
+namespace {
+
+constexpr int UM_BM = BLK_UMMA_BM;      // 128 rows per work item
+constexpr int UM_BN = 256;              // columns per accumulator
+constexpr int UM_BK = 64;               // k elements per shared-memory stage (one 128-byte swizzle row)
+constexpr int UM_STAGES = 4;
+constexpr int UM_A_BYTES = UM_BM * UM_BK * 2;  // 16 KB
+constexpr int UM_B_BYTES = UM_BN * UM_BK * 2;  // 32 KB
+constexpr int UM_STAGE_BYTES = UM_A_BYTES + UM_B_BYTES;
+constexpr int UM_THREADS = 192;
+constexpr int UM_EPI_WARPS = 4;
+constexpr int UM_PIECE = 32;                          // columns per tcgen05.ld
+constexpr int UM_STRIP_PITCH = UM_PIECE * 4 + 16;     // bytes per strip row (fp32 piece + pad)
+constexpr int UM_STRIP_BYTES = 32 * UM_STRIP_PITCH;   // per epilogue warp
+constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + UM_EPI_WARPS * UM_STRIP_BYTES + 256 + 1024;
+constexpr uint32_t UM_SPIN_LIMIT = 6u << 20;
+
+// ---- PTX wrappers -------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred q;\n mbarrier.test_wait.parity.shared::cta.b64 q, [%1], %2;\n selp.u32 %0, 1, 0, q;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when another role has already given up or when the bound is hit
+// (then the status word and the CTA's abort flag are set).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int code) {
+    for (uint32_t i = 0; i < UM_SPIN_LIMIT; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if (i > 128) __nanosleep(64);
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(status, 0, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n .reg .pred q;\n setp.ne.b32 q, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, q;\n}\n"
+        ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,"
+        "%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,"
+        "%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};\n"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+          "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+          "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// K-major operand tile, rows of 128 bytes, 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16, fp32 accumulate, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t instr_desc(int bf16, int n) {
+    return (1u << 4) | ((uint32_t)bf16 << 7) | ((uint32_t)bf16 << 10) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(UM_BM >> 4) << 24);
+}
+
+struct Work {
+    BlkUmmaItem it;
+    int head;
+    int nchunks;
+    int sweeps;
+};
+
+__device__ __forceinline__ bool next_work(const BlkUmmaParams& p, uint32_t w, Work& wk) {
+    const uint32_t total = (uint32_t)p.num_items * (uint32_t)p.H;
+    if (w >= total) return false;
+    const uint32_t item = w / (uint32_t)p.H;
+    wk.head = (int)(w - item * (uint32_t)p.H);
+    wk.it = p.items[item];
+    wk.nchunks = (wk.it.N + UM_BN - 1) / UM_BN;
+    wk.sweeps = (p.epi == BLK_EPI_SOFTMAX && wk.nchunks > 2) ? 2 : 1;
+    return true;
+}
+
+// Writes one 32-row x 32-column piece (this warp's rows) from the strip to global memory with lanes on
+// consecutive addresses.  vals are already scaled; row = this thread's row inside the item.
+template <typename Tag, bool OUT32>
+__device__ __forceinline__ void store_piece(const BlkUmmaParams& p, const float (&v)[32], unsigned char* strip,
+                                            int64_t cbase, int row0, int M, int N, int col0, int lane) {
+    constexpr int ES = OUT32 ? 4 : 2;
+    constexpr int PB = UM_PIECE * ES;  // bytes of a piece row
+    // thread -> strip row `lane`
+    unsigned char* mine = strip + lane * UM_STRIP_PITCH;
+    if (OUT32) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(mine + 16 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint4 u;
+            u.x = BlkCvt<Tag>::pack2(v[8 * i], v[8 * i + 1]);
+            u.y = BlkCvt<Tag>::pack2(v[8 * i + 2], v[8 * i + 3]);
+            u.z = BlkCvt<Tag>::pack2(v[8 * i + 4], v[8 * i + 5]);
+            u.w = BlkCvt<Tag>::pack2(v[8 * i + 6], v[8 * i + 7]);
+            *reinterpret_cast<uint4*>(mine + 16 * i) = u;
+        }
+    }
+    __syncwarp();
+    constexpr int WPR = PB / 4;    // 4-byte words per piece row: 16 (16-bit) or 32 (fp32)
+    constexpr int RPP = 32 / WPR;  // rows per pass: 2 or 1
+    const int wl = lane % WPR, rl = lane / WPR;
+    unsigned char* C = reinterpret_cast<unsigned char*>(p.C);
+#pragma unroll 4
+    for (int r = rl; r < 32; r += RPP) {
+        const int row = row0 + r;
+        if (row < M) {
+            const int64_t e0 = cbase + (int64_t)row * N + col0;  // element index of the piece row's first column
+            const unsigned char* src = strip + r * UM_STRIP_PITCH;
+            if (OUT32) {
+                const int col = col0 + wl;
+                if (col < N) *reinterpret_cast<float*>(C + (e0 + wl) * 4) = *reinterpret_cast<const float*>(src + 4 * wl);
+            } else if ((e0 & 1) == 0) {
+                const int col = col0 + 2 * wl;
+                if (col + 1 < N)
+                    *reinterpret_cast<uint32_t*>(C + (e0 + 2 * wl) * 2) = *reinterpret_cast<const uint32_t*>(src + 4 * wl);
+                else if (col < N)
+                    *reinterpret_cast<uint16_t*>(C + (e0 + 2 * wl) * 2) = *reinterpret_cast<const uint16_t*>(src + 4 * wl);
+            } else {
+                // odd element offset: single elements, two per lane
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int c = wl + 16 * h;
+                    if (col0 + c < N)
+                        *reinterpret_cast<uint16_t*>(C + (e0 + c) * 2) = *reinterpret_cast<const uint16_t*>(src + 2 * c);
+                }
+            }
+        }
+    }
+    __syncwarp();
+}
+
+template <typename Tag, bool OUT32>
+__global__ void __launch_bounds__(UM_THREADS, 1)
+blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap mapA,
+                     const __grid_constant__ CUtensorMap mapB) {
+    extern __shared__ unsigned char um_smem_raw[];
+    // 1024-byte aligned base for the swizzled tiles
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(um_smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* strips = smem + UM_STAGES * UM_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(strips + UM_EPI_WARPS * UM_STRIP_BYTES);
+    // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t smem_u32 = blk_smem_u32(smem);
+    const uint32_t bar0 = blk_smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (4 + s); };
+    auto tfull_bar = [&](int b) { return bar0 + 8u * (8 + b); };
+    auto tempty_bar = [&](int b) { return bar0 + 8u * (10 + b); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < UM_STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tfull_bar(b), 1);
+            mbar_init(tempty_bar(b), UM_EPI_WARPS);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(blk_smem_u32(tmem_slot)),
+                     "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int nkb = p.K / UM_BK;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            Work wk;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x) {
+                for (int sw = 0; ok && sw < wk.sweeps; ++sw)
+                    for (int ch = 0; ok && ch < wk.nchunks; ++ch)
+                        for (int kb = 0; kb < nkb; ++kb) {
+                            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+                            const uint32_t sA = smem_u32 + stage * UM_STAGE_BYTES, sB = sA + UM_A_BYTES;
+                            mbar_expect_tx(full_bar(stage), UM_STAGE_BYTES);
+                            tma_load_3d(sA, &mapA, full_bar(stage), kb * UM_BK, wk.it.rowA, wk.head);
+                            tma_load_3d(sB, &mapB, full_bar(stage), kb * UM_BK, wk.it.rowB + ch * UM_BN, wk.head);
+                            if (++stage == UM_STAGES) { stage = 0; phase ^= 1u; }
+                        }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0, slot = 0;
+            Work wk;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x) {
+                for (int sw = 0; ok && sw < wk.sweeps; ++sw)
+                    for (int ch = 0; ok && ch < wk.nchunks; ++ch) {
+                        const int buf = slot & 1;
+                        if (!mbar_wait(tempty_bar(buf), ((slot >> 1) & 1u) ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+                        tc_fence_after();
+                        const int ncols = min(wk.it.N - ch * UM_BN, UM_BN);
+                        const uint32_t idesc = instr_desc(p.bf16, (ncols + 15) & ~15);
+                        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * UM_BN);
+                        for (int kb = 0; kb < nkb; ++kb) {
+                            if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3)) { ok = false; break; }
+                            tc_fence_after();
+                            const uint32_t sA = smem_u32 + stage * UM_STAGE_BYTES, sB = sA + UM_A_BYTES;
+#pragma unroll
+                            for (int k = 0; k < UM_BK / 16; ++k)
+                                tc_mma_f16(d_tmem, smem_desc_sw128(sA + 32 * k), smem_desc_sw128(sB + 32 * k), idesc,
+                                           (kb | k) != 0);
+                            tc_commit(empty_bar(stage));  // stage reusable once these products have read it
+                            if (++stage == UM_STAGES) { stage = 0; phase ^= 1u; }
+                        }
+                        if (!ok) break;
+                        tc_commit(tfull_bar(buf));
+                        ++slot;
+                    }
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, lane quarter = warp % 4 ----------------
+        const int q = warp & 3;
+        unsigned char* strip = strips + (warp - 2) * UM_STRIP_BYTES;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        uint32_t slot = 0;
+        Work wk;
+        bool ok = true;
+        const bool softmax = p.epi == BLK_EPI_SOFTMAX;
+        const float sl = softmax ? fabsf(p.scale) * BLK_LOG2E : p.scale;
+        const float sgn = (softmax && p.scale < 0.f) ? -1.f : 1.f;
+        for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x) {
+            const int M = wk.it.M - wk.it.tm * UM_BM;  // rows of the segment from this block on
+            const int N = wk.it.N;
+            const int64_t cbase = (int64_t)wk.head * p.Dout + wk.it.offC + (int64_t)wk.it.tm * UM_BM * N;
+            const int row0 = q * 32;
+            uint32_t r[32];
+            float v[32];
+            if (!softmax) {
+                for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
+                    const int buf = slot & 1;
+                    if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 4)) { ok = false; break; }
+                    tc_fence_after();
+                    const int ncols = min(N - ch * UM_BN, UM_BN);
+                    for (int c = 0; c < ncols; c += UM_PIECE) {
+                        tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c), r);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * sl;
+                        store_piece<Tag, OUT32>(p, v, strip, cbase, row0, M, N, ch * UM_BN + c, lane);
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                }
+            } else if (wk.sweeps == 1) {
+                // whole row resident: chunk k of the row sits in accumulator (slot + k) & 1
+                for (int ch = 0; ok && ch < wk.nchunks; ++ch)
+                    if (!mbar_wait(tfull_bar((slot + ch) & 1), ((slot + ch) >> 1) & 1u, abort_flag, p.status, 5)) ok = false;
+                if (!ok) break;
+                tc_fence_after();
+                auto col_addr = [&](int c) {  // tensor-memory column of row column c
+                    return lane_addr + (uint32_t)((((slot + (c >> 8)) & 1) * UM_BN) + (c & (UM_BN - 1)));
+                };
+                float mx = -INFINITY;
+                for (int c = 0; c < N; c += UM_PIECE) {
+                    tc_ld32(col_addr(c), r);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float x = (c + i < N) ? __uint_as_float(r[i]) * sgn : -INFINITY;
+                        mx = fmaxf(mx, x);
+                    }
+                }
+                const float nm = -mx * sl;
+                float sum = 0.f;
+                for (int c = 0; c < N; c += UM_PIECE) {
+                    tc_ld32(col_addr(c), r);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float e = (c + i < N) ? blk_exp2(fmaf(__uint_as_float(r[i]) * sgn, sl, nm)) : 0.f;
+                        sum += e;
+                        r[i] = __float_as_uint(e);
+                    }
+                    tc_st32(col_addr(c), r);
+                }
+                tc_wait_st();
+                const float inv = __frcp_rn(sum);
+                for (int c = 0; c < N; c += UM_PIECE) {
+                    tc_ld32(col_addr(c), r);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * inv;
+                    store_piece<Tag, OUT32>(p, v, strip, cbase, row0, M, N, c, lane);
+                }
+                tc_fence_before();
+                __syncwarp();
+                for (int ch = 0; ch < wk.nchunks; ++ch)
+                    if (lane == 0) mbar_arrive(tempty_bar((slot + ch) & 1));
+                slot += wk.nchunks;
+            } else {
+                // two sweeps: running (max, sum), then recompute and store
+                float mx = -INFINITY, sum = 0.f;
+                for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
+                    const int buf = slot & 1;
+                    if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 6)) { ok = false; break; }
+                    tc_fence_after();
+                    const int ncols = min(N - ch * UM_BN, UM_BN);
+                    for (int c = 0; c < ncols; c += UM_PIECE) {
+                        tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c), r);
+                        float pm = -INFINITY;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            v[i] = (c + i < ncols) ? __uint_as_float(r[i]) * sgn : -INFINITY;
+                            pm = fmaxf(pm, v[i]);
+                        }
+                        const float mnew = fmaxf(mx, pm);  // finite: column c of the piece is inside the row
+                        const float nm = -mnew * sl;
+                        float ps = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ps += blk_exp2(fmaf(v[i], sl, nm));
+                        sum = sum * blk_exp2((mx - mnew) * sl) + ps;
+                        mx = mnew;
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                }
+                if (!ok) break;
+                const float nm = -mx * sl, inv = __frcp_rn(sum);
+                for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
+                    const int buf = slot & 1;
+                    if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 7)) { ok = false; break; }
+                    tc_fence_after();
+                    const int ncols = min(N - ch * UM_BN, UM_BN);
+                    for (int c = 0; c < ncols; c += UM_PIECE) {
+                        tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c), r);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = blk_exp2(fmaf(__uint_as_float(r[i]) * sgn, sl, nm)) * inv;
+                        store_piece<Tag, OUT32>(p, v, strip, cbase, row0, M, N, ch * UM_BN + c, lane);
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // a role gave up: let copies that may still be in flight land before the CTA's memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// View of a packed operand as (k, row, head): K contiguous elements per row, D elements per head.
+bool make_map(CUtensorMap* map, const void* base, int bf16, int64_t K, int64_t rows, int64_t H, int64_t D,
+              int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)H};
+    const cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)D * 2};
+    const cuuint32_t box[3] = {(cuuint32_t)UM_BK, (cuuint32_t)box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename Tag, bool OUT32>
+cudaError_t launch(const BlkUmmaParams& p, const CUtensorMap& a, const CUtensorMap& b, int sms, cudaStream_t st) {
+    auto kern = blk_gemm_umma_kernel<Tag, OUT32>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    const int64_t total = (int64_t)p.num_items * p.H;
+    const dim3 grid((unsigned)(total < sms ? total : sms)), block(UM_THREADS);
+    kern<<<grid, block, UM_SMEM_BYTES, st>>>(p, a, b);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p, const void* A, const void* B, int64_t Dm1, int64_t Dm2,
+                                 int sms, cudaStream_t st) {
+    if ((int64_t)p.num_items * p.H == 0) return cudaSuccess;
+    CUtensorMap mapA, mapB;
+    // rows of each view: whole rows that fit one head strip
+    if (!make_map(&mapA, A, p.bf16, p.K, Dm1 / p.K, p.H, Dm1, UM_BM) ||
+        !make_map(&mapB, B, p.bf16, p.K, Dm2 / p.K, p.H, Dm2, UM_BN))
+        return cudaErrorInvalidValue;
+    if (p.bf16) return p.out_f32 ? launch<BlkBf16Tag, true>(p, mapA, mapB, sms, st) : launch<BlkBf16Tag, false>(p, mapA, mapB, sms, st);
+    return p.out_f32 ? launch<BlkHalfTag, true>(p, mapA, mapB, sms, st) : launch<BlkHalfTag, false>(p, mapA, mapB, sms, st);
+}

@@ -264,6 +264,31 @@ int blk_build_gemm_schedule(blk_plan* p) {
     p->Dout = p->ao[S];
 
     const bool allow_small = !blk_env_flag("BLK_DISABLE_SMALL");
+    const bool allow_umma = !blk_env_flag("BLK_DISABLE_UMMA") && p->dtype_in != BLK_F32 && !p->ta && !p->tb &&
+                            p->Dm1 % 8 == 0 && p->Dm2 % 8 == 0;
+    // The tcgen05 kernel views each operand as one (rows, K) matrix per head, so it takes the segments of
+    // one K only: the K (a multiple of 64) that carries the most work among the segments too big for the
+    // packed small-segment kernel and whose offsets are whole rows of that view.
+    auto umma_candidate = [&](int64_t s) {
+        const int64_t m = p->M[s], n = p->N[s], k = p->K[s];
+        return allow_umma && m > 0 && n > 0 && k >= 64 && k % 64 == 0 && (m > BLK_SMALL_MAXM || n > BLK_SMALL_MAXN || !allow_small) &&
+               p->a1[s] % k == 0 && p->a2[s] % k == 0 && p->Dm1 / k < INT32_MAX && p->Dm2 / k < INT32_MAX;
+    };
+    p->umma_K = 0;
+    if (allow_umma) {
+        std::vector<std::pair<int64_t, double>> work;  // (K, work)
+        for (int64_t s = 0; s < S; ++s) {
+            if (!umma_candidate(s)) continue;
+            const double wk = (double)p->M[s] * (double)p->N[s] * (double)p->K[s];
+            bool found = false;
+            for (auto& kv : work)
+                if (kv.first == p->K[s]) { kv.second += wk; found = true; }
+            if (!found) work.push_back(std::make_pair(p->K[s], wk));
+        }
+        double best = 0;
+        for (auto& kv : work)
+            if (kv.second > best) { best = kv.second; p->umma_K = (int)kv.first; }
+    }
     p->segs.resize(S);
     p->flops = p->bytes = 0;
     for (int64_t s = 0; s < S; ++s) {
@@ -301,6 +326,13 @@ int blk_build_gemm_schedule(blk_plan* p) {
                 BlkSmallItem{sd.offA, sd.offB, sd.offC, (int32_t)m, (int32_t)n});
             continue;
         }
+        if (p->umma_K != 0 && k == p->umma_K && umma_candidate(s)) {
+            const int32_t tms = (int32_t)((m + BLK_UMMA_BM - 1) / BLK_UMMA_BM);
+            for (int32_t tm = 0; tm < tms; ++tm)
+                p->umma_items.push_back(BlkUmmaItem{(int32_t)s, tm, (int32_t)(sd.offA / k + (int64_t)tm * BLK_UMMA_BM),
+                                                    (int32_t)(sd.offB / k), sd.offC, (int32_t)m, (int32_t)n});
+            continue;
+        }
         const int32_t tms = (int32_t)((m + BLK_TILE_BM - 1) / BLK_TILE_BM);
         const int32_t tns = (int32_t)((n + BLK_TILE_BN - 1) / BLK_TILE_BN);
         for (int32_t tm = 0; tm < tms; ++tm) {
@@ -311,6 +343,10 @@ int blk_build_gemm_schedule(blk_plan* p) {
             }
         }
     }
+    // Persistent CTAs of the tcgen05 kernel take items with a fixed stride: heaviest first evens the tails.
+    std::stable_sort(p->umma_items.begin(), p->umma_items.end(), [](const BlkUmmaItem& a, const BlkUmmaItem& b) {
+        return (int64_t)std::min(a.M - a.tm * BLK_UMMA_BM, BLK_UMMA_BM) * a.N > (int64_t)std::min(b.M - b.tm * BLK_UMMA_BM, BLK_UMMA_BM) * b.N;
+    });
     // Persistent warps take small items in list order with a fixed stride: heaviest first evens the tails.
     for (auto& v : p->small_items)
         std::stable_sort(v.begin(), v.end(), [](const BlkSmallItem& a, const BlkSmallItem& b) {

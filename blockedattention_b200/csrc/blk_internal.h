@@ -52,11 +52,12 @@ struct BlkSmxChunk {
 struct BlkUmmaItem {
     int32_t seg;
     int32_t tm;       // 128-row block inside the segment
-    int32_t rowA;     // first row of that block in the [sum M, K] operand view
-    int32_t rowB;     // first row of the segment in the [sum N, K] operand view
+    int32_t rowA;     // first row of that block in the (rows, K) view of the first operand
+    int32_t rowB;     // first row of the segment in the (rows, K) view of the second operand
     int64_t offC;     // element offset of the segment's output block
-    int32_t M, N;
+    int32_t M, N;     // extents of the whole segment
 };
+static_assert(sizeof(BlkUmmaItem) == 32, "BlkUmmaItem layout");
 
 // ---- kernel geometry constants the scheduler must agree with ----------------
 constexpr int BLK_TILE_BM = 64;

@@ -45,6 +45,20 @@ struct BlkSmallParams {
     float scale;
 };
 
+struct BlkUmmaParams {
+    void* C;
+    const BlkUmmaItem* items;
+    int64_t Dout;
+    int num_items;
+    int H;
+    int K;
+    int bf16;
+    int out_f32;
+    int epi;
+    float scale;
+    int* status;
+};
+
 struct BlkSmxParams {
     const void* src;
     void* dst;
@@ -59,4 +73,6 @@ cudaError_t blk_launch_gemm_tile(const BlkGemmParams& p, int dtype_in, int ta, i
 cudaError_t blk_launch_gemm_simt(const BlkSimtParams& p, cudaStream_t st);
 cudaError_t blk_launch_scores_small(const BlkSmallParams& p, int dtype_in, int K, int bucket, int sms,
                                     cudaStream_t st);
+cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p, const void* A, const void* B, int64_t Dm1, int64_t Dm2,
+                                 int sms, cudaStream_t st);
 cudaError_t blk_launch_softmax(const BlkSmxParams& p, int dtype, cudaStream_t st);

@@ -81,6 +81,40 @@ def test_exhaustive_small_fused_softmax(cuda_device, K):
         assert (p.summary["small_items"] > 0) == (env is None)
 
 
+UMMA_SHAPES = dict(
+    M=[65, 128, 129, 100, 300, 7, 512, 640, 1, 200],
+    N=[70, 256, 257, 65, 513, 300, 512, 1030, 129, 96],
+)
+
+
+@pytest.mark.parametrize("dtype", [F16, BF16])
+@pytest.mark.parametrize("K", [64, 128, 256])
+@pytest.mark.parametrize("mode", ["scores", "scores32", "softmax"])
+def test_tcgen05_path(cuda_device, dtype, K, mode):
+    # segments too big for the packed kernel with K a multiple of 64: the TMA + tcgen05 kernel.
+    # N <= 256: one accumulator; N <= 512: whole row in tensor memory; N > 512: two sweeps.
+    M, N = UMMA_SHAPES["M"], UMMA_SHAPES["N"]
+    kw = dict(softmax=mode == "softmax", out_dtype=F32 if mode == "scores32" else None,
+              scale=0.125 if mode == "softmax" else 0.5, seed=K)
+    p = run_case(cuda_device, M, N, [K] * len(M), 3, dtype, what=f"tcgen05 {mode} K={K}", **kw)
+    assert p.summary["umma_items"] == int(np.ceil(np.array(M) / 128).sum())
+    p.check()
+    # same problem on the staged mma.sync kernel
+    p2 = run_case(cuda_device, M, N, [K] * len(M), 3, dtype, env={"BLK_DISABLE_UMMA": "1"},
+                  what=f"tile kernel {mode} K={K}", **kw)
+    assert p2.summary["umma_items"] == 0 and p2.summary["tile_items"] > 0
+
+
+def test_tcgen05_mixed_batch_and_negative_scale(cuda_device):
+    # small, tcgen05 and staged-kernel segments in one batch (K = 64 carries the tcgen05 bin; K = 48 and
+    # the odd offsets after it go to the staged kernel)
+    M = [20, 300, 64, 130, 33, 500, 90]; N = [20, 300, 64, 70, 40, 600, 200]; K = [64, 64, 64, 64, 48, 64, 64]
+    p = run_case(cuda_device, M, N, K, 2, BF16, softmax=True, scale=-0.2, what="mixed batch")
+    s = p.summary
+    assert s["umma_items"] > 0 and s["small_items"] > 0 and s["tile_items"] > 0
+    run_case(cuda_device, M, N, K, 2, F16, scale=-1.5, what="mixed batch scores")
+
+
 @pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("dtype", [F16, BF16, F32])
 def test_transposes(cuda_device, dtype, ta, tb):
