@@ -1,7 +1,8 @@
 """Builds ``blockedattention_b200/lib/libblkattn.so`` for sm_100a with nvcc.
 
 The library is built in-tree (no JIT cache) so that it travels with the source
-tree.  ``python -m blockedattention_b200.build`` rebuilds what is out of date;
+tree.  ``python blockedattention_b200/build.py`` rebuilds what is out of date (run it
+as a script: importing the package first would load the old library);
 ``--force`` rebuilds everything; ``--verbose`` adds ``-Xptxas -v``.
 """
 from __future__ import annotations
