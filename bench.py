@@ -297,6 +297,11 @@ def main():
                     "kernel": kernel, "launches_per_step": launches_per_step,
                     "algorithmic_bytes_per_step": w.bytes()}
 
+    # DRAM traffic of one step from the committed ncu capture of this workload (profiles/), where there is one
+    if args.workload == "molecular" and world == 1 and args.seed == 0:
+        roofline["traffic"] = 221.0e6  # dram__bytes_read.sum + dram__bytes_write.sum over the step's launches
+        roofline["traffic_source"] = "profiles/blk_scores_small_kernel_molecular.md"
+
     # ---- end to end through the public operator with host buffers ----------
     e2e = None
     if not args.no_e2e:

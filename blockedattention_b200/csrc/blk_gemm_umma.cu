@@ -5,7 +5,7 @@
 // item being a 128-row block of one segment of one head.  Roles:
 //   warp 0   producer: one lane issues 3-D tiled TMA loads (k, row, head) of a
 //            128 x 64 tile of the first operand and a 256 x 64 tile of the
-//            second into a 4-stage ring of 128-byte-swizzled shared memory;
+//            second into a 3-stage ring of 128-byte-swizzled shared memory;
 //   warp 1   MMA: allocates the 512 tensor-memory columns, and one lane issues
 //            tcgen05.mma (M = 128, N up to 256, K = 16 per instruction) into
 //            one of two 256-column accumulators; tcgen05.commit hands shared
@@ -45,17 +45,20 @@ namespace {
 constexpr int UM_BM = BLK_UMMA_BM;      // 128 rows per work item
 constexpr int UM_BN = 256;              // columns per accumulator
 constexpr int UM_BK = 64;               // k elements per shared-memory stage (one 128-byte swizzle row)
-constexpr int UM_STAGES = 4;
+constexpr int UM_STAGES = 3;
 constexpr int UM_A_BYTES = UM_BM * UM_BK * 2;  // 16 KB
 constexpr int UM_B_BYTES = UM_BN * UM_BK * 2;  // 32 KB
 constexpr int UM_STAGE_BYTES = UM_A_BYTES + UM_B_BYTES;
 constexpr int UM_THREADS = 192;
 constexpr int UM_EPI_WARPS = 4;
 constexpr int UM_PIECE = 32;                          // columns per tcgen05.ld
-constexpr int UM_STRIP_PITCH = UM_PIECE * 4 + 16;     // bytes per strip row (fp32 piece + pad)
+constexpr int UM_ROWPIECE_BYTES = 256;                // bytes of an output row staged per flush (128 x 16-bit, 64 x fp32)
+constexpr int UM_STRIP_PITCH = UM_ROWPIECE_BYTES + 16;  // bytes per strip row (pad keeps 16-byte stores conflict-free)
 constexpr int UM_STRIP_BYTES = 32 * UM_STRIP_PITCH;   // per epilogue warp
 constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + UM_EPI_WARPS * UM_STRIP_BYTES + 256 + 1024;
 constexpr uint32_t UM_SPIN_LIMIT = 6u << 20;
+static_assert(UM_SMEM_BYTES <= 227 * 1024, "shared memory budget");
+static_assert(UM_STAGES <= 4, "barrier slots");
 
 // ---- PTX wrappers -------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -159,15 +162,12 @@ __device__ __forceinline__ bool next_work(const BlkUmmaParams& p, uint32_t w, Wo
     return true;
 }
 
-// Writes one 32-row x 32-column piece (this warp's rows) from the strip to global memory with lanes on
-// consecutive addresses.  vals are already scaled; row = this thread's row inside the item.
+// Stage 32 consecutive columns of this thread's row (strip row = lane) at column offset `sub` * 32 of the
+// current row piece.
 template <typename Tag, bool OUT32>
-__device__ __forceinline__ void store_piece(const BlkUmmaParams& p, const float (&v)[32], unsigned char* strip,
-                                            int64_t cbase, int row0, int M, int N, int col0, int lane) {
+__device__ __forceinline__ void emit32(const float (&v)[32], unsigned char* strip, int sub, int lane) {
     constexpr int ES = OUT32 ? 4 : 2;
-    constexpr int PB = UM_PIECE * ES;  // bytes of a piece row
-    // thread -> strip row `lane`
-    unsigned char* mine = strip + lane * UM_STRIP_PITCH;
+    unsigned char* mine = strip + lane * UM_STRIP_PITCH + sub * (UM_PIECE * ES);
     if (OUT32) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -183,34 +183,52 @@ __device__ __forceinline__ void store_piece(const BlkUmmaParams& p, const float 
             *reinterpret_cast<uint4*>(mine + 16 * i) = u;
         }
     }
+}
+
+// Strip -> global for the warp's 32 rows x `ncols` columns starting at column col0: two rows per pass,
+// half a warp on consecutive addresses of each, with the widest store the row's address allows
+// (16 bytes, 4 bytes, or single 16-bit elements).
+template <bool OUT32>
+__device__ __forceinline__ void flush_piece(const BlkUmmaParams& p, unsigned char* strip, int64_t cbase, int row0,
+                                            int M, int N, int col0, int ncols, int lane) {
+    constexpr int ES = OUT32 ? 4 : 2;
+    constexpr int EPV = 16 / ES;  // elements per 16-byte vector
     __syncwarp();
-    constexpr int WPR = PB / 4;    // 4-byte words per piece row: 16 (16-bit) or 32 (fp32)
-    constexpr int RPP = 32 / WPR;  // rows per pass: 2 or 1
-    const int wl = lane % WPR, rl = lane / WPR;
     unsigned char* C = reinterpret_cast<unsigned char*>(p.C);
-#pragma unroll 4
-    for (int r = rl; r < 32; r += RPP) {
+    const int hl = lane & 15, rsel = lane >> 4;
+#pragma unroll 2
+    for (int r = rsel; r < 32; r += 2) {
         const int row = row0 + r;
-        if (row < M) {
-            const int64_t e0 = cbase + (int64_t)row * N + col0;  // element index of the piece row's first column
-            const unsigned char* src = strip + r * UM_STRIP_PITCH;
-            if (OUT32) {
-                const int col = col0 + wl;
-                if (col < N) *reinterpret_cast<float*>(C + (e0 + wl) * 4) = *reinterpret_cast<const float*>(src + 4 * wl);
-            } else if ((e0 & 1) == 0) {
-                const int col = col0 + 2 * wl;
-                if (col + 1 < N)
-                    *reinterpret_cast<uint32_t*>(C + (e0 + 2 * wl) * 2) = *reinterpret_cast<const uint32_t*>(src + 4 * wl);
-                else if (col < N)
-                    *reinterpret_cast<uint16_t*>(C + (e0 + 2 * wl) * 2) = *reinterpret_cast<const uint16_t*>(src + 4 * wl);
+        if (row >= M) continue;
+        const int64_t b0 = (cbase + (int64_t)row * N + col0) * ES;  // byte offset of the row piece in the output
+        const unsigned char* src = strip + r * UM_STRIP_PITCH;
+        unsigned char* dst = C + b0;
+        const int mis = (int)(b0 & 15);
+        if (mis == 0) {
+            const int e = hl * EPV;  // this lane's vector
+            if (e + EPV <= ncols) {
+                *reinterpret_cast<uint4*>(dst + 16 * hl) = *reinterpret_cast<const uint4*>(src + 16 * hl);
             } else {
-                // odd element offset: single elements, two per lane
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int c = wl + 16 * h;
-                    if (col0 + c < N)
-                        *reinterpret_cast<uint16_t*>(C + (e0 + c) * 2) = *reinterpret_cast<const uint16_t*>(src + 2 * c);
+                for (int i = e; i < ncols; ++i) {
+                    if (OUT32) *reinterpret_cast<float*>(dst + 4 * i) = *reinterpret_cast<const float*>(src + 4 * i);
+                    else *reinterpret_cast<uint16_t*>(dst + 2 * i) = *reinterpret_cast<const uint16_t*>(src + 2 * i);
                 }
+            }
+        } else if (OUT32 || (mis & 3) == 0) {
+            constexpr int EPW = 4 / ES;  // elements per 4-byte word
+#pragma unroll
+            for (int i = 0; i < UM_ROWPIECE_BYTES / 4 / 16; ++i) {
+                const int w = hl + 16 * i, e = w * EPW;
+                if (e + EPW <= ncols)
+                    *reinterpret_cast<uint32_t*>(dst + 4 * w) = *reinterpret_cast<const uint32_t*>(src + 4 * w);
+                else if (!OUT32 && e < ncols)
+                    *reinterpret_cast<uint16_t*>(dst + 4 * w) = *reinterpret_cast<const uint16_t*>(src + 4 * w);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < UM_ROWPIECE_BYTES / 2 / 16; ++i) {
+                const int e = hl + 16 * i;
+                if (e < ncols) *reinterpret_cast<uint16_t*>(dst + 2 * e) = *reinterpret_cast<const uint16_t*>(src + 2 * e);
             }
         }
     }
@@ -226,7 +244,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(um_smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* strips = smem + UM_STAGES * UM_STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(strips + UM_EPI_WARPS * UM_STRIP_BYTES);
-    // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty
+    // bars[0..3] full (UM_STAGES used), [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
 
@@ -325,6 +343,8 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
         const bool softmax = p.epi == BLK_EPI_SOFTMAX;
         const float sl = softmax ? fabsf(p.scale) * BLK_LOG2E : p.scale;
         const float sgn = (softmax && p.scale < 0.f) ? -1.f : 1.f;
+        const float sls = sl * sgn;                       // signed scale in the base-2 domain
+        constexpr int RP = UM_ROWPIECE_BYTES / (OUT32 ? 4 : 2);  // columns per staged row piece
         for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x) {
             const int M = wk.it.M - wk.it.tm * UM_BM;  // rows of the segment from this block on
             const int N = wk.it.N;
@@ -338,11 +358,15 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                     if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 4)) { ok = false; break; }
                     tc_fence_after();
                     const int ncols = min(N - ch * UM_BN, UM_BN);
-                    for (int c = 0; c < ncols; c += UM_PIECE) {
-                        tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c), r);
+                    for (int c0 = 0; c0 < ncols; c0 += RP) {
+                        const int pc = min(RP, ncols - c0);
+                        for (int c = 0; c < pc; c += UM_PIECE) {
+                            tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c0 + c), r);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * sl;
-                        store_piece<Tag, OUT32>(p, v, strip, cbase, row0, M, N, ch * UM_BN + c, lane);
+                            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * sl;
+                            emit32<Tag, OUT32>(v, strip, c / UM_PIECE, lane);
+                        }
+                        flush_piece<OUT32>(p, strip, cbase, row0, M, N, ch * UM_BN + c0, pc, lane);
                     }
                     tc_fence_before();
                     __syncwarp();
@@ -380,11 +404,15 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 }
                 tc_wait_st();
                 const float inv = __frcp_rn(sum);
-                for (int c = 0; c < N; c += UM_PIECE) {
-                    tc_ld32(col_addr(c), r);
+                for (int c0 = 0; c0 < N; c0 += RP) {
+                    const int pc = min(RP, N - c0);
+                    for (int c = 0; c < pc; c += UM_PIECE) {
+                        tc_ld32(col_addr(c0 + c), r);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * inv;
-                    store_piece<Tag, OUT32>(p, v, strip, cbase, row0, M, N, c, lane);
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * inv;
+                        emit32<Tag, OUT32>(v, strip, c / UM_PIECE, lane);
+                    }
+                    flush_piece<OUT32>(p, strip, cbase, row0, M, N, c0, pc, lane);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -426,11 +454,15 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                     if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 7)) { ok = false; break; }
                     tc_fence_after();
                     const int ncols = min(N - ch * UM_BN, UM_BN);
-                    for (int c = 0; c < ncols; c += UM_PIECE) {
-                        tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c), r);
+                    for (int c0 = 0; c0 < ncols; c0 += RP) {
+                        const int pc = min(RP, ncols - c0);
+                        for (int c = 0; c < pc; c += UM_PIECE) {
+                            tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c0 + c), r);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = blk_exp2(fmaf(__uint_as_float(r[i]) * sgn, sl, nm)) * inv;
-                        store_piece<Tag, OUT32>(p, v, strip, cbase, row0, M, N, ch * UM_BN + c, lane);
+                            for (int i = 0; i < 32; ++i) v[i] = blk_exp2(fmaf(__uint_as_float(r[i]), sls, nm)) * inv;
+                            emit32<Tag, OUT32>(v, strip, c / UM_PIECE, lane);
+                        }
+                        flush_piece<OUT32>(p, strip, cbase, row0, M, N, ch * UM_BN + c0, pc, lane);
                     }
                     tc_fence_before();
                     __syncwarp();
