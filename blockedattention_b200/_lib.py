@@ -40,6 +40,7 @@ SIGNATURES = {
     "blk_softmax_plan_create": (C.c_int, [C.POINTER(_vp), _i64p, _i64p, _i64p, C.c_int64, C.c_int64, C.c_int,
                                           C.c_int]),
     "blk_softmax_run": (C.c_int, [_vp, _vp, _vp, C.c_float, _vp]),
+    "blk_softmax_noalloc": (C.c_int, [_vp, _vp, _i64p, _i64p, C.c_int64, C.c_int64, C.c_int, C.c_float, _vp]),
     "blk_plan_destroy": (None, [_vp]),
     "blk_plan_extents": (C.c_int, [_vp, _i64p, _i64p, _i64p]),
     "blk_plan_offsets": (C.c_int, [_vp, _i64p, _i64p, _i64p]),
@@ -60,7 +61,7 @@ class BlkError(RuntimeError):
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m blockedattention_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python blockedattention_b200/build.py` "
             "(nvcc, sm_100a). There is no CPU or PyTorch fallback.")
     lib = C.CDLL(LIB_PATH)
     for name, (res, args) in SIGNATURES.items():

@@ -71,6 +71,7 @@ constexpr int BLK_SMALL_MAXM = 64;
 constexpr int BLK_SMALL_BUCKETS = 2;  // N <= 32, N <= 64
 constexpr int BLK_SMX_WINDOW_BYTES = 16384;
 constexpr int BLK_UMMA_BM = 128;
+constexpr int BLK_NOALLOC_MAX_CHUNKS = 65536;  // entries of the built-in chunk table of blk_softmax_noalloc
 
 // ---- the plan ----------------------------------------------------------------
 struct blk_plan {

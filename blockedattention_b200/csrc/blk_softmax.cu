@@ -16,6 +16,8 @@
 // Replaces upstream sparseBlockedSoftmax_warp / _block
 // (csrc/cuda/spBlkSoftmax.cu:88-138, :182-269) and the per-row host table
 // (csrc/cuda/spBlkSoftmax.cu:358-373).
+#include <string>
+
 #include "blk_device.cuh"
 #include "blk_kernels.h"
 
@@ -197,4 +199,106 @@ cudaError_t blk_launch_softmax(const BlkSmxParams& p, int dtype, cudaStream_t st
     else if (dtype == BLK_BF16) blk_softmax_kernel<SmxIO16<BlkBf16Tag>><<<grid, block, 0, st>>>(p);
     else blk_softmax_kernel<SmxIO32><<<grid, block, 0, st>>>(p);
     return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Softmax without a plan and without any device allocation.
+//
+// Some hosts of this library may not allocate device memory at the point where
+// they need the operator: a runtime that has handed all device memory to its
+// own arena, a plugin called inside someone else's memory pool, a caller on a
+// real-time path where cudaMalloc's implicit synchronisation is not acceptable.
+// For them the chunk table that blk_softmax_plan_create would upload into a
+// cudaMalloc'ed buffer lives instead in the fixed array below, which every GPU
+// that loads the library carries (1 MB) until the process exits.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) BlkSmxChunk g_noalloc_chunks[BLK_NOALLOC_MAX_CHUNKS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+// Device address of g_noalloc_chunks per device; the symbol's name is only a host-side handle.
+BlkSmxChunk* g_noalloc_dev_ptr[NOALLOC_MAX_DEVICES] = {};
+}  // namespace
+
+extern "C" int blk_softmax_noalloc(const void* src, void* out, const int64_t* rows, const int64_t* cols, int64_t S,
+                                   int64_t H, int dtype, float scale, void* cuda_stream) {
+    if (S < 0 || H < 0 || (S > 0 && (!rows || !cols))) {
+        blk_set_error("blk_softmax_noalloc: negative count or null list");
+        return BLK_ERR_INVALID;
+    }
+    if (dtype < BLK_F16 || dtype > BLK_F32) {
+        blk_set_error("blk_softmax_noalloc: unsupported dtype");
+        return BLK_ERR_UNSUPPORTED;
+    }
+    // host-side schedule only (device = -1: nothing is uploaded or allocated on the GPU)
+    blk_plan plan;
+    plan.kind = 1;
+    plan.S = S;
+    plan.H = H;
+    plan.dtype_in = plan.dtype_out = dtype;
+    plan.device = -1;
+    plan.M.assign(rows, rows + S);
+    plan.N.assign(cols, cols + S);
+    plan.a1.resize(S + 1);
+    int rc = blk_softmax_offsets(rows, cols, S, plan.a1.data());
+    if (rc == BLK_OK) rc = blk_build_softmax_schedule(&plan);
+    if (rc != BLK_OK) return rc;
+    const size_t nchunks = plan.smx_chunks.size();
+    if (nchunks == 0 || H == 0) return BLK_OK;
+    if (nchunks > (size_t)BLK_NOALLOC_MAX_CHUNKS) {
+        blk_set_error("blk_softmax_noalloc: this batch needs " + std::to_string(nchunks) +
+                      " chunks of 16 KB, the built-in table holds " + std::to_string(BLK_NOALLOC_MAX_CHUNKS) +
+                      "; use blk_softmax_plan_create / blk_softmax_run for larger batches");
+        return BLK_ERR_UNSUPPORTED;
+    }
+    if ((int64_t)nchunks * H > 0x7fffffffLL) {
+        blk_set_error("blk_softmax_noalloc: chunks x heads exceeds 2^31-1 CTAs");
+        return BLK_ERR_UNSUPPORTED;
+    }
+    if (!src || !out) {
+        blk_set_error("blk_softmax_noalloc: null buffer");
+        return BLK_ERR_INVALID;
+    }
+    if ((reinterpret_cast<uintptr_t>(src) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u)) {
+        blk_set_error("blk_softmax_noalloc: device pointers must be 16-byte aligned");
+        return BLK_ERR_UNALIGNED;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+        blk_set_error("blk_softmax_noalloc: cannot identify the current device");
+        return BLK_ERR_CUDA;
+    }
+    if (!g_noalloc_dev_ptr[dev]) {
+        // one-time set-up on this device (it is the current one): resolve the array's device address
+        BlkSmxChunk* ptr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_chunks);
+        if (e != cudaSuccess || !ptr) {
+            blk_set_error(std::string("blk_softmax_noalloc: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
+            return BLK_ERR_CUDA;
+        }
+        g_noalloc_dev_ptr[dev] = ptr;
+    }
+    BlkSmxChunk* table = g_noalloc_dev_ptr[dev];
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    // every call rewrites the entries it uses; nothing in the table has to start at zero
+    e = cudaMemcpyAsync(table, plan.smx_chunks.data(), nchunks * sizeof(BlkSmxChunk), cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) {
+        blk_set_error(std::string("blk_softmax_noalloc: table upload failed: ") + cudaGetErrorString(e));
+        return BLK_ERR_CUDA;
+    }
+    BlkSmxParams xp{};
+    xp.src = src;
+    xp.dst = out;
+    xp.chunks = table;
+    xp.D = plan.Dm1;
+    xp.num_chunks = (int)nchunks;
+    xp.H = (int)H;
+    xp.scale = scale;
+    e = blk_launch_softmax(xp, dtype, st);
+    if (e != cudaSuccess) {
+        blk_set_error(std::string("blk_softmax_noalloc: launch failed: ") + cudaGetErrorString(e));
+        return BLK_ERR_CUDA;
+    }
+    return BLK_OK;
 }
