@@ -284,7 +284,7 @@ __device__ __forceinline__ void tile_body(const BlkGemmParams& p, const BlkSeg& 
 }
 
 template <typename Tag, bool TA, bool TB>
-__global__ void __launch_bounds__(NT) blk_gemm_tile_kernel(const BlkGemmParams p) {
+__global__ void __launch_bounds__(NT, 3) blk_gemm_tile_kernel(const BlkGemmParams p) {
     __shared__ __align__(16) uint16_t sA[2][A_STAGE];
     __shared__ __align__(16) uint16_t sB[2][B_STAGE];
     const int64_t bid = blockIdx.x;

@@ -1,7 +1,7 @@
 // Large-segment kernel of the varlen blocked GEMM on the 5th-generation tensor
 // cores: TMA-fed tcgen05.mma with the accumulator in tensor memory.
 //
-// A persistent CTA (one per SM, 6 warps) walks a static list of work items, an
+// A persistent CTA (one per SM, 10 warps) walks a static list of work items, an
 // item being a 128-row block of one segment of one head.  Roles:
 //   warp 0   producer: one lane issues 3-D tiled TMA loads (k, row, head) of a
 //            128 x 64 tile of the first operand and a 256 x 64 tile of the
@@ -10,10 +10,13 @@
 //            tcgen05.mma (M = 128, N up to 256, K = 16 per instruction) into
 //            one of two 256-column accumulators; tcgen05.commit hands shared
 //            memory stages back to the producer and accumulators to the epilogue;
-//   warps 2-5 epilogue: each owns 32 accumulator lanes (= rows).  A thread
-//            reads its row 32 columns at a time (tcgen05.ld), applies the
-//            epilogue and the warp writes the piece out through a padded
-//            shared-memory strip so that lanes store consecutive addresses.
+//   warps 2-9 epilogue: a warp may read the 32 accumulator lanes (= rows) of its
+//            quarter; the two warps of a quarter take alternate 128-column
+//            blocks of the row and exchange partial row statistics through
+//            shared memory.  A thread reads its row 32 columns at a time
+//            (tcgen05.ld), applies the epilogue and the warp writes the piece
+//            out through a padded shared-memory strip so that lanes store
+//            consecutive addresses with the widest store the row allows.
 //
 // Epilogues.  Scores: scale and round.  Softmax with N <= 512: both
 // accumulators hold the whole row; pass 1 takes the row maximum, pass 2 writes
@@ -49,13 +52,14 @@ constexpr int UM_STAGES = 3;
 constexpr int UM_A_BYTES = UM_BM * UM_BK * 2;  // 16 KB
 constexpr int UM_B_BYTES = UM_BN * UM_BK * 2;  // 32 KB
 constexpr int UM_STAGE_BYTES = UM_A_BYTES + UM_B_BYTES;
-constexpr int UM_THREADS = 192;
-constexpr int UM_EPI_WARPS = 4;
+constexpr int UM_THREADS = 320;
+constexpr int UM_EPI_WARPS = 8;
 constexpr int UM_PIECE = 32;                          // columns per tcgen05.ld
 constexpr int UM_ROWPIECE_BYTES = 256;                // bytes of an output row staged per flush (128 x 16-bit, 64 x fp32)
 constexpr int UM_STRIP_PITCH = UM_ROWPIECE_BYTES + 16;  // bytes per strip row (pad keeps 16-byte stores conflict-free)
 constexpr int UM_STRIP_BYTES = 32 * UM_STRIP_PITCH;   // per epilogue warp
-constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + UM_EPI_WARPS * UM_STRIP_BYTES + 256 + 1024;
+constexpr int UM_XCH_BYTES = 2 * 4 * 128 * 4;  // row statistics exchanged between the two halves, double-buffered
+constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + UM_EPI_WARPS * UM_STRIP_BYTES + UM_XCH_BYTES + 256 + 1024;
 constexpr uint32_t UM_SPIN_LIMIT = 6u << 20;
 static_assert(UM_SMEM_BYTES <= 227 * 1024, "shared memory budget");
 static_assert(UM_STAGES <= 4, "barrier slots");
@@ -139,9 +143,9 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 // kind::f16, fp32 accumulate, both operands K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t instr_desc(int bf16, int n) {
-    return (1u << 4) | ((uint32_t)bf16 << 7) | ((uint32_t)bf16 << 10) | ((uint32_t)(n >> 3) << 17) |
-           ((uint32_t)(UM_BM >> 4) << 24);
+__device__ __forceinline__ uint32_t instr_desc(int bf16, int n, int negate_a) {
+    return (1u << 4) | ((uint32_t)bf16 << 7) | ((uint32_t)bf16 << 10) | ((uint32_t)negate_a << 13) |
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(UM_BM >> 4) << 24);
 }
 
 struct Work {
@@ -163,72 +167,68 @@ __device__ __forceinline__ bool next_work(const BlkUmmaParams& p, uint32_t w, Wo
 }
 
 // Stage 32 consecutive columns of this thread's row (strip row = lane) at column offset `sub` * 32 of the
-// current row piece.
+// current row piece.  The row is written `shift` bytes into its strip row, where shift is the row's byte
+// offset modulo 16 in the output: the strip then mirrors global memory modulo 16 bytes and every row can be
+// copied out with aligned 16-byte vectors.  `carry` holds the last word of the previous call of this piece.
 template <typename Tag, bool OUT32>
-__device__ __forceinline__ void emit32(const float (&v)[32], unsigned char* strip, int sub, int lane) {
-    constexpr int ES = OUT32 ? 4 : 2;
-    unsigned char* mine = strip + lane * UM_STRIP_PITCH + sub * (UM_PIECE * ES);
+__device__ __forceinline__ void emit32(const float (&v)[32], unsigned char* strip, int sub, int lane, int shift,
+                                       uint32_t& carry) {
+    const uint32_t base = blk_smem_u32(strip) + lane * UM_STRIP_PITCH + (shift & ~3) + sub * (UM_PIECE * (OUT32 ? 4 : 2));
     if (OUT32) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<float4*>(mine + 16 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        for (int i = 0; i < 32; ++i) blk_sts_f32(base + 4 * i, v[i]);
     } else {
+        const int sb = (shift & 2) * 8;  // 0 or 16 bits: odd element offset of the row
+        uint32_t prev = carry;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint4 u;
-            u.x = BlkCvt<Tag>::pack2(v[8 * i], v[8 * i + 1]);
-            u.y = BlkCvt<Tag>::pack2(v[8 * i + 2], v[8 * i + 3]);
-            u.z = BlkCvt<Tag>::pack2(v[8 * i + 4], v[8 * i + 5]);
-            u.w = BlkCvt<Tag>::pack2(v[8 * i + 6], v[8 * i + 7]);
-            *reinterpret_cast<uint4*>(mine + 16 * i) = u;
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t w = BlkCvt<Tag>::pack2(v[2 * i], v[2 * i + 1]);
+            blk_sts_b32(base + 4 * i, __funnelshift_l(prev, w, sb));
+            prev = w;
         }
+        blk_sts_b32(base + 64, __funnelshift_l(prev, 0u, sb));  // spill-over half word (rewritten by the next call)
+        carry = prev;
     }
 }
 
-// Strip -> global for the warp's 32 rows x `ncols` columns starting at column col0: two rows per pass,
-// half a warp on consecutive addresses of each, with the widest store the row's address allows
-// (16 bytes, 4 bytes, or single 16-bit elements).
+// Strip -> global for the warp's 32 rows x `ncols` columns starting at column col0: two rows per pass, half a
+// warp on consecutive 16-byte vectors of each (the strip is laid out so that they are aligned in global
+// memory too); only the ragged first and last vector of a row piece go out as single elements.
 template <bool OUT32>
 __device__ __forceinline__ void flush_piece(const BlkUmmaParams& p, unsigned char* strip, int64_t cbase, int row0,
                                             int M, int N, int col0, int ncols, int lane) {
     constexpr int ES = OUT32 ? 4 : 2;
-    constexpr int EPV = 16 / ES;  // elements per 16-byte vector
     __syncwarp();
     unsigned char* C = reinterpret_cast<unsigned char*>(p.C);
     const int hl = lane & 15, rsel = lane >> 4;
+    const int nbytes = ncols * ES;
 #pragma unroll 2
     for (int r = rsel; r < 32; r += 2) {
         const int row = row0 + r;
         if (row >= M) continue;
         const int64_t b0 = (cbase + (int64_t)row * N + col0) * ES;  // byte offset of the row piece in the output
-        const unsigned char* src = strip + r * UM_STRIP_PITCH;
-        unsigned char* dst = C + b0;
-        const int mis = (int)(b0 & 15);
-        if (mis == 0) {
-            const int e = hl * EPV;  // this lane's vector
-            if (e + EPV <= ncols) {
-                *reinterpret_cast<uint4*>(dst + 16 * hl) = *reinterpret_cast<const uint4*>(src + 16 * hl);
-            } else {
-                for (int i = e; i < ncols; ++i) {
-                    if (OUT32) *reinterpret_cast<float*>(dst + 4 * i) = *reinterpret_cast<const float*>(src + 4 * i);
-                    else *reinterpret_cast<uint16_t*>(dst + 2 * i) = *reinterpret_cast<const uint16_t*>(src + 2 * i);
-                }
-            }
-        } else if (OUT32 || (mis & 3) == 0) {
-            constexpr int EPW = 4 / ES;  // elements per 4-byte word
-#pragma unroll
-            for (int i = 0; i < UM_ROWPIECE_BYTES / 4 / 16; ++i) {
-                const int w = hl + 16 * i, e = w * EPW;
-                if (e + EPW <= ncols)
-                    *reinterpret_cast<uint32_t*>(dst + 4 * w) = *reinterpret_cast<const uint32_t*>(src + 4 * w);
-                else if (!OUT32 && e < ncols)
-                    *reinterpret_cast<uint16_t*>(dst + 4 * w) = *reinterpret_cast<const uint16_t*>(src + 4 * w);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < UM_ROWPIECE_BYTES / 2 / 16; ++i) {
-                const int e = hl + 16 * i;
-                if (e < ncols) *reinterpret_cast<uint16_t*>(dst + 2 * e) = *reinterpret_cast<const uint16_t*>(src + 2 * e);
+        const int sh = (int)(b0 & 15);
+        const unsigned char* src = strip + r * UM_STRIP_PITCH;  // byte sh of src <-> byte b0 of the output
+        unsigned char* dst = C + (b0 - sh);                     // 16-byte aligned
+        const int end = sh + nbytes;
+        // full vectors [16 j, 16 j + 16) inside [sh, end): lane hl takes j = hl, lane 0 also j = 16
+        {
+            const int lo = 16 * hl;
+            if (lo >= sh && lo + 16 <= end)
+                *reinterpret_cast<uint4*>(dst + lo) = *reinterpret_cast<const uint4*>(src + lo);
+            if (hl == 0 && 272 <= end)
+                *reinterpret_cast<uint4*>(dst + 256) = *reinterpret_cast<const uint4*>(src + 256);
+        }
+        // the ragged first and last vector, one element per lane: lanes 0-7 the first, lanes 8-15 the last
+        {
+            const int tail = end & ~15;
+            const bool is_tail = hl >= 8;
+            const int b = (is_tail ? tail : 0) + ES * (hl & 7);
+            const bool first_full = sh == 0 && end >= 16;
+            const bool ok = (hl & 7) * ES < 16 && b >= sh && b < end && (is_tail ? tail != 0 : !first_full);
+            if (ok) {
+                if (OUT32) *reinterpret_cast<float*>(dst + b) = *reinterpret_cast<const float*>(src + b);
+                else *reinterpret_cast<uint16_t*>(dst + b) = *reinterpret_cast<const uint16_t*>(src + b);
             }
         }
     }
@@ -243,7 +243,8 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
     // 1024-byte aligned base for the swizzled tiles
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(um_smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* strips = smem + UM_STAGES * UM_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(strips + UM_EPI_WARPS * UM_STRIP_BYTES);
+    float* xch = reinterpret_cast<float*>(strips + UM_EPI_WARPS * UM_STRIP_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(strips + UM_EPI_WARPS * UM_STRIP_BYTES + UM_XCH_BYTES);
     // bars[0..3] full (UM_STAGES used), [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
@@ -266,6 +267,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
             mbar_init(tempty_bar(b), UM_EPI_WARPS);
         }
         *abort_flag = 0;
+        for (int i = 0; i < 4; ++i) reinterpret_cast<volatile uint32_t*>(bars + 14)[i] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
@@ -313,7 +315,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                         if (!mbar_wait(tempty_bar(buf), ((slot >> 1) & 1u) ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
                         tc_fence_after();
                         const int ncols = min(wk.it.N - ch * UM_BN, UM_BN);
-                        const uint32_t idesc = instr_desc(p.bf16, (ncols + 15) & ~15);
+                        const uint32_t idesc = instr_desc(p.bf16, (ncols + 15) & ~15, p.epi == BLK_EPI_SOFTMAX && p.scale < 0.f);
                         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * UM_BN);
                         for (int kb = 0; kb < nkb; ++kb) {
                             if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3)) { ok = false; break; }
@@ -333,41 +335,78 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..5, lane quarter = warp % 4 ----------------
-        const int q = warp & 3;
+        // ---------------- epilogue: warps 2..9 ----------------
+        // lane quarter q = warp % 4 (the 32 accumulator lanes a warp may read); the two warps of a quarter
+        // split the row's 128-column blocks by parity (half h) and exchange their partial row statistics.
+        const int q = warp & 3, h = (warp - 2) >> 2;
         unsigned char* strip = strips + (warp - 2) * UM_STRIP_BYTES;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-        uint32_t slot = 0;
+        const int myrow = q * 32 + lane;
+        uint32_t slot = 0, seq = 0;
         Work wk;
         bool ok = true;
         const bool softmax = p.epi == BLK_EPI_SOFTMAX;
-        const float sl = softmax ? fabsf(p.scale) * BLK_LOG2E : p.scale;
-        const float sgn = (softmax && p.scale < 0.f) ? -1.f : 1.f;
-        const float sls = sl * sgn;                       // signed scale in the base-2 domain
+        const float sl = softmax ? fabsf(p.scale) * BLK_LOG2E : p.scale;  // a negative softmax scale is applied by
+                                                                          // the MMA (negated A), see instr_desc
         constexpr int RP = UM_ROWPIECE_BYTES / (OUT32 ? 4 : 2);  // columns per staged row piece
-        for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x) {
+        constexpr int CB = 128;                                  // columns per block owned by one half
+        // Rendezvous of the two warps of a quarter (after each has published its row statistics): a shared
+        // counter and a bounded spin, so that a warp whose partner gave up cannot wait for ever.
+        volatile uint32_t* pair_cnt = reinterpret_cast<volatile uint32_t*>(bars + 14) + q;
+        uint32_t pair_target = 0;
+        auto pair_sync = [&]() -> bool {
+            pair_target += 2;
+            __threadfence_block();
+            __syncwarp();
+            if (lane == 0) atomicAdd(const_cast<uint32_t*>(pair_cnt), 1u);
+            bool good = false;
+            for (uint32_t i = 0; i < UM_SPIN_LIMIT; ++i) {
+                if ((int32_t)(*pair_cnt - pair_target) >= 0) { good = true; break; }
+                if (i > 64) __nanosleep(32);
+                if ((i & 255u) == 255u && *abort_flag) break;
+            }
+            if (!good) {
+                *abort_flag = 1;
+                atomicCAS(p.status, 0, 8);
+            }
+            __syncwarp();
+            __threadfence_block();
+            return good;
+        };
+        // scale, round and store columns [c_lo, c_hi) of the row; tcol(c) gives the tensor-memory column
+        auto store_cols = [&](int c_lo, int c_hi, auto tcol, auto xform, int64_t cbase, int M, int N) {
+            uint32_t r[32];
+            float v[32];
+            for (int c0 = c_lo; c0 < c_hi; c0 += RP) {
+                const int pc = min(RP, c_hi - c0);
+                // this thread's row of the piece starts at this byte offset modulo 16 in the output
+                const int shift = (int)(((cbase + (int64_t)myrow * N + c0) * (OUT32 ? 4 : 2)) & 15);
+                uint32_t carry = 0;
+                for (int c = 0; c < pc; c += UM_PIECE) {
+                    tc_ld32(lane_addr + tcol(c0 + c), r);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = xform(__uint_as_float(r[i]));
+                    emit32<Tag, OUT32>(v, strip, c / UM_PIECE, lane, shift, carry);
+                }
+                flush_piece<OUT32>(p, strip, cbase, q * 32, M, N, c0, pc, lane);
+            }
+        };
+        for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x, ++seq) {
             const int M = wk.it.M - wk.it.tm * UM_BM;  // rows of the segment from this block on
             const int N = wk.it.N;
             const int64_t cbase = (int64_t)wk.head * p.Dout + wk.it.offC + (int64_t)wk.it.tm * UM_BM * N;
-            const int row0 = q * 32;
-            uint32_t r[32];
-            float v[32];
+            volatile float* xm = xch + (seq & 1) * 512;  // [half][row] maxima, then [2 + half][row] sums
             if (!softmax) {
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
                     const int buf = slot & 1;
                     if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 4)) { ok = false; break; }
                     tc_fence_after();
                     const int ncols = min(N - ch * UM_BN, UM_BN);
-                    for (int c0 = 0; c0 < ncols; c0 += RP) {
-                        const int pc = min(RP, ncols - c0);
-                        for (int c = 0; c < pc; c += UM_PIECE) {
-                            tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c0 + c), r);
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * sl;
-                            emit32<Tag, OUT32>(v, strip, c / UM_PIECE, lane);
-                        }
-                        flush_piece<OUT32>(p, strip, cbase, row0, M, N, ch * UM_BN + c0, pc, lane);
-                    }
+                    const int lo = h * CB, hi = min(lo + CB, ncols);
+                    if (lo < hi)
+                        store_cols(ch * UM_BN + lo, ch * UM_BN + hi,
+                                   [&](int c) { return (uint32_t)(buf * UM_BN + (c - ch * UM_BN)); },
+                                   [&](float x) { return x * sl; }, cbase, M, N);
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty_bar(buf));
@@ -378,69 +417,89 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                     if (!mbar_wait(tfull_bar((slot + ch) & 1), ((slot + ch) >> 1) & 1u, abort_flag, p.status, 5)) ok = false;
                 if (!ok) break;
                 tc_fence_after();
-                auto col_addr = [&](int c) {  // tensor-memory column of row column c
-                    return lane_addr + (uint32_t)((((slot + (c >> 8)) & 1) * UM_BN) + (c & (UM_BN - 1)));
+                auto tcol = [&](int c) {  // tensor-memory column of row column c
+                    return (uint32_t)((((slot + (c >> 8)) & 1) * UM_BN) + (c & (UM_BN - 1)));
                 };
+                uint32_t r[32];
+                // pass 1: maximum over this half's blocks
                 float mx = -INFINITY;
-                for (int c = 0; c < N; c += UM_PIECE) {
-                    tc_ld32(col_addr(c), r);
+                for (int b0 = h * CB; b0 < N; b0 += 2 * CB) {
+                    const int bend = min(b0 + CB, N);
+                    for (int c = b0; c < bend; c += UM_PIECE) {
+                        tc_ld32(lane_addr + tcol(c), r);
+                        if (c + 32 <= bend) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float x = (c + i < N) ? __uint_as_float(r[i]) * sgn : -INFINITY;
-                        mx = fmaxf(mx, x);
+                            for (int i = 0; i < 32; i += 2)
+                                mx = fmaxf(mx, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (c + i < bend) mx = fmaxf(mx, __uint_as_float(r[i]));
+                        }
                     }
                 }
+                xm[h * 128 + myrow] = mx;
+                if (!pair_sync()) { ok = false; break; }
+                mx = fmaxf(mx, xm[(h ^ 1) * 128 + myrow]);
                 const float nm = -mx * sl;
-                float sum = 0.f;
-                for (int c = 0; c < N; c += UM_PIECE) {
-                    tc_ld32(col_addr(c), r);
+                // pass 2: exponentials back into tensor memory, partial sum
+                float s4[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int b0 = h * CB; b0 < N; b0 += 2 * CB) {
+                    const int bend = min(b0 + CB, N);
+                    for (int c = b0; c < bend; c += UM_PIECE) {
+                        tc_ld32(lane_addr + tcol(c), r);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float e = (c + i < N) ? blk_exp2(fmaf(__uint_as_float(r[i]) * sgn, sl, nm)) : 0.f;
-                        sum += e;
-                        r[i] = __float_as_uint(e);
+                        for (int i = 0; i < 32; ++i) {
+                            float e = blk_exp2(fmaf(__uint_as_float(r[i]), sl, nm));
+                            if (c + 32 > bend) e = (c + i < bend) ? e : 0.f;
+                            s4[i & 3] += e;
+                            r[i] = __float_as_uint(e);
+                        }
+                        tc_st32(lane_addr + tcol(c), r);
                     }
-                    tc_st32(col_addr(c), r);
                 }
                 tc_wait_st();
+                float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+                xm[(2 + h) * 128 + myrow] = sum;
+                if (!pair_sync()) { ok = false; break; }
+                sum += xm[(2 + (h ^ 1)) * 128 + myrow];
                 const float inv = __frcp_rn(sum);
-                for (int c0 = 0; c0 < N; c0 += RP) {
-                    const int pc = min(RP, N - c0);
-                    for (int c = 0; c < pc; c += UM_PIECE) {
-                        tc_ld32(col_addr(c0 + c), r);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * inv;
-                        emit32<Tag, OUT32>(v, strip, c / UM_PIECE, lane);
-                    }
-                    flush_piece<OUT32>(p, strip, cbase, row0, M, N, c0, pc, lane);
-                }
+                // pass 3: normalise and store
+                for (int b0 = h * CB; b0 < N; b0 += 2 * CB)
+                    store_cols(b0, min(b0 + CB, N), tcol, [&](float x) { return x * inv; }, cbase, M, N);
                 tc_fence_before();
                 __syncwarp();
                 for (int ch = 0; ch < wk.nchunks; ++ch)
                     if (lane == 0) mbar_arrive(tempty_bar((slot + ch) & 1));
                 slot += wk.nchunks;
             } else {
-                // two sweeps: running (max, sum), then recompute and store
+                // two sweeps: running (max, sum) over this half's blocks, then recompute and store
                 float mx = -INFINITY, sum = 0.f;
+                uint32_t r[32];
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
                     const int buf = slot & 1;
                     if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 6)) { ok = false; break; }
                     tc_fence_after();
                     const int ncols = min(N - ch * UM_BN, UM_BN);
-                    for (int c = 0; c < ncols; c += UM_PIECE) {
+                    const int lo = h * CB, hi = min(lo + CB, ncols);
+                    for (int c = lo; c < hi; c += UM_PIECE) {
                         tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c), r);
+                        const bool part = c + 32 > hi;
+                        if (part) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (c + i >= hi) r[i] = 0xff800000u;  // -inf
+                        }
                         float pm = -INFINITY;
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            v[i] = (c + i < ncols) ? __uint_as_float(r[i]) * sgn : -INFINITY;
-                            pm = fmaxf(pm, v[i]);
-                        }
+                        for (int i = 0; i < 32; i += 2)
+                            pm = fmaxf(pm, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
                         const float mnew = fmaxf(mx, pm);  // finite: column c of the piece is inside the row
                         const float nm = -mnew * sl;
-                        float ps = 0.f;
+                        float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) ps += blk_exp2(fmaf(v[i], sl, nm));
-                        sum = sum * blk_exp2((mx - mnew) * sl) + ps;
+                        for (int i = 0; i < 32; ++i) s4[i & 3] += blk_exp2(fmaf(__uint_as_float(r[i]), sl, nm));
+                        sum = sum * blk_exp2((mx - mnew) * sl) + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
                         mx = mnew;
                     }
                     tc_fence_before();
@@ -448,22 +507,26 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                     if (lane == 0) mbar_arrive(tempty_bar(buf));
                 }
                 if (!ok) break;
+                xm[h * 128 + myrow] = mx;
+                xm[(2 + h) * 128 + myrow] = sum;
+                if (!pair_sync()) break;
+                {
+                    const float m2 = xm[(h ^ 1) * 128 + myrow], l2 = xm[(2 + (h ^ 1)) * 128 + myrow];
+                    const float m = fmaxf(mx, m2);
+                    sum = sum * blk_exp2((mx - m) * sl) + l2 * blk_exp2((m2 - m) * sl);
+                    mx = m;
+                }
                 const float nm = -mx * sl, inv = __frcp_rn(sum);
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
                     const int buf = slot & 1;
                     if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 7)) { ok = false; break; }
                     tc_fence_after();
                     const int ncols = min(N - ch * UM_BN, UM_BN);
-                    for (int c0 = 0; c0 < ncols; c0 += RP) {
-                        const int pc = min(RP, ncols - c0);
-                        for (int c = 0; c < pc; c += UM_PIECE) {
-                            tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c0 + c), r);
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = blk_exp2(fmaf(__uint_as_float(r[i]), sls, nm)) * inv;
-                            emit32<Tag, OUT32>(v, strip, c / UM_PIECE, lane);
-                        }
-                        flush_piece<OUT32>(p, strip, cbase, row0, M, N, ch * UM_BN + c0, pc, lane);
-                    }
+                    const int lo = h * CB, hi = min(lo + CB, ncols);
+                    if (lo < hi)
+                        store_cols(ch * UM_BN + lo, ch * UM_BN + hi,
+                                   [&](int c) { return (uint32_t)(buf * UM_BN + (c - ch * UM_BN)); },
+                                   [&](float x) { return blk_exp2(fmaf(x, sl, nm)) * inv; }, cbase, M, N);
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty_bar(buf));
