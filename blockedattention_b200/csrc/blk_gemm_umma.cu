@@ -1,7 +1,7 @@
 // Large-segment kernel of the varlen blocked GEMM on the 5th-generation tensor
 // cores: TMA-fed tcgen05.mma with the accumulator in tensor memory.
 //
-// A persistent CTA (one per SM, 10 warps) walks a static list of work items, an
+// A persistent CTA (one per SM, 18 warps) walks a static list of work items, an
 // item being a 128-row block of one segment of one head.  Roles:
 //   warp 0   producer: one lane issues 3-D tiled TMA loads (k, row, head) of a
 //            128 x 64 tile of the first operand and a 256 x 64 tile of the
@@ -10,9 +10,9 @@
 //            tcgen05.mma (M = 128, N up to 256, K = 16 per instruction) into
 //            one of two 256-column accumulators; tcgen05.commit hands shared
 //            memory stages back to the producer and accumulators to the epilogue;
-//   warps 2-9 epilogue: a warp may read the 32 accumulator lanes (= rows) of its
-//            quarter; the two warps of a quarter take alternate 128-column
-//            blocks of the row and exchange partial row statistics through
+//   warps 2-17 epilogue: a warp may read the 32 accumulator lanes (= rows) of its
+//            quarter; the four warps of a quarter each take 64 of every 256
+//            columns of the row and exchange partial row statistics through
 //            shared memory.  A thread reads its row 32 columns at a time
 //            (tcgen05.ld), applies the epilogue and the warp writes the piece
 //            out through a padded shared-memory strip so that lanes store
@@ -52,14 +52,16 @@ constexpr int UM_STAGES = 3;
 constexpr int UM_A_BYTES = UM_BM * UM_BK * 2;  // 16 KB
 constexpr int UM_B_BYTES = UM_BN * UM_BK * 2;  // 32 KB
 constexpr int UM_STAGE_BYTES = UM_A_BYTES + UM_B_BYTES;
-constexpr int UM_THREADS = 320;
-constexpr int UM_EPI_WARPS = 8;
+constexpr int UM_SPLIT = 4;                           // epilogue warps per accumulator-lane quarter
+constexpr int UM_EPI_WARPS = 4 * UM_SPLIT;
+constexpr int UM_THREADS = 64 + 32 * UM_EPI_WARPS;
+constexpr int UM_CB = UM_BN / UM_SPLIT;               // columns of a chunk owned by one of them
 constexpr int UM_PIECE = 32;                          // columns per tcgen05.ld
-constexpr int UM_ROWPIECE_BYTES = 256;                // bytes of an output row staged per flush (128 x 16-bit, 64 x fp32)
-constexpr int UM_STRIP_PITCH = UM_ROWPIECE_BYTES + 16;  // bytes per strip row (pad keeps 16-byte stores conflict-free)
+constexpr int UM_ROWPIECE_BYTES = 128;                // bytes of an output row staged per flush (64 x 16-bit, 32 x fp32)
+constexpr int UM_STRIP_PITCH = UM_ROWPIECE_BYTES + 20;  // bytes per strip row: 37 words, odd, so lanes on one column hit 32 banks
 constexpr int UM_STRIP_BYTES = 32 * UM_STRIP_PITCH;   // per epilogue warp
-constexpr int UM_XCH_BYTES = 2 * 4 * 128 * 4;  // row statistics exchanged between the two halves, double-buffered
-constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + UM_EPI_WARPS * UM_STRIP_BYTES + UM_XCH_BYTES + 256 + 1024;
+constexpr int UM_XCH_BYTES = 2 * 2 * UM_SPLIT * 128 * 4;  // row statistics exchanged between the two halves, double-buffered
+constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + UM_EPI_WARPS * UM_STRIP_BYTES + UM_XCH_BYTES + 256;
 constexpr uint32_t UM_SPIN_LIMIT = 6u << 20;
 static_assert(UM_SMEM_BYTES <= 227 * 1024, "shared memory budget");
 static_assert(UM_STAGES <= 4, "barrier slots");
@@ -167,69 +169,86 @@ __device__ __forceinline__ bool next_work(const BlkUmmaParams& p, uint32_t w, Wo
 }
 
 // Stage 32 consecutive columns of this thread's row (strip row = lane) at column offset `sub` * 32 of the
-// current row piece.  The row is written `shift` bytes into its strip row, where shift is the row's byte
-// offset modulo 16 in the output: the strip then mirrors global memory modulo 16 bytes and every row can be
-// copied out with aligned 16-byte vectors.  `carry` holds the last word of the previous call of this piece.
+// current row piece.  The strip pitch is an odd number of words (37), so the 32 lanes of a store hit 32
+// different banks.
 template <typename Tag, bool OUT32>
-__device__ __forceinline__ void emit32(const float (&v)[32], unsigned char* strip, int sub, int lane, int shift,
-                                       uint32_t& carry) {
-    const uint32_t base = blk_smem_u32(strip) + lane * UM_STRIP_PITCH + (shift & ~3) + sub * (UM_PIECE * (OUT32 ? 4 : 2));
+__device__ __forceinline__ void emit32(const float (&v)[32], unsigned char* strip, int sub, int lane) {
+    const uint32_t base = blk_smem_u32(strip) + lane * UM_STRIP_PITCH + sub * (UM_PIECE * (OUT32 ? 4 : 2));
     if (OUT32) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) blk_sts_f32(base + 4 * i, v[i]);
     } else {
-        const int sb = (shift & 2) * 8;  // 0 or 16 bits: odd element offset of the row
-        uint32_t prev = carry;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const uint32_t w = BlkCvt<Tag>::pack2(v[2 * i], v[2 * i + 1]);
-            blk_sts_b32(base + 4 * i, __funnelshift_l(prev, w, sb));
-            prev = w;
-        }
-        blk_sts_b32(base + 64, __funnelshift_l(prev, 0u, sb));  // spill-over half word (rewritten by the next call)
-        carry = prev;
+        for (int i = 0; i < 16; ++i) blk_sts_b32(base + 4 * i, BlkCvt<Tag>::pack2(v[2 * i], v[2 * i + 1]));
     }
 }
 
-// Strip -> global for the warp's 32 rows x `ncols` columns starting at column col0: two rows per pass, half a
-// warp on consecutive 16-byte vectors of each (the strip is laid out so that they are aligned in global
-// memory too); only the ragged first and last vector of a row piece go out as single elements.
+// Predicated global stores as single instructions (no branch around them).
+__device__ __forceinline__ void stg_v4_if(void* p, const uint4& v, bool ok) {
+    asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %5, 0;\n @q st.global.v4.b32 [%0], {%1, %2, %3, %4};\n}\n" ::"l"(p),
+                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"((int)ok)
+                 : "memory");
+}
+__device__ __forceinline__ void stg_b16_if(void* p, uint16_t v, bool ok) {
+    asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %2, 0;\n @q st.global.b16 [%0], %1;\n}\n" ::"l"(p), "h"(v), "r"((int)ok)
+                 : "memory");
+}
+__device__ __forceinline__ void stg_b32_if(void* p, uint32_t v, bool ok) {
+    asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %2, 0;\n @q st.global.b32 [%0], %1;\n}\n" ::"l"(p), "r"(v), "r"((int)ok)
+                 : "memory");
+}
+
+// Strip -> global for the warp's 32 rows x `ncols` columns starting at column col0.  Four rows per pass,
+// eight lanes per row; lane hl owns the 16-byte vector hl of the row piece *as aligned in global memory*.
+// A row piece starts at an arbitrary 2-byte (4-byte for fp32) offset sh inside its first vector, so the
+// lane gathers its 16 bytes from the strip as five words and funnel-shifts them into place; only the
+// ragged first and last vector of a row piece go out as single elements, one per lane.  Branch-free.
 template <bool OUT32>
 __device__ __forceinline__ void flush_piece(const BlkUmmaParams& p, unsigned char* strip, int64_t cbase, int row0,
                                             int M, int N, int col0, int ncols, int lane) {
     constexpr int ES = OUT32 ? 4 : 2;
+    constexpr int LPR = UM_ROWPIECE_BYTES / 16;  // lanes (vectors) per row
+    constexpr int RPP = 32 / LPR;                // rows per pass
     __syncwarp();
-    unsigned char* C = reinterpret_cast<unsigned char*>(p.C);
-    const int hl = lane & 15, rsel = lane >> 4;
+    const int hl = lane % LPR, rsel = lane / LPR;
     const int nbytes = ncols * ES;
-#pragma unroll 2
-    for (int r = rsel; r < 32; r += 2) {
-        const int row = row0 + r;
-        if (row >= M) continue;
-        const int64_t b0 = (cbase + (int64_t)row * N + col0) * ES;  // byte offset of the row piece in the output
+    const int eoff = ES * hl;  // byte of this lane's edge elements inside the first / last vector
+    int64_t b0 = (cbase + (int64_t)(row0 + rsel) * N + col0) * ES;  // byte offset of this lane's row piece
+    const int64_t bstep = (int64_t)RPP * N * ES;
+    const unsigned char* src = strip + rsel * UM_STRIP_PITCH;  // byte 0 of src <-> byte b0 of the output
+    unsigned char* C = reinterpret_cast<unsigned char*>(p.C);
+#pragma unroll 4
+    for (int r = rsel; r < 32; r += RPP, b0 += bstep, src += RPP * UM_STRIP_PITCH) {
+        const bool row_ok = row0 + r < M;
         const int sh = (int)(b0 & 15);
-        const unsigned char* src = strip + r * UM_STRIP_PITCH;  // byte sh of src <-> byte b0 of the output
-        unsigned char* dst = C + (b0 - sh);                     // 16-byte aligned
-        const int end = sh + nbytes;
-        // full vectors [16 j, 16 j + 16) inside [sh, end): lane hl takes j = hl, lane 0 also j = 16
-        {
-            const int lo = 16 * hl;
-            if (lo >= sh && lo + 16 <= end)
-                *reinterpret_cast<uint4*>(dst + lo) = *reinterpret_cast<const uint4*>(src + lo);
-            if (hl == 0 && 272 <= end)
-                *reinterpret_cast<uint4*>(dst + 256) = *reinterpret_cast<const uint4*>(src + 256);
-        }
-        // the ragged first and last vector, one element per lane: lanes 0-7 the first, lanes 8-15 the last
-        {
-            const int tail = end & ~15;
-            const bool is_tail = hl >= 8;
-            const int b = (is_tail ? tail : 0) + ES * (hl & 7);
-            const bool first_full = sh == 0 && end >= 16;
-            const bool ok = (hl & 7) * ES < 16 && b >= sh && b < end && (is_tail ? tail != 0 : !first_full);
-            if (ok) {
-                if (OUT32) *reinterpret_cast<float*>(dst + b) = *reinterpret_cast<const float*>(src + b);
-                else *reinterpret_cast<uint16_t*>(dst + b) = *reinterpret_cast<const uint16_t*>(src + b);
-            }
+        unsigned char* dst = C + (b0 - sh);  // 16-byte aligned
+        const int end = sh + nbytes;         // the row piece is bytes [sh, end) counted from dst
+        // vector [16 hl, 16 hl + 16) if it lies inside [sh, end): strip bytes [x, x + 16), x = 16 hl - sh
+        const int lo = 16 * hl, x = lo - sh;
+        const int xw = x > 0 ? (x & ~3) : 0;
+        const int sb = (x & 2) * 8;
+        const uint32_t* wp = reinterpret_cast<const uint32_t*>(src + xw);
+        const uint32_t w0 = wp[0], w1 = wp[1], w2 = wp[2], w3 = wp[3], w4 = wp[4];
+        uint4 vec;
+        vec.x = __funnelshift_r(w0, w1, sb);
+        vec.y = __funnelshift_r(w1, w2, sb);
+        vec.z = __funnelshift_r(w2, w3, sb);
+        vec.w = __funnelshift_r(w3, w4, sb);
+        stg_v4_if(dst + lo, vec, row_ok && lo >= sh && lo + 16 <= end);
+        // ragged first and last vector: lane hl takes element hl of each
+        const int tail = end & ~15;
+        const bool in_vec = eoff < 16;
+        const bool first_full = sh == 0 && end >= 16;
+        const bool ok_h = row_ok && in_vec && !first_full && eoff >= sh && eoff < end;
+        const int bt = tail + eoff;
+        const bool ok_t = row_ok && in_vec && tail != 0 && bt < end;
+        const int sh_h = ok_h ? eoff - sh : 0, sh_t = ok_t ? bt - sh : 0;  // strip bytes of the two elements
+        if (OUT32) {
+            stg_b32_if(dst + eoff, *reinterpret_cast<const uint32_t*>(src + sh_h), ok_h);
+            stg_b32_if(dst + bt, *reinterpret_cast<const uint32_t*>(src + sh_t), ok_t);
+        } else {
+            stg_b16_if(dst + eoff, *reinterpret_cast<const uint16_t*>(src + sh_h), ok_h);
+            stg_b16_if(dst + bt, *reinterpret_cast<const uint16_t*>(src + sh_t), ok_t);
         }
     }
     __syncwarp();
@@ -239,9 +258,12 @@ template <typename Tag, bool OUT32>
 __global__ void __launch_bounds__(UM_THREADS, 1)
 blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap mapA,
                      const __grid_constant__ CUtensorMap mapB) {
-    extern __shared__ unsigned char um_smem_raw[];
-    // 1024-byte aligned base for the swizzled tiles
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(um_smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) unsigned char um_smem_raw[];  // the swizzled tiles need a 1024-byte aligned base
+    unsigned char* smem = um_smem_raw;
+    if (blk_smem_u32(smem) & 1023u) {  // cannot happen with the alignment above; checked because the swizzle relies on it
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, 9);
+        return;
+    }
     unsigned char* strips = smem + UM_STAGES * UM_STAGE_BYTES;
     float* xch = reinterpret_cast<float*>(strips + UM_EPI_WARPS * UM_STRIP_BYTES);
     uint64_t* bars = reinterpret_cast<uint64_t*>(strips + UM_EPI_WARPS * UM_STRIP_BYTES + UM_XCH_BYTES);
@@ -335,10 +357,10 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..9 ----------------
-        // lane quarter q = warp % 4 (the 32 accumulator lanes a warp may read); the two warps of a quarter
+        // ---------------- epilogue: warps 2..17 ----------------
+        // lane quarter q = warp % 4 (the 32 accumulator lanes a warp may read); the UM_SPLIT warps of a quarter
         // split the row's 128-column blocks by parity (half h) and exchange their partial row statistics.
-        const int q = warp & 3, h = (warp - 2) >> 2;
+        const int q = warp & 3, h = (warp - 2) >> 2;  // h in [0, UM_SPLIT)
         unsigned char* strip = strips + (warp - 2) * UM_STRIP_BYTES;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         const int myrow = q * 32 + lane;
@@ -349,13 +371,13 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
         const float sl = softmax ? fabsf(p.scale) * BLK_LOG2E : p.scale;  // a negative softmax scale is applied by
                                                                           // the MMA (negated A), see instr_desc
         constexpr int RP = UM_ROWPIECE_BYTES / (OUT32 ? 4 : 2);  // columns per staged row piece
-        constexpr int CB = 128;                                  // columns per block owned by one half
-        // Rendezvous of the two warps of a quarter (after each has published its row statistics): a shared
+        constexpr int CB = UM_CB;                                // columns of a chunk owned by this warp
+        // Rendezvous of the warps of a quarter (after each has published its row statistics): a shared
         // counter and a bounded spin, so that a warp whose partner gave up cannot wait for ever.
         volatile uint32_t* pair_cnt = reinterpret_cast<volatile uint32_t*>(bars + 14) + q;
         uint32_t pair_target = 0;
         auto pair_sync = [&]() -> bool {
-            pair_target += 2;
+            pair_target += UM_SPLIT;
             __threadfence_block();
             __syncwarp();
             if (lane == 0) atomicAdd(const_cast<uint32_t*>(pair_cnt), 1u);
@@ -379,14 +401,11 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
             float v[32];
             for (int c0 = c_lo; c0 < c_hi; c0 += RP) {
                 const int pc = min(RP, c_hi - c0);
-                // this thread's row of the piece starts at this byte offset modulo 16 in the output
-                const int shift = (int)(((cbase + (int64_t)myrow * N + c0) * (OUT32 ? 4 : 2)) & 15);
-                uint32_t carry = 0;
                 for (int c = 0; c < pc; c += UM_PIECE) {
                     tc_ld32(lane_addr + tcol(c0 + c), r);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = xform(__uint_as_float(r[i]));
-                    emit32<Tag, OUT32>(v, strip, c / UM_PIECE, lane, shift, carry);
+                    emit32<Tag, OUT32>(v, strip, c / UM_PIECE, lane);
                 }
                 flush_piece<OUT32>(p, strip, cbase, q * 32, M, N, c0, pc, lane);
             }
@@ -395,7 +414,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
             const int M = wk.it.M - wk.it.tm * UM_BM;  // rows of the segment from this block on
             const int N = wk.it.N;
             const int64_t cbase = (int64_t)wk.head * p.Dout + wk.it.offC + (int64_t)wk.it.tm * UM_BM * N;
-            volatile float* xm = xch + (seq & 1) * 512;  // [half][row] maxima, then [2 + half][row] sums
+            volatile float* xm = xch + (seq & 1) * (2 * UM_SPLIT * 128);  // [part][row] maxima, then [UM_SPLIT + part][row] sums
             if (!softmax) {
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
                     const int buf = slot & 1;
@@ -423,7 +442,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 uint32_t r[32];
                 // pass 1: maximum over this half's blocks
                 float mx = -INFINITY;
-                for (int b0 = h * CB; b0 < N; b0 += 2 * CB) {
+                for (int b0 = h * CB; b0 < N; b0 += UM_BN) {
                     const int bend = min(b0 + CB, N);
                     for (int c = b0; c < bend; c += UM_PIECE) {
                         tc_ld32(lane_addr + tcol(c), r);
@@ -440,11 +459,12 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 }
                 xm[h * 128 + myrow] = mx;
                 if (!pair_sync()) { ok = false; break; }
-                mx = fmaxf(mx, xm[(h ^ 1) * 128 + myrow]);
+#pragma unroll
+                for (int o = 0; o < UM_SPLIT; ++o) mx = fmaxf(mx, xm[o * 128 + myrow]);
                 const float nm = -mx * sl;
                 // pass 2: exponentials back into tensor memory, partial sum
                 float s4[4] = {0.f, 0.f, 0.f, 0.f};
-                for (int b0 = h * CB; b0 < N; b0 += 2 * CB) {
+                for (int b0 = h * CB; b0 < N; b0 += UM_BN) {
                     const int bend = min(b0 + CB, N);
                     for (int c = b0; c < bend; c += UM_PIECE) {
                         tc_ld32(lane_addr + tcol(c), r);
@@ -460,12 +480,14 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 }
                 tc_wait_st();
                 float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
-                xm[(2 + h) * 128 + myrow] = sum;
+                xm[(UM_SPLIT + h) * 128 + myrow] = sum;
                 if (!pair_sync()) { ok = false; break; }
-                sum += xm[(2 + (h ^ 1)) * 128 + myrow];
+                sum = 0.f;
+#pragma unroll
+                for (int o = 0; o < UM_SPLIT; ++o) sum += xm[(UM_SPLIT + o) * 128 + myrow];
                 const float inv = __frcp_rn(sum);
                 // pass 3: normalise and store
-                for (int b0 = h * CB; b0 < N; b0 += 2 * CB)
+                for (int b0 = h * CB; b0 < N; b0 += UM_BN)
                     store_cols(b0, min(b0 + CB, N), tcol, [&](float x) { return x * inv; }, cbase, M, N);
                 tc_fence_before();
                 __syncwarp();
@@ -508,13 +530,18 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 }
                 if (!ok) break;
                 xm[h * 128 + myrow] = mx;
-                xm[(2 + h) * 128 + myrow] = sum;
+                xm[(UM_SPLIT + h) * 128 + myrow] = sum;
                 if (!pair_sync()) break;
                 {
-                    const float m2 = xm[(h ^ 1) * 128 + myrow], l2 = xm[(2 + (h ^ 1)) * 128 + myrow];
-                    const float m = fmaxf(mx, m2);
-                    sum = sum * blk_exp2((mx - m) * sl) + l2 * blk_exp2((m2 - m) * sl);
+                    float m = -INFINITY;
+#pragma unroll
+                    for (int o = 0; o < UM_SPLIT; ++o) m = fmaxf(m, xm[o * 128 + myrow]);
+                    float l = 0.f;
+#pragma unroll
+                    for (int o = 0; o < UM_SPLIT; ++o)
+                        l += xm[(UM_SPLIT + o) * 128 + myrow] * blk_exp2((xm[o * 128 + myrow] - m) * sl);
                     mx = m;
+                    sum = l;
                 }
                 const float nm = -mx * sl, inv = __frcp_rn(sum);
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
