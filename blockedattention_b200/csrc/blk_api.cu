@@ -61,6 +61,8 @@ int upload_plan(blk_plan* p) {
             p->num_sms = sms;
     }
     if ((rc = upload(p->umma_items, &p->d_umma_items, "upload umma items")) != BLK_OK) return rc;
+    if ((rc = upload(p->packs, &p->d_packs, "upload packs")) != BLK_OK) return rc;
+    if ((rc = upload(p->pack_blocks, &p->d_pack_blocks, "upload pack blocks")) != BLK_OK) return rc;
     if ((rc = upload(p->smx_chunks, &p->d_smx_chunks, "upload softmax chunks")) != BLK_OK) return rc;
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&p->d_status), 2 * sizeof(int));
     if (e != cudaSuccess) return cuda_fail("allocate status word", e);
@@ -147,7 +149,8 @@ extern "C" int blk_gemm_plan_create(blk_plan_t** plan, const int64_t* M, const i
                           grid_ok((int64_t)p->simt_items.size(), H, "gemm plan") &&
                           grid_ok((int64_t)p->smx_chunks.size(), H, "gemm plan") &&
                           grid_ok((int64_t)small_count(p), H, "gemm plan") &&
-                          grid_ok((int64_t)p->umma_items.size(), H, "gemm plan")))
+                          grid_ok((int64_t)p->umma_items.size(), H, "gemm plan") &&
+                          grid_ok((int64_t)p->packs.size(), H, "gemm plan")))
         rc = BLK_ERR_UNSUPPORTED;
     if (rc == BLK_OK) rc = upload_plan(p);
     if (rc != BLK_OK) {
@@ -211,6 +214,8 @@ extern "C" void blk_plan_destroy(blk_plan_t* p) {
         cudaFree(p->d_simt_items);
         for (int b = 0; b < BLK_SMALL_BUCKETS; ++b) cudaFree(p->d_small_items[b]);
         cudaFree(p->d_umma_items);
+        cudaFree(p->d_packs);
+        cudaFree(p->d_pack_blocks);
         cudaFree(p->d_smx_chunks);
         cudaFree(p->d_status);
     }
@@ -242,6 +247,7 @@ extern "C" int blk_plan_offsets(const blk_plan_t* p, int64_t* a1, int64_t* a2, i
 
 static int launches_per_run(const blk_plan* p) {
     int n = (!p->tile_items.empty()) + (!p->simt_items.empty()) + (!p->umma_items.empty()) + (!p->smx_chunks.empty());
+    if (p->small_pipe) return n + 1;
     for (const auto& v : p->small_items) n += !v.empty();
     return n;
 }
@@ -258,7 +264,7 @@ extern "C" int blk_plan_summary(const blk_plan_t* p, int64_t counts[8]) {
     counts[4] = (int64_t)p->smx_chunks.size();
     counts[5] = p->H > 0 ? launches_per_run(p) : 0;
     counts[6] = (int64_t)p->simt_items.size();
-    counts[7] = 0;
+    counts[7] = (int64_t)p->packs.size();
     return BLK_OK;
 }
 
@@ -339,7 +345,23 @@ extern "C" int blk_gemm_run(const blk_plan_t* p, const void* mat1, const void* m
             if ((e = blk_launch_softmax(xp, BLK_F32, st)) != cudaSuccess) return cuda_fail("softmax launch", e);
         }
     }
-    for (int b = 0; b < BLK_SMALL_BUCKETS; ++b) {
+    if (p->small_pipe) {
+        BlkPackParams pp{};
+        pp.A = reinterpret_cast<const uint16_t*>(mat1);
+        pp.B = reinterpret_cast<const uint16_t*>(mat2);
+        pp.C = out;
+        pp.packs = p->d_packs;
+        pp.blocks = p->d_pack_blocks;
+        pp.Dm1 = p->Dm1; pp.Dm2 = p->Dm2; pp.Dout = p->Dout;
+        pp.num_packs = (int)p->packs.size();
+        pp.H = (int)p->H;
+        pp.epi = p->epi;
+        pp.scale = scale;
+        pp.status = p->d_status;
+        if ((e = blk_launch_scores_pipe(pp, p->dtype_in, p->num_sms, st)) != cudaSuccess)
+            return cuda_fail("pipelined small-segment launch", e);
+    }
+    for (int b = 0; b < BLK_SMALL_BUCKETS && !p->small_pipe; ++b) {
         if (p->small_items[b].empty()) continue;
         BlkSmallParams mp{};
         mp.A = reinterpret_cast<const uint16_t*>(mat1);

@@ -291,6 +291,7 @@ int blk_build_gemm_schedule(blk_plan* p) {
     }
     p->segs.resize(S);
     p->flops = p->bytes = 0;
+    std::vector<int64_t> small_segs;  // segments of the small bin, in batch order
     for (int64_t s = 0; s < S; ++s) {
         const int64_t m = p->M[s], n = p->N[s], k = p->K[s];
         BlkSeg& sd = p->segs[s];
@@ -322,6 +323,7 @@ int blk_build_gemm_schedule(blk_plan* p) {
                               (p->small_K == 0 || p->small_K == (int)k);
         if (small_ok) {
             p->small_K = (int)k;
+            small_segs.push_back(s);
             p->small_items[n <= 32 ? 0 : 1].push_back(
                 BlkSmallItem{sd.offA, sd.offB, sd.offC, (int32_t)m, (int32_t)n});
             continue;
@@ -347,6 +349,48 @@ int blk_build_gemm_schedule(blk_plan* p) {
     std::stable_sort(p->umma_items.begin(), p->umma_items.end(), [](const BlkUmmaItem& a, const BlkUmmaItem& b) {
         return (int64_t)std::min(a.M - a.tm * BLK_UMMA_BM, BLK_UMMA_BM) * a.N > (int64_t)std::min(b.M - b.tm * BLK_UMMA_BM, BLK_UMMA_BM) * b.N;
     });
+    // K = 64 with 16-bit output: the small segments run on the pipelined kernel, grouped into packs of
+    // consecutive segments whose operands are contiguous in memory (one bulk copy per operand per pack).
+    p->small_pipe = 0;
+    if (p->small_K == 64 && p->dtype_out != BLK_F32 && blk_env_flag("BLK_ENABLE_PIPE") && !small_segs.empty()) {
+        p->small_pipe = 1;
+        struct Tmp { BlkPack pk; std::vector<BlkPackBlock> blocks; double cost; };
+        std::vector<Tmp> tmp;
+        for (size_t q = 0; q < small_segs.size(); ++q) {
+            const BlkSeg& sd = p->segs[small_segs[q]];
+            bool extend = false;
+            if (!tmp.empty()) {
+                const Tmp& t = tmp.back();
+                extend = t.pk.offA + (int64_t)t.pk.rowsA * 64 == sd.offA && t.pk.offB + (int64_t)t.pk.rowsB * 64 == sd.offB &&
+                         t.pk.rowsA + sd.M <= BLK_PACK_ROWS && t.pk.rowsB + sd.N <= BLK_PACK_ROWS &&
+                         t.pk.nblocks < BLK_PACK_BLOCKS;
+            }
+            if (!extend) {
+                Tmp t;
+                t.pk = BlkPack{sd.offA, sd.offB, 0, 0, 0, 0};
+                t.cost = 0;
+                tmp.push_back(t);
+            }
+            Tmp& t = tmp.back();
+            t.blocks.push_back(BlkPackBlock{sd.offC, t.pk.rowsA, t.pk.rowsB, sd.M, sd.N, 0, 0});
+            t.pk.rowsA += sd.M;
+            t.pk.rowsB += sd.N;
+            t.pk.nblocks += 1;
+            t.cost += (double)sd.M * sd.N + (double)(sd.M + sd.N) * 64;
+        }
+        // heaviest packs first: persistent CTAs take packs with a fixed stride
+        std::stable_sort(tmp.begin(), tmp.end(), [](const Tmp& a, const Tmp& b) { return a.cost > b.cost; });
+        for (Tmp& t : tmp) {
+            t.pk.first_block = (int32_t)p->pack_blocks.size();
+            for (BlkPackBlock& bl : t.blocks) {
+                bl.nblocks = t.pk.nblocks;
+                p->pack_blocks.push_back(bl);
+            }
+            p->packs.push_back(t.pk);
+        }
+        // the block table is read in 16-record pieces: keep 16 records of slack behind the last pack
+        for (int q = 0; q < BLK_PACK_BLOCKS; ++q) p->pack_blocks.push_back(BlkPackBlock{0, 0, 0, 0, 0, 0, 0});
+    }
     // Persistent warps take small items in list order with a fixed stride: heaviest first evens the tails.
     for (auto& v : p->small_items)
         std::stable_sort(v.begin(), v.end(), [](const BlkSmallItem& a, const BlkSmallItem& b) {

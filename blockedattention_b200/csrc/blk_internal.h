@@ -39,6 +39,24 @@ struct BlkSmallItem {
 };
 static_assert(sizeof(BlkSmallItem) == 32, "BlkSmallItem layout");
 
+// Pipelined small-segment kernel: a pack is a run of consecutive small segments whose first operands, and
+// whose second operands, are each one contiguous piece of a head strip (<= BLK_PACK_ROWS rows, <= 16 segments),
+// fetched by one bulk copy each; its blocks are the segments.
+struct BlkPack {
+    int64_t offA, offB;  // element offsets of the run inside the head strips
+    int32_t rowsA, rowsB;
+    int32_t first_block, nblocks;
+};
+static_assert(sizeof(BlkPack) == 32, "BlkPack layout");
+struct BlkPackBlock {
+    int64_t offC;        // element offset of the block's output inside a head strip
+    int32_t rowA, rowB;  // first row of the block inside the pack's operand runs
+    int32_t M, N;
+    int32_t nblocks;     // blocks in this pack (repeated in every record)
+    int32_t pad;
+};
+static_assert(sizeof(BlkPackBlock) == 32, "BlkPackBlock layout");
+
 // One CTA of the softmax kernel: `rows` consecutive rows of `cols` elements
 // starting at element `off` of the head strip.  rows*cols fits the CTA's
 // shared-memory window, or rows == 1 for a row longer than the window.
@@ -69,6 +87,8 @@ constexpr int BLK_SMALL_MAXN = 64;
 constexpr int BLK_SMALL_WARPS = 4;
 constexpr int BLK_SMALL_MAXM = 64;
 constexpr int BLK_SMALL_BUCKETS = 2;  // N <= 32, N <= 64
+constexpr int BLK_PACK_ROWS = 192;    // rows of each operand a pack may hold
+constexpr int BLK_PACK_BLOCKS = 16;   // segments a pack may hold
 constexpr int BLK_SMX_WINDOW_BYTES = 16384;
 constexpr int BLK_UMMA_BM = 128;
 constexpr int BLK_NOALLOC_MAX_CHUNKS = 65536;  // entries of the built-in chunk table of blk_softmax_noalloc
@@ -90,6 +110,11 @@ struct blk_plan {
     std::vector<BlkSmxChunk> smx_chunks;    // softmax kernel (also second pass of fp32 scores)
     int umma_K = 0;                         // uniform K of the tcgen05 bin
     int small_K = 0;                        // uniform K of the small bin
+    int small_pipe = 0;                     // 1: the small segments run as packs on the pipelined kernel
+    std::vector<BlkPack> packs;
+    std::vector<BlkPackBlock> pack_blocks;
+    BlkPack* d_packs = nullptr;
+    BlkPackBlock* d_pack_blocks = nullptr;
 
     // device copies
     BlkSeg* d_segs = nullptr;

@@ -59,6 +59,20 @@ struct BlkUmmaParams {
     int* status;
 };
 
+struct BlkPackParams {
+    const uint16_t* A;
+    const uint16_t* B;
+    void* C;
+    const BlkPack* packs;
+    const BlkPackBlock* blocks;
+    int64_t Dm1, Dm2, Dout;
+    int num_packs;
+    int H;
+    int epi;
+    float scale;
+    int* status;
+};
+
 struct BlkSmxParams {
     const void* src;
     void* dst;
@@ -75,4 +89,5 @@ cudaError_t blk_launch_scores_small(const BlkSmallParams& p, int dtype_in, int K
                                     cudaStream_t st);
 cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p, const void* A, const void* B, int64_t Dm1, int64_t Dm2,
                                  int sms, cudaStream_t st);
+cudaError_t blk_launch_scores_pipe(const BlkPackParams& p, int dtype_in, int sms, cudaStream_t st);
 cudaError_t blk_launch_softmax(const BlkSmxParams& p, int dtype, cudaStream_t st);

@@ -64,7 +64,7 @@ class _Plan:
     def summary(self) -> dict:
         arr = (C.c_int64 * 8)()
         L.check(L.lib.blk_plan_summary(self._h, arr))
-        keys = ["segments", "small_items", "tile_items", "umma_items", "softmax_chunks", "launches", "simt_items"]
+        keys = ["segments", "small_items", "tile_items", "umma_items", "softmax_chunks", "launches", "simt_items", "packs"]
         return {k: int(arr[i]) for i, k in enumerate(keys)}
 
     @property

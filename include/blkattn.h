@@ -170,7 +170,8 @@ BLK_API int blk_plan_offsets(const blk_plan_t* plan, int64_t* accum1, int64_t* a
 /* Schedule summary: counts[0] = segments, [1] = work items of the packed
  * small-segment kernel, [2] = tiles of the staged mma.sync kernel, [3] = tiles
  * of the tcgen05 kernel, [4] = softmax chunks, [5] = kernels launched per
- * run, [6] = tiles of the fp32 SIMT kernel, [7] = reserved. */
+ * run, [6] = tiles of the fp32 SIMT kernel, [7] = packs of the pipelined
+ * small-segment kernel (0 unless it was enabled). */
 BLK_API int blk_plan_summary(const blk_plan_t* plan, int64_t counts[8]);
 
 /* Algorithmic work of one run over all heads: flops = 2 H sum(M N K) (0 for a
