@@ -352,18 +352,19 @@ int blk_build_gemm_schedule(blk_plan* p) {
     // K = 64 with 16-bit output: the small segments run on the pipelined kernel, grouped into packs of
     // consecutive segments whose operands are contiguous in memory (one bulk copy per operand per pack).
     p->small_pipe = 0;
-    if (p->small_K == 64 && p->dtype_out != BLK_F32 && blk_env_flag("BLK_ENABLE_PIPE") && !small_segs.empty()) {
+    if (p->small_K == 64 && p->dtype_out != BLK_F32 && !blk_env_flag("BLK_DISABLE_PIPE") && !small_segs.empty()) {
         p->small_pipe = 1;
         struct Tmp { BlkPack pk; std::vector<BlkPackBlock> blocks; double cost; };
         std::vector<Tmp> tmp;
         for (size_t q = 0; q < small_segs.size(); ++q) {
             const BlkSeg& sd = p->segs[small_segs[q]];
+            const int32_t mblocks = (sd.M + 15) / 16;  // one block per 16 first-operand rows of the segment
             bool extend = false;
             if (!tmp.empty()) {
                 const Tmp& t = tmp.back();
                 extend = t.pk.offA + (int64_t)t.pk.rowsA * 64 == sd.offA && t.pk.offB + (int64_t)t.pk.rowsB * 64 == sd.offB &&
                          t.pk.rowsA + sd.M <= BLK_PACK_ROWS && t.pk.rowsB + sd.N <= BLK_PACK_ROWS &&
-                         t.pk.nblocks < BLK_PACK_BLOCKS;
+                         t.pk.nblocks + mblocks <= BLK_PACK_BLOCKS;
             }
             if (!extend) {
                 Tmp t;
@@ -372,16 +373,20 @@ int blk_build_gemm_schedule(blk_plan* p) {
                 tmp.push_back(t);
             }
             Tmp& t = tmp.back();
-            t.blocks.push_back(BlkPackBlock{sd.offC, t.pk.rowsA, t.pk.rowsB, sd.M, sd.N, 0, 0});
+            for (int32_t mb = 0; mb < mblocks; ++mb)
+                t.blocks.push_back(BlkPackBlock{sd.offC + (int64_t)mb * 16 * sd.N, t.pk.rowsA + 16 * mb, t.pk.rowsB,
+                                                std::min<int32_t>(16, sd.M - 16 * mb), sd.N, 0, 0});
             t.pk.rowsA += sd.M;
             t.pk.rowsB += sd.N;
-            t.pk.nblocks += 1;
+            t.pk.nblocks += mblocks;
             t.cost += (double)sd.M * sd.N + (double)(sd.M + sd.N) * 64;
         }
         // heaviest packs first: persistent CTAs take packs with a fixed stride
         std::stable_sort(tmp.begin(), tmp.end(), [](const Tmp& a, const Tmp& b) { return a.cost > b.cost; });
         for (Tmp& t : tmp) {
             t.pk.first_block = (int32_t)p->pack_blocks.size();
+            // consumers claim blocks in table order: widest first
+            std::stable_sort(t.blocks.begin(), t.blocks.end(), [](const BlkPackBlock& a, const BlkPackBlock& b) { return a.N > b.N; });
             for (BlkPackBlock& bl : t.blocks) {
                 bl.nblocks = t.pk.nblocks;
                 p->pack_blocks.push_back(bl);

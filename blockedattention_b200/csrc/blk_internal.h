@@ -40,8 +40,8 @@ struct BlkSmallItem {
 static_assert(sizeof(BlkSmallItem) == 32, "BlkSmallItem layout");
 
 // Pipelined small-segment kernel: a pack is a run of consecutive small segments whose first operands, and
-// whose second operands, are each one contiguous piece of a head strip (<= BLK_PACK_ROWS rows, <= 16 segments),
-// fetched by one bulk copy each; its blocks are the segments.
+// whose second operands, are each one contiguous piece of a head strip (<= BLK_PACK_ROWS rows), fetched by one
+// bulk copy each; its blocks (<= BLK_PACK_BLOCKS) are the 16-row pieces of the segments' first operands.
 struct BlkPack {
     int64_t offA, offB;  // element offsets of the run inside the head strips
     int32_t rowsA, rowsB;

@@ -1,8 +1,9 @@
 // Pipelined packed small-segment kernel (K = 64, 16-bit output).
 //
-// Small segments are grouped on the host into packs: runs of up to 16
-// consecutive segments whose first operands -- and whose second operands -- are
-// one contiguous piece of a head strip of at most 192 rows (24 KB).  One
+// Small segments are grouped on the host into packs: runs of consecutive
+// segments whose first operands -- and whose second operands -- are one
+// contiguous piece of a head strip of at most 192 rows (24 KB), cut into at
+// most 16 blocks of up to 16 first-operand rows of one segment each.  One
 // persistent CTA per SM walks its share of the cost-sorted (pack, head) list:
 //   warp 0      producer: one lane brings each pack into a 4-slot shared-memory
 //               ring with three bulk asynchronous copies (first operands,
@@ -10,20 +11,19 @@
 //               the slot's mbarrier -- few, large copies keep the copy engine
 //               at memory speed, and the latency is paid by the ring instead of
 //               by the registers and occupancy of the arithmetic warps;
-//   warps 1-16  consumers: each takes one block (segment) of a pack, computes it
-//               as the register-fed small kernel does (k-permuted 128-bit
-//               fragment reads, here from shared memory; mma.sync.m16n8k16;
-//               softmax in registers; exact tile-count specialisation), lays
-//               the result out over the block's own first-operand rows (dead
+//   warps 1-16  consumers: each takes one block of a pack, computes it as the
+//               register-fed small kernel does (k-permuted 128-bit fragment
+//               reads, here from shared memory; mma.sync.m16n8k16; softmax in
+//               registers; one copy of the tile code for every shape), lays the
+//               result out over the block's own first-operand rows (dead
 //               once their fragments are in registers), and copies it to global
 //               memory as aligned 16-byte vectors, re-aligning on the fly.
-// Every consumer arrives on every slot's "empty" barrier, so a slot is reused
-// only when all sixteen are done with it; every wait is bounded and reports
-// through the status word.
+// The consumers claim a pack's blocks through a per-slot counter, heaviest block
+// first, so a warp that finishes early takes more.  Every consumer arrives on
+// every slot's "empty" barrier, so a slot is reused only when all sixteen are
+// done with it; every wait is bounded and reports through the status word.
 //
 // Same arithmetic and the same upstream counterparts as blk_scores_small.cu.
-#include <cstdlib>
-
 #include "blk_device.cuh"
 #include "blk_kernels.h"
 
@@ -38,10 +38,14 @@ constexpr int P_OPER_BYTES = BLK_PACK_ROWS * ROWB;  // 24 KB per operand per slo
 constexpr int P_REC_BYTES = BLK_PACK_BLOCKS * (int)sizeof(BlkPackBlock);
 constexpr int P_SLOT_BYTES = 2 * P_OPER_BYTES + P_REC_BYTES;
 constexpr int P_SLOTS = 4;
-constexpr int P_SMEM_BYTES = P_SLOTS * P_SLOT_BYTES + 16 * P_SLOTS + 64;
-constexpr uint32_t P_SPIN_LIMIT = 6u << 20;
+constexpr int P_TAIL_PAD = 1024;  // second-operand rows are read up to 7 rows past a run's end
+constexpr int P_GROUPS = 2;        // consumer groups; unit u belongs to group u % P_GROUPS
+constexpr int P_GROUP_WARPS = P_CONSUMERS / P_GROUPS;
+constexpr int P_SCRATCH_BYTES = 128;  // target of staging stores that must not land
+constexpr int P_SMEM_BYTES = P_SLOTS * P_SLOT_BYTES + P_TAIL_PAD + 16 * P_SLOTS + 16 + 4 * P_SLOTS + P_SCRATCH_BYTES;
+static_assert(P_SLOTS % P_GROUPS == 0 && P_CONSUMERS % P_GROUPS == 0, "groups own whole slots");
+constexpr uint32_t P_SPIN_LIMIT = 1u << 22;
 static_assert(P_SMEM_BYTES <= 227 * 1024, "shared memory budget");
-static_assert(BLK_PACK_BLOCKS == P_CONSUMERS, "one consumer per block of a pack");
 
 __device__ __forceinline__ void pb_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
@@ -52,20 +56,21 @@ __device__ __forceinline__ void pb_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void pb_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool pb_test(uint32_t bar, uint32_t parity) {
+// One attempt: the hardware suspends the thread for a bounded, implementation-defined time while the phase is pending.
+__device__ __forceinline__ bool pb_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
-        "{\n .reg .pred q;\n mbarrier.test_wait.parity.shared::cta.b64 q, [%1], %2;\n selp.u32 %0, 1, 0, q;\n}\n"
+        "{\n .reg .pred q;\n mbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n selp.u32 %0, 1, 0, q;\n}\n"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
 }
+// Bounded wait: gives up after P_SPIN_LIMIT attempts (or when another role gave up), recording `code`.
 __device__ __forceinline__ bool pb_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
     for (uint32_t i = 0; i < P_SPIN_LIMIT; ++i) {
-        if (pb_test(bar, parity)) return true;
-        if (i > 64) __nanosleep(40);
-        if ((i & 255u) == 255u && *abort_flag) return false;
+        if (pb_try(bar, parity)) return true;
+        if ((i & 63u) == 63u && *abort_flag) return false;
     }
     *abort_flag = 1;
     atomicCAS(status, 0, code);
@@ -77,30 +82,12 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
-__device__ __forceinline__ uint4 lds16(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
+// Shared-memory stores by 32-bit address, and predicated global stores as single instructions.
+__device__ __forceinline__ void sts_b32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(addr), "r"(v) : "memory");
 }
-__device__ __forceinline__ uint32_t lds4(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint16_t lds2(uint32_t addr) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));
-    return v;
-}
-// Predicated stores as single instructions.
-__device__ __forceinline__ void sts_b32_if(uint32_t addr, uint32_t v, bool ok) {
-    asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %2, 0;\n @q st.shared.b32 [%0], %1;\n}\n" ::"r"(addr), "r"(v), "r"((int)ok)
-                 : "memory");
-}
-__device__ __forceinline__ void sts_b16_if(uint32_t addr, uint32_t v, bool ok) {
-    asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %2, 0;\n @q st.shared.b16 [%0], %1;\n}\n" ::"r"(addr), "h"((uint16_t)v),
-                 "r"((int)ok)
-                 : "memory");
+__device__ __forceinline__ void sts_b16(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.b16 [%0], %1;\n" ::"r"(addr), "h"((uint16_t)v) : "memory");
 }
 __device__ __forceinline__ void stg_v4_if(void* p, const uint4& v, bool ok) {
     asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %5, 0;\n @q st.global.v4.b32 [%0], {%1, %2, %3, %4};\n}\n" ::"l"(p),
@@ -112,152 +99,211 @@ __device__ __forceinline__ void stg_b16_if(void* p, uint16_t v, bool ok) {
                  : "memory");
 }
 
-// One block with exactly NT column tiles: operands at shared-window addresses sA / sB, result staged over the
-// block's own first-operand rows (M * N * 2 <= M * 128 bytes) and copied to the output at element cbase.
-template <typename Tag, int NT, bool SOFTMAX>
-__device__ __forceinline__ void pack_block(void* C, uint32_t sA, uint32_t sB, int64_t cbase, int M, int N, float sl,
-                                           bool flip, int lane) {
-    const int g = lane >> 2, t = lane & 3;
-    const bool pair_ok = (N & 1) == 0;  // staged rows start on 4-byte boundaries
+// Non-volatile mma wrappers: pure functions of their operands, so the compiler may interleave them with loads.
+template <typename Tag>
+__device__ __forceinline__ void pk_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1);
+template <>
+__device__ __forceinline__ void pk_mma<BlkHalfTag>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                   uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void pk_mma<BlkBf16Tag>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                   uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
-    uint4 a[2][PKC];
-    auto load_a = [&](int mb) {
+// First product of a tile: the accumulator input is the constant zero, so no registers are cleared beforehand.
+template <typename Tag>
+__device__ __forceinline__ void pk_mma0(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1);
+template <>
+__device__ __forceinline__ void pk_mma0<BlkHalfTag>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                    uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+template <>
+__device__ __forceinline__ void pk_mma0<BlkBf16Tag>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                    uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+// The arithmetic of one block with exactly NT column tiles: products, optional row softmax, and the staging
+// stores (rows g and g + 8 of the block at shared addresses s0a / s1a).  Columns 8 (NT - 1) + 2 t and + 1 of the
+// last tile exist when last0 / last1; stores that must not land go to `scratch`.
+template <typename Tag, int NT, bool SOFTMAX>
+__device__ __forceinline__ void pack_tiles(const uint32_t (&af)[2 * PKC][4], const unsigned char* lb, float sl, bool last0,
+                                           bool last1, bool pairs, uint32_t s0a, uint32_t s1a, uint32_t scratch) {
+    float acc[NT][4];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint32_t pa = sA + min(mb * 16 + g + 8 * h, M - 1) * ROWB + 16 * t;
-#pragma unroll
-            for (int c = 0; c < PKC; ++c) a[h][c] = lds16(pa + 64 * c);
-        }
-    };
-    load_a(0);
-    // rows of the second operand this lane reads (clamped past the end; their columns are masked below)
-    uint32_t pb[NT];
-#pragma unroll
-    for (int j = 0; j < NT; ++j) pb[j] = sB + min(8 * j + g, N - 1) * ROWB + 16 * t;
-    const bool last0 = 8 * (NT - 1) + 2 * t < N, last1 = 8 * (NT - 1) + 2 * t + 1 < N;
-    const uint32_t srow = sA + (g * N + 2 * t) * 2;
-    const int nmb = (M + 15) >> 4;
-    for (int mb = 0; mb < nmb; ++mb) {
-        uint32_t af[2 * PKC][4];
+    for (int j = 0; j < NT; ++j) {
 #pragma unroll
         for (int c = 0; c < PKC; ++c) {
-            af[2 * c][0] = a[0][c].x; af[2 * c][1] = a[1][c].x; af[2 * c][2] = a[0][c].y; af[2 * c][3] = a[1][c].y;
-            af[2 * c + 1][0] = a[0][c].z; af[2 * c + 1][1] = a[1][c].z;
-            af[2 * c + 1][2] = a[0][c].w; af[2 * c + 1][3] = a[1][c].w;
+            const uint4 b = *reinterpret_cast<const uint4*>(lb + j * 8 * ROWB + 64 * c);
+            if (c == 0)
+                pk_mma0<Tag>(acc[j], af[0][0], af[0][1], af[0][2], af[0][3], b.x, b.y);
+            else
+                pk_mma<Tag>(acc[j], af[2 * c][0], af[2 * c][1], af[2 * c][2], af[2 * c][3], b.x, b.y);
+            pk_mma<Tag>(acc[j], af[2 * c + 1][0], af[2 * c + 1][1], af[2 * c + 1][2], af[2 * c + 1][3], b.z, b.w);
         }
-        if (SOFTMAX && flip) {
+    }
+    float r0 = sl, r1 = sl;
+    if (SOFTMAX) {
+        acc[NT - 1][0] = last0 ? acc[NT - 1][0] : -INFINITY;
+        acc[NT - 1][2] = last0 ? acc[NT - 1][2] : -INFINITY;
+        acc[NT - 1][1] = last1 ? acc[NT - 1][1] : -INFINITY;
+        acc[NT - 1][3] = last1 ? acc[NT - 1][3] : -INFINITY;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            mx0 = fmaxf(mx0, fmaxf(acc[j][0], acc[j][1]));
+            mx1 = fmaxf(mx1, fmaxf(acc[j][2], acc[j][3]));
+        }
+        const float nm0 = -blk_quad_max(mx0) * sl, nm1 = -blk_quad_max(mx1) * sl;
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            acc[j][0] = blk_exp2(fmaf(acc[j][0], sl, nm0));
+            acc[j][1] = blk_exp2(fmaf(acc[j][1], sl, nm0));
+            acc[j][2] = blk_exp2(fmaf(acc[j][2], sl, nm1));
+            acc[j][3] = blk_exp2(fmaf(acc[j][3], sl, nm1));
+            s0 += acc[j][0] + acc[j][1];
+            s1 += acc[j][2] + acc[j][3];
+        }
+        r0 = __frcp_rn(blk_quad_sum(s0));
+        r1 = __frcp_rn(blk_quad_sum(s1));
+    }
+    // Rows that do not exist were given the address of a scratch area by the caller, so only the last tile's
+    // columns need a per-store decision; it is made by choosing the address, which keeps the stores unpredicated.
+    if (pairs) {  // every staged pair starts on a 4-byte boundary
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const uint32_t lo = BlkCvt<Tag>::pack2(acc[j][0] * r0, acc[j][1] * r0);
+            const uint32_t hi = BlkCvt<Tag>::pack2(acc[j][2] * r1, acc[j][3] * r1);
+            sts_b32(j < NT - 1 || last0 ? s0a + 16 * j : scratch, lo);
+            sts_b32(j < NT - 1 || last0 ? s1a + 16 * j : scratch, hi);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const uint32_t lo = BlkCvt<Tag>::pack2(acc[j][0] * r0, acc[j][1] * r0);
+            const uint32_t hi = BlkCvt<Tag>::pack2(acc[j][2] * r1, acc[j][3] * r1);
+            sts_b16(j < NT - 1 || last0 ? s0a + 16 * j : scratch, lo);
+            sts_b16(j < NT - 1 || last0 ? s1a + 16 * j : scratch, hi);
+            sts_b16(j < NT - 1 || last1 ? s0a + 16 * j + 2 : scratch, lo >> 16);
+            sts_b16(j < NT - 1 || last1 ? s1a + 16 * j + 2 : scratch, hi >> 16);
+        }
+    }
+}
+
+// One block = up to 16 first-operand rows of one segment against that segment's N <= 64 second-operand rows.
+// pA / pB point at the block's operand rows inside the slot.  Only the tile arithmetic is specialised by the
+// number of 8-column tiles (one jump per block); fragment loads, staging layout and copy-out are shared, which
+// keeps the code the sixteen warps run concurrently small enough for the instruction cache.
+// Rows past M and past N are read as whatever follows in shared memory: such rows of the result are never
+// stored and such columns are masked before the row reduction.  The result is staged over the block's own
+// first-operand rows (M * N * 2 <= M * 128 bytes) and copied to the output at element cbase.
+template <typename Tag, bool SOFTMAX, bool FLIP>
+__device__ __forceinline__ void pack_block(void* C, unsigned char* pA, const unsigned char* pB, int64_t cbase, int M,
+                                           int N, float sl, uint32_t scratch, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const int nt = (N + 7) >> 3;
+
+    uint32_t af[2 * PKC][4];
+    {
+        const unsigned char* la = pA + g * ROWB + 16 * t;
+#pragma unroll
+        for (int c = 0; c < PKC; ++c) {
+            const uint4 lo = *reinterpret_cast<const uint4*>(la + 64 * c);
+            const uint4 hi = *reinterpret_cast<const uint4*>(la + 8 * ROWB + 64 * c);
+            af[2 * c][0] = lo.x; af[2 * c][1] = hi.x; af[2 * c][2] = lo.y; af[2 * c][3] = hi.y;
+            af[2 * c + 1][0] = lo.z; af[2 * c + 1][1] = hi.z; af[2 * c + 1][2] = lo.w; af[2 * c + 1][3] = hi.w;
+        }
+        if (SOFTMAX && FLIP) {  // negative scale: softmax of the negated scores
 #pragma unroll
             for (int c = 0; c < 2 * PKC; ++c)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) af[c][e] ^= 0x80008000u;
         }
-        if (mb + 1 < nmb) load_a(mb + 1);  // the next rows are in registers before this block's output lands near them
-        float acc[NT][4];
-#pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-#pragma unroll
-            for (int c = 0; c < PKC; ++c) {
-                const uint4 b = lds16(pb[j] + 64 * c);
-                blk_mma16816<Tag>(acc[j], af[2 * c][0], af[2 * c][1], af[2 * c][2], af[2 * c][3], b.x, b.y);
-                blk_mma16816<Tag>(acc[j], af[2 * c + 1][0], af[2 * c + 1][1], af[2 * c + 1][2], af[2 * c + 1][3], b.z, b.w);
-            }
-        }
-        if (SOFTMAX) {
-            acc[NT - 1][0] = last0 ? acc[NT - 1][0] : -INFINITY;
-            acc[NT - 1][2] = last0 ? acc[NT - 1][2] : -INFINITY;
-            acc[NT - 1][1] = last1 ? acc[NT - 1][1] : -INFINITY;
-            acc[NT - 1][3] = last1 ? acc[NT - 1][3] : -INFINITY;
-            float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                mx0 = fmaxf(mx0, fmaxf(acc[j][0], acc[j][1]));
-                mx1 = fmaxf(mx1, fmaxf(acc[j][2], acc[j][3]));
-            }
-            const float nm0 = -blk_quad_max(mx0) * sl, nm1 = -blk_quad_max(mx1) * sl;
-            float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                acc[j][0] = blk_exp2(fmaf(acc[j][0], sl, nm0));
-                acc[j][1] = blk_exp2(fmaf(acc[j][1], sl, nm0));
-                acc[j][2] = blk_exp2(fmaf(acc[j][2], sl, nm1));
-                acc[j][3] = blk_exp2(fmaf(acc[j][3], sl, nm1));
-                s0 += acc[j][0] + acc[j][1];
-                s1 += acc[j][2] + acc[j][3];
-            }
-            const float i0 = __frcp_rn(blk_quad_sum(s0)), i1 = __frcp_rn(blk_quad_sum(s1));
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                acc[j][0] *= i0; acc[j][1] *= i0; acc[j][2] *= i1; acc[j][3] *= i1;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                acc[j][0] *= sl; acc[j][1] *= sl; acc[j][2] *= sl; acc[j][3] *= sl;
-            }
-        }
-        // stage rows 16 mb + g and + 8 if they exist (the staged block must stay inside this block's own rows)
-        const uint32_t s0a = srow + (uint32_t)(mb * 16 * N * 2), s1a = s0a + 8 * N * 2;
-        const bool v0 = mb * 16 + g < M, v1 = mb * 16 + g + 8 < M;
-        if (pair_ok) {
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                const bool in = j < NT - 1 || last0;
-                sts_b32_if(s0a + 16 * j, BlkCvt<Tag>::pack2(acc[j][0], acc[j][1]), in && v0);
-                sts_b32_if(s1a + 16 * j, BlkCvt<Tag>::pack2(acc[j][2], acc[j][3]), in && v1);
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                const bool in0 = j < NT - 1 || last0, in1 = j < NT - 1 || last1;
-                const uint32_t lo = BlkCvt<Tag>::pack2(acc[j][0], acc[j][1]);
-                const uint32_t hi = BlkCvt<Tag>::pack2(acc[j][2], acc[j][3]);
-                sts_b16_if(s0a + 16 * j, lo, in0 && v0);
-                sts_b16_if(s1a + 16 * j, hi, in0 && v1);
-                sts_b16_if(s0a + 16 * j + 2, lo >> 16, in1 && v0);
-                sts_b16_if(s1a + 16 * j + 2, hi >> 16, in1 && v1);
-            }
+    }
+    // The block's M * N results are contiguous in the output, starting mis bytes into a 16-byte vector.  They
+    // are staged at the same offset from the block's (128-byte aligned) rows when that fits, so that staged and
+    // global vectors line up and the copy-out needs no shifting.
+    const int nbytes = M * N * 2;
+    const int64_t g0 = cbase * 2;
+    const int mis = (int)(g0 & 15);
+    const int so = mis + nbytes <= M * ROWB ? mis : 0;
+    {
+        const unsigned char* lb = pB + g * ROWB + 16 * t;
+        const bool last0 = 8 * (nt - 1) + 2 * t < N, last1 = 8 * (nt - 1) + 2 * t + 1 < N;
+        // rows g and g + 8 of the staged block; a row past M is pointed at the scratch area instead
+        const uint32_t row0 = blk_smem_u32(pA) + (uint32_t)(so + (g * N + 2 * t) * 2);
+        const uint32_t s0a = g < M ? row0 : scratch, s1a = g + 8 < M ? row0 + 8 * N * 2 : scratch;
+        const bool pairs = ((N | (so >> 1)) & 1) == 0;
+        // one jump to the code for this tile count; only the tile arithmetic is specialised
+        switch (nt) {
+            case 1: pack_tiles<Tag, 1, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 2: pack_tiles<Tag, 2, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 3: pack_tiles<Tag, 3, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 4: pack_tiles<Tag, 4, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 5: pack_tiles<Tag, 5, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 6: pack_tiles<Tag, 6, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 7: pack_tiles<Tag, 7, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            default: pack_tiles<Tag, 8, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
         }
     }
     __syncwarp();
-    // staged block (M * N contiguous elements at sA) -> global.  Lane j owns the 16-byte vector j of the block *as
-    // aligned in global memory*; the block starts mis bytes into its first vector, so a lane gathers its bytes
-    // from the staged copy as five words and funnel-shifts them into place.  The ragged first and last vector
-    // go out as single elements (lanes 0-7 and 8-15).
+    // staged block -> global.  Lane j owns the 16-byte vector j of the block as aligned in global memory.  The
+    // ragged first and last vector go out as single elements (lanes 0-7 and 8-15).
     {
-        const int nbytes = M * N * 2;
-        const int64_t g0 = cbase * 2;
-        const int mis = (int)(g0 & 15);
         unsigned char* dst = reinterpret_cast<unsigned char*>(C) + (g0 - mis);  // 16-byte aligned
         const int end = mis + nbytes;
-        for (int lo = 16 * lane; lo < end; lo += 16 * 32) {
-            const int x = lo - mis;  // staged byte that goes to dst + lo
-            const int xw = x > 0 ? (x & ~3) : 0;
-            const int sb = (x & 2) * 8;
-            const uint32_t w0 = lds4(sA + xw), w1 = lds4(sA + xw + 4), w2 = lds4(sA + xw + 8), w3 = lds4(sA + xw + 12),
-                           w4 = lds4(sA + xw + 16);
-            uint4 v;
-            v.x = __funnelshift_r(w0, w1, sb);
-            v.y = __funnelshift_r(w1, w2, sb);
-            v.z = __funnelshift_r(w2, w3, sb);
-            v.w = __funnelshift_r(w3, w4, sb);
-            stg_v4_if(dst + lo, v, lo >= mis && lo + 16 <= end);
+        if (so == mis) {
+            for (int lo = 16 * lane; lo < end; lo += 16 * 32)
+                stg_v4_if(dst + lo, *reinterpret_cast<const uint4*>(pA + lo), lo >= mis && lo + 16 <= end);
+        } else {
+            // staged at offset 0: a lane gathers its bytes as five words and funnel-shifts them into place
+            for (int lo = 16 * lane; lo < end; lo += 16 * 32) {
+                const int x = lo - mis;  // staged byte that goes to dst + lo
+                const int xw = x > 0 ? (x & ~3) : 0;
+                const int sb = (x & 2) * 8;
+                const uint32_t* w = reinterpret_cast<const uint32_t*>(pA + xw);
+                const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3], w4 = w[4];
+                uint4 v;
+                v.x = __funnelshift_r(w0, w1, sb);
+                v.y = __funnelshift_r(w1, w2, sb);
+                v.z = __funnelshift_r(w2, w3, sb);
+                v.w = __funnelshift_r(w3, w4, sb);
+                stg_v4_if(dst + lo, v, lo >= mis && lo + 16 <= end);
+            }
         }
         const int tail = end & ~15;
         const bool is_tail = lane >= 8;
         const int b = (is_tail ? tail : 0) + 2 * (lane & 7);  // byte, counted from dst, of this lane's edge element
         const bool first_full = mis == 0 && end >= 16;
         const bool ok = lane < 16 && b >= mis && b < end && (is_tail ? tail != 0 : !first_full);
-        const int sx = ok ? b - mis : 0;
-        stg_b16_if(dst + b, lds2(sA + sx), ok);
+        const int sx = ok ? b - mis + so : 0;
+        stg_b16_if(dst + b, *reinterpret_cast<const uint16_t*>(pA + sx), ok);
     }
 }
 
-template <typename Tag, bool SOFTMAX>
-__global__ void __launch_bounds__(P_THREADS, 1) blk_scores_pipe_kernel(const BlkPackParams p, int dbg) {
+template <typename Tag, bool SOFTMAX, bool FLIP>
+__global__ void __launch_bounds__(P_THREADS, 1) blk_scores_pipe_kernel(const BlkPackParams p) {
     extern __shared__ __align__(128) unsigned char pipe_smem[];
-    uint64_t* bars = reinterpret_cast<uint64_t*>(pipe_smem + P_SLOTS * P_SLOT_BYTES);  // [s] full, [P_SLOTS + s] empty
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * P_SLOTS);
+    unsigned char* ctl = pipe_smem + P_SLOTS * P_SLOT_BYTES + P_TAIL_PAD;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ctl);  // [s] full, [P_SLOTS + s] empty
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(ctl + 16 * P_SLOTS);
+    int* next_block = reinterpret_cast<int*>(ctl + 16 * P_SLOTS + 16);  // [s]: next unclaimed block of the pack in slot s
+    const uint32_t scratch = blk_smem_u32(ctl + 16 * P_SLOTS + 16 + 4 * P_SLOTS);  // P_SCRATCH_BYTES, written, never read
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem0 = blk_smem_u32(pipe_smem), bar0 = blk_smem_u32(bars);
     auto full_bar = [&](uint32_t s) { return bar0 + 8u * s; };
@@ -266,66 +312,72 @@ __global__ void __launch_bounds__(P_THREADS, 1) blk_scores_pipe_kernel(const Blk
     if (threadIdx.x == 0) {
         for (int s = 0; s < P_SLOTS; ++s) {
             pb_init(full_bar(s), 1);
-            pb_init(empty_bar(s), P_CONSUMERS);
+            pb_init(empty_bar(s), P_GROUP_WARPS);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
 
+    // The CTA's u-th unit is (pack, head) number w = blockIdx.x + u * G, pack = w / H, head = w % H; it uses ring
+    // slot u % P_SLOTS and belongs to consumer group u % P_GROUPS (so each group owns P_SLOTS / P_GROUPS slots).
     const uint32_t total = (uint32_t)p.num_packs * (uint32_t)p.H;  // < 2^31, checked at plan creation
     const uint32_t H = (uint32_t)p.H, G = gridDim.x;
-    // the CTA's u-th unit is (pack, head) number w = blockIdx.x + u * G; it uses ring slot u % P_SLOTS
     if (warp == 0) {
         if (lane == 0) {
+            const uint32_t dq = G / H, dr = G - dq * H;  // (pack, head) advance by (dq, dr) per unit
+            uint32_t pack = blockIdx.x / H, hd = blockIdx.x - pack * H;  // blockIdx.x < total by the launch
+            BlkPack nxt = p.packs[pack];
             uint32_t u = 0;
-            BlkPack nxt = p.packs[blockIdx.x / H];  // blockIdx.x < total by the launch
             for (uint32_t w = blockIdx.x; w < total; w += G, ++u) {
                 const BlkPack pk = nxt;
-                const uint32_t pack = w / H, hd = w - pack * H;
-                if (w + G < total) nxt = p.packs[(w + G) / H];  // next record in flight during this unit's wait
+                const uint32_t hd_now = hd;
+                pack += dq;
+                hd += dr;
+                if (hd >= H) {
+                    hd -= H;
+                    ++pack;
+                }
+                if (w + G < total) nxt = p.packs[pack];  // next record in flight during this unit's wait
                 const uint32_t s = u % P_SLOTS;
                 if (!pb_wait(empty_bar(s), ((u / P_SLOTS) & 1u) ^ 1u, abort_flag, p.status, 11)) break;
                 const uint32_t bytesA = (uint32_t)pk.rowsA * ROWB, bytesB = (uint32_t)pk.rowsB * ROWB;
                 const uint32_t bytesR = (uint32_t)pk.nblocks * (uint32_t)sizeof(BlkPackBlock);
                 const uint32_t dst = smem0 + s * P_SLOT_BYTES;
+                *reinterpret_cast<volatile int*>(next_block + s) = 0;  // ordered before the consumers' claims by the barrier
                 pb_expect_tx(full_bar(s), bytesA + bytesB + bytesR);
-                bulk_g2s(dst, p.A + ((int64_t)hd * p.Dm1 + pk.offA), bytesA, full_bar(s));
-                bulk_g2s(dst + P_OPER_BYTES, p.B + ((int64_t)hd * p.Dm2 + pk.offB), bytesB, full_bar(s));
+                bulk_g2s(dst, p.A + ((int64_t)hd_now * p.Dm1 + pk.offA), bytesA, full_bar(s));
+                bulk_g2s(dst + P_OPER_BYTES, p.B + ((int64_t)hd_now * p.Dm2 + pk.offB), bytesB, full_bar(s));
                 bulk_g2s(dst + 2 * P_OPER_BYTES, p.blocks + pk.first_block, bytesR, full_bar(s));
             }
         }
     } else {
-        const uint32_t cw = warp - 1;
-        const bool flip = p.scale < 0.f;
+        const uint32_t group = (uint32_t)(warp - 1) % P_GROUPS;
         const float sl = SOFTMAX ? fabsf(p.scale) * BLK_LOG2E : p.scale;
-        uint32_t u = 0;
-        for (uint32_t w = blockIdx.x; w < total; w += G, ++u) {
+        const uint32_t step = P_GROUPS * G, dq = step / H, dr = step - dq * H;
+        uint32_t w = blockIdx.x + group * G;
+        uint32_t hd = w % H;
+        for (uint32_t u = group; w < total; w += step, u += P_GROUPS) {
             const uint32_t s = u % P_SLOTS;
+            const int64_t hbase = (int64_t)hd * p.Dout;
+            hd += dr;
+            if (hd >= H) hd -= H;
             if (!pb_wait(full_bar(s), (u / P_SLOTS) & 1u, abort_flag, p.status, 12)) break;
-            const unsigned char* slot = pipe_smem + s * P_SLOT_BYTES;
+            unsigned char* slot = pipe_smem + s * P_SLOT_BYTES;
             const BlkPackBlock* recs = reinterpret_cast<const BlkPackBlock*>(slot + 2 * P_OPER_BYTES);
-            // block b of unit u goes to consumer (b + 5 u) mod 16: spreads short packs over all consumers
-            const uint32_t b = (cw - 5u * u) & (P_CONSUMERS - 1);
-            if ((int)b < recs[0].nblocks && !(dbg & 1)) {
+            const int nb = recs[0].nblocks;
+            // the group's warps claim the pack's blocks (widest first) one at a time: a warp that finishes early takes more
+            for (;;) {
+                int b = 0;
+                if (lane == 0) b = atomicAdd(next_block + s, 1);
+                b = __shfl_sync(0xffffffffu, b, 0);
+                if (b >= nb) break;
                 const BlkPackBlock r = recs[b];
-                const uint32_t hd = w - (w / H) * H;
-                const uint32_t sA = smem0 + s * P_SLOT_BYTES + (uint32_t)r.rowA * ROWB;
-                const uint32_t sB = smem0 + s * P_SLOT_BYTES + P_OPER_BYTES + (uint32_t)r.rowB * ROWB;
-                const int64_t cbase = (int64_t)hd * p.Dout + r.offC;
-                switch ((r.N + 7) >> 3) {
-                    case 1: pack_block<Tag, 1, SOFTMAX>(p.C, sA, sB, cbase, r.M, r.N, sl, flip, lane); break;
-                    case 2: pack_block<Tag, 2, SOFTMAX>(p.C, sA, sB, cbase, r.M, r.N, sl, flip, lane); break;
-                    case 3: pack_block<Tag, 3, SOFTMAX>(p.C, sA, sB, cbase, r.M, r.N, sl, flip, lane); break;
-                    case 4: pack_block<Tag, 4, SOFTMAX>(p.C, sA, sB, cbase, r.M, r.N, sl, flip, lane); break;
-                    case 5: pack_block<Tag, 5, SOFTMAX>(p.C, sA, sB, cbase, r.M, r.N, sl, flip, lane); break;
-                    case 6: pack_block<Tag, 6, SOFTMAX>(p.C, sA, sB, cbase, r.M, r.N, sl, flip, lane); break;
-                    case 7: pack_block<Tag, 7, SOFTMAX>(p.C, sA, sB, cbase, r.M, r.N, sl, flip, lane); break;
-                    default: pack_block<Tag, 8, SOFTMAX>(p.C, sA, sB, cbase, r.M, r.N, sl, flip, lane); break;
-                }
-                // this warp's reads and writes of the slot are done: order them before the next bulk copy into it
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                pack_block<Tag, SOFTMAX, FLIP>(p.C, slot + r.rowA * ROWB, slot + P_OPER_BYTES + r.rowB * ROWB, hbase + r.offC, r.M,
+                                               r.N, sl, scratch, lane);
             }
+            // this warp's reads and writes of the slot are done: order them before the next bulk copy into it
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) pb_arrive(empty_bar(s));
         }
@@ -345,10 +397,11 @@ cudaError_t launch_pipe(const BlkPackParams& p, int sms, cudaStream_t st) {
     auto go = [&](auto kern) -> cudaError_t {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        kern<<<grid, block, P_SMEM_BYTES, st>>>(p, getenv("BLK_PIPE_DBG") ? atoi(getenv("BLK_PIPE_DBG")) : 0);
+        kern<<<grid, block, P_SMEM_BYTES, st>>>(p);
         return cudaGetLastError();
     };
-    return p.epi == BLK_EPI_SOFTMAX ? go(blk_scores_pipe_kernel<Tag, true>) : go(blk_scores_pipe_kernel<Tag, false>);
+    if (p.epi != BLK_EPI_SOFTMAX) return go(blk_scores_pipe_kernel<Tag, false, false>);
+    return p.scale < 0.f ? go(blk_scores_pipe_kernel<Tag, true, true>) : go(blk_scores_pipe_kernel<Tag, true, false>);
 }
 
 }  // namespace

@@ -75,21 +75,19 @@ def test_exhaustive_small_extents(cuda_device, dtype, K):
 def test_exhaustive_small_fused_softmax(cuda_device, K):
     g = np.arange(1, 41)
     M, N = [a.ravel() for a in np.meshgrid(g, g, indexing="ij")]
-    # default (register-fed small kernel), staged kernel only, pipelined pack kernel (takes K = 64 only)
-    for env in (None, {"BLK_DISABLE_SMALL": "1"}, {"BLK_ENABLE_PIPE": "1"}):
+    # default (K = 64: pipelined pack kernel, K = 32: register-fed small kernel), staged kernel only, register-fed only
+    for env in (None, {"BLK_DISABLE_SMALL": "1"}, {"BLK_DISABLE_PIPE": "1"}):
         p = run_case(cuda_device, M, N, np.full(M.size, K), 2, F16, softmax=True, scale=0.3, seed=K, env=env,
                      what=f"fused grid K={K} env={env}")
-        assert (p.summary["small_items"] > 0) == (env is None or "BLK_ENABLE_PIPE" in env)
-        assert (p.summary["packs"] > 0) == (K == 64 and env is not None and "BLK_ENABLE_PIPE" in env)
+        assert (p.summary["small_items"] > 0) == (env is None or "BLK_DISABLE_PIPE" in env)
+        pipe_off = bool(env) or os.environ.get("BLK_DISABLE_PIPE", "0") not in ("", "0")
+        assert (p.summary["packs"] > 0) == (K == 64 and not pipe_off)
         p.check()
-    for env in ({"BLK_ENABLE_PIPE": "1"},):
-        run_case(cuda_device, M, N, np.full(M.size, K), 2, BF16, scale=0.5, seed=K, env=env, what=f"pack scores grid K={K}")
-        run_case(cuda_device, M, N, np.full(M.size, K), 3, BF16, softmax=True, scale=-0.7, seed=K + 1, env=env,
-                 what=f"pack fused grid negative scale K={K}")
     # scores only and bf16 through the same kernels, a negative scale on the fused path
-    run_case(cuda_device, M, N, np.full(M.size, K), 2, BF16, scale=0.5, seed=K, what=f"scores grid K={K}")
-    run_case(cuda_device, M, N, np.full(M.size, K), 3, BF16, softmax=True, scale=-0.7, seed=K + 1,
-             what=f"fused grid negative scale K={K}")
+    for env in (None, {"BLK_DISABLE_PIPE": "1"}):
+        run_case(cuda_device, M, N, np.full(M.size, K), 2, BF16, scale=0.5, seed=K, env=env, what=f"scores grid K={K}")
+        run_case(cuda_device, M, N, np.full(M.size, K), 3, BF16, softmax=True, scale=-0.7, seed=K + 1, env=env,
+                 what=f"fused grid negative scale K={K}")
 
 
 UMMA_SHAPES = dict(
