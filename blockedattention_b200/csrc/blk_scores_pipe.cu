@@ -32,14 +32,20 @@ namespace {
 constexpr int PK = 64;  // contraction length handled here
 constexpr int PKC = PK / 32;
 constexpr int ROWB = PK * 2;  // bytes per operand row
-constexpr int P_CONSUMERS = 16;
+#ifndef BLK_PIPE_CONSUMERS
+#define BLK_PIPE_CONSUMERS 16
+#endif
+#ifndef BLK_PIPE_GROUPS
+#define BLK_PIPE_GROUPS 2
+#endif
+constexpr int P_CONSUMERS = BLK_PIPE_CONSUMERS;
 constexpr int P_THREADS = 32 * (1 + P_CONSUMERS);
 constexpr int P_OPER_BYTES = BLK_PACK_ROWS * ROWB;  // 24 KB per operand per slot
 constexpr int P_REC_BYTES = BLK_PACK_BLOCKS * (int)sizeof(BlkPackBlock);
 constexpr int P_SLOT_BYTES = 2 * P_OPER_BYTES + P_REC_BYTES;
 constexpr int P_SLOTS = 4;
 constexpr int P_TAIL_PAD = 1024;  // second-operand rows are read up to 7 rows past a run's end
-constexpr int P_GROUPS = 2;        // consumer groups; unit u belongs to group u % P_GROUPS
+constexpr int P_GROUPS = BLK_PIPE_GROUPS;        // consumer groups; unit u belongs to group u % P_GROUPS
 constexpr int P_GROUP_WARPS = P_CONSUMERS / P_GROUPS;
 constexpr int P_SCRATCH_BYTES = 128;  // target of staging stores that must not land
 constexpr int P_SMEM_BYTES = P_SLOTS * P_SLOT_BYTES + P_TAIL_PAD + 16 * P_SLOTS + 16 + 4 * P_SLOTS + P_SCRATCH_BYTES;
