@@ -6,9 +6,10 @@
 // One CTA (4 warps) owns a 64-row block of one segment of one head and a
 // 128-column tile of it; warp w owns rows 16w..16w+15 across all 128 columns,
 // so a row's reduction never leaves a quad.  Operands are staged through
-// shared memory (register-staged double buffer, 16-byte / 4-byte / 2-byte
-// global loads chosen per segment and head from the actual alignment) and fed
-// to mma.sync.m16n8k16 through ldmatrix.  With the softmax epilogue the CTA
+// shared memory (register-staged double buffer; per operand, segment and head
+// either plain 16-byte global loads or, for rows that start at odd element
+// offsets, aligned 16-byte loads shifted into place in registers) and fed to
+// mma.sync.m16n8k16 through ldmatrix.  With the softmax epilogue the CTA
 // sweeps the column tiles of its rows twice -- first keeping only a running
 // (max, sum) per row, then recomputing the products and writing normalised
 // probabilities -- so the scores never reach global memory; a segment with
@@ -27,52 +28,67 @@ constexpr int A_STAGE = (BM * A_PITCH_N > BK * A_PITCH_T) ? BM * A_PITCH_N : BK 
 constexpr int B_STAGE = (BN * B_PITCH_N > BK * B_PITCH_T) ? BN * B_PITCH_N : BK * B_PITCH_T;
 constexpr int NJ = BN / 8;  // n8 tiles per warp row block
 
-// Register staging of an OUTER x INNER tile of a row-major matrix, U 16-bit
-// elements per access (8 -> one 16-byte load, 2 -> one 4-byte load or, with
-// SCALAR, two 2-byte loads).
-template <int OUTER, int INNER, int U, bool SCALAR>
+// Eight consecutive 16-bit elements starting at any element address: the two 16-byte aligned vectors that
+// cover them are loaded and the wanted bytes shifted into place.  Elements from nvalid (1..8) on read as zero;
+// the second vector is fetched only when a wanted byte lies in it, so no vector without a valid byte is touched.
+__device__ __forceinline__ uint4 ldg8_any(const uint16_t* src, int nvalid) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(src);
+    const uint4* base = reinterpret_cast<const uint4*>(a & ~static_cast<uintptr_t>(15));
+    const uint32_t m = static_cast<uint32_t>(a) & 15u;  // even
+    const uint4 v0 = __ldg(base);
+    uint4 v1 = make_uint4(0u, 0u, 0u, 0u);
+    if ((int)m + 2 * nvalid > 16) v1 = __ldg(base + 1);
+    uint32_t w0 = v0.x, w1 = v0.y, w2 = v0.z, w3 = v0.w, w4 = v1.x, w5 = v1.y;
+    if (m & 8u) {
+        w0 = w2; w1 = w3; w2 = w4; w3 = w5; w4 = v1.z; w5 = v1.w;
+    }
+    if (m & 4u) {
+        w0 = w1; w1 = w2; w2 = w3; w3 = w4; w4 = w5;
+    }
+    const uint32_t sh = (m & 2u) * 8u;
+    uint4 r;
+    r.x = __funnelshift_r(w0, w1, sh);
+    r.y = __funnelshift_r(w1, w2, sh);
+    r.z = __funnelshift_r(w2, w3, sh);
+    r.w = __funnelshift_r(w3, w4, sh);
+    if (nvalid < 8) {
+        auto keep = [&](uint32_t w, int j) { return nvalid >= 2 * j + 2 ? w : (nvalid == 2 * j + 1 ? (w & 0xffffu) : 0u); };
+        r.x = keep(r.x, 0); r.y = keep(r.y, 1); r.z = keep(r.z, 2); r.w = keep(r.w, 3);
+    }
+    return r;
+}
+
+// Register staging of an OUTER x INNER tile of a row-major matrix in units of eight 16-bit elements: one
+// 16-byte load per unit when the matrix is ALIGNED (16-byte aligned base and a pitch that is a multiple of
+// eight elements, so the inner extent is one too), the shifting load above otherwise.
+template <int OUTER, int INNER, bool ALIGNED>
 struct TileStage {
-    static constexpr int UPR = INNER / U;
+    static constexpr int UPR = INNER / 8;
     static constexpr int UNITS = OUTER * UPR;
     static constexpr int PT = UNITS / NT;
     static_assert(UNITS % NT == 0, "tile must divide among the threads");
-    uint32_t r[PT * (U / 2)];
+    uint4 r[PT];
 
     __device__ __forceinline__ void load(const uint16_t* __restrict__ g, int64_t ld, int o0, int i0, int o_lim,
                                          int i_lim, int tid) {
 #pragma unroll
         for (int j = 0; j < PT; ++j) {
             const int u = tid + j * NT;
-            const int o = o0 + u / UPR, i = i0 + (u % UPR) * U;
+            const int o = o0 + u / UPR, i = i0 + (u % UPR) * 8;
             const uint16_t* src = g + (int64_t)o * ld + i;
-            if constexpr (U == 8) {
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (o < o_lim && i < i_lim) v = blk_ldg16(src);
-                r[4 * j + 0] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
-            } else if constexpr (!SCALAR) {
-                uint32_t v = 0u;
-                if (o < o_lim && i < i_lim) v = __ldg(reinterpret_cast<const uint32_t*>(src));
-                r[j] = v;
-            } else {
-                uint32_t lo = 0u, hi = 0u;
-                if (o < o_lim) {
-                    if (i < i_lim) lo = __ldg(src);
-                    if (i + 1 < i_lim) hi = __ldg(src + 1);
-                }
-                r[j] = lo | (hi << 16);
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (o < o_lim && i < i_lim) {
+                if constexpr (ALIGNED) v = blk_ldg16(src);
+                else v = ldg8_any(src, min(8, i_lim - i));
             }
+            r[j] = v;
         }
     }
     __device__ __forceinline__ void store(uint16_t* s, int pitch, int tid) const {
 #pragma unroll
         for (int j = 0; j < PT; ++j) {
             const int u = tid + j * NT;
-            uint16_t* dst = s + (u / UPR) * pitch + (u % UPR) * U;
-            if constexpr (U == 8) {
-                *reinterpret_cast<uint4*>(dst) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-            } else {
-                *reinterpret_cast<uint32_t*>(dst) = r[j];
-            }
+            *reinterpret_cast<uint4*>(s + (u / UPR) * pitch + (u % UPR) * 8) = r[j];
         }
     }
 };
@@ -110,7 +126,7 @@ __device__ __forceinline__ void mma_stage(float (&acc)[NJ][4], const uint16_t* s
 }
 
 // acc = A[m0.., :] * B[n0.., :]^T for the CTA's 64 x 128 tile.
-template <typename Tag, bool TA, bool TB, int U, bool SCALAR>
+template <typename Tag, bool TA, bool TB, bool AA, bool AB>
 __device__ __forceinline__ void compute_tile(float (&acc)[NJ][4], const uint16_t* __restrict__ gA,
                                              const uint16_t* __restrict__ gB, int M, int N, int K, int m0, int n0,
                                              uint16_t (*sA)[A_STAGE], uint16_t (*sB)[B_STAGE], int tid) {
@@ -122,8 +138,8 @@ __device__ __forceinline__ void compute_tile(float (&acc)[NJ][4], const uint16_t
     const bool active = m0 + warp * 16 < M;
     const int ncols = min(N - n0, BN);
 
-    TileStage<TA ? BK : BM, TA ? BM : BK, U, SCALAR> stA;
-    TileStage<TB ? BK : BN, TB ? BN : BK, U, SCALAR> stB;
+    TileStage<TA ? BK : BM, TA ? BM : BK, AA> stA;
+    TileStage<TB ? BK : BN, TB ? BN : BK, AB> stB;
     auto loadA = [&](int k0) {
         if constexpr (!TA) stA.load(gA, K, m0, k0, M, K, tid); else stA.load(gA, M, k0, m0, K, M, tid);
     };
@@ -190,7 +206,7 @@ __device__ __forceinline__ void store_frag(void* C, int out_f32, int64_t cbase, 
     }
 }
 
-template <typename Tag, bool TA, bool TB, int U, bool SCALAR>
+template <typename Tag, bool TA, bool TB, bool AA, bool AB>
 __device__ __forceinline__ void tile_body(const BlkGemmParams& p, const BlkSeg& sd, const BlkTileItem& it,
                                           const uint16_t* gA, const uint16_t* gB, int64_t cbase,
                                           uint16_t (*sA)[A_STAGE], uint16_t (*sB)[B_STAGE]) {
@@ -203,7 +219,7 @@ __device__ __forceinline__ void tile_body(const BlkGemmParams& p, const BlkSeg& 
 
     if (p.epi == BLK_EPI_SCORES) {
         const int n0 = it.tn * BN;
-        compute_tile<Tag, TA, TB, U, SCALAR>(acc, gA, gB, M, N, K, m0, n0, sA, sB, tid);
+        compute_tile<Tag, TA, TB, AA, AB>(acc, gA, gB, M, N, K, m0, n0, sA, sB, tid);
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
             acc[j][0] *= p.scale; acc[j][1] *= p.scale; acc[j][2] *= p.scale; acc[j][3] *= p.scale;
@@ -217,7 +233,7 @@ __device__ __forceinline__ void tile_body(const BlkGemmParams& p, const BlkSeg& 
     float mrun[2] = {-INFINITY, -INFINITY}, lrun[2] = {0.f, 0.f};
     for (int tn = 0; tn < it.ntn; ++tn) {
         const int n0 = tn * BN;
-        compute_tile<Tag, TA, TB, U, SCALAR>(acc, gA, gB, M, N, K, m0, n0, sA, sB, tid);
+        compute_tile<Tag, TA, TB, AA, AB>(acc, gA, gB, M, N, K, m0, n0, sA, sB, tid);
         float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
@@ -273,7 +289,7 @@ __device__ __forceinline__ void tile_body(const BlkGemmParams& p, const BlkSeg& 
     }
     for (int tn = 0; tn < it.ntn; ++tn) {
         const int n0 = tn * BN;
-        compute_tile<Tag, TA, TB, U, SCALAR>(acc, gA, gB, M, N, K, m0, n0, sA, sB, tid);
+        compute_tile<Tag, TA, TB, AA, AB>(acc, gA, gB, M, N, K, m0, n0, sA, sB, tid);
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
 #pragma unroll
@@ -296,13 +312,14 @@ __global__ void __launch_bounds__(NT, 3) blk_gemm_tile_kernel(const BlkGemmParam
     const uint16_t* gA = p.A + baseA;
     const uint16_t* gB = p.B + baseB;
     const int64_t pitchA = TA ? sd.M : sd.K, pitchB = TB ? sd.N : sd.K;
-    const int64_t bits = baseA | baseB | pitchA | pitchB;
-    if ((bits & 7) == 0) {
-        tile_body<Tag, TA, TB, 8, false>(p, sd, it, gA, gB, cbase, sA, sB);
-    } else if ((bits & 1) == 0) {
-        tile_body<Tag, TA, TB, 2, false>(p, sd, it, gA, gB, cbase, sA, sB);
+    // per operand: plain 16-byte loads when every row of this (segment, head) starts on a 16-byte boundary
+    const bool alignedA = ((baseA | pitchA) & 7) == 0, alignedB = ((baseB | pitchB) & 7) == 0;
+    if (alignedA) {
+        if (alignedB) tile_body<Tag, TA, TB, true, true>(p, sd, it, gA, gB, cbase, sA, sB);
+        else tile_body<Tag, TA, TB, true, false>(p, sd, it, gA, gB, cbase, sA, sB);
     } else {
-        tile_body<Tag, TA, TB, 2, true>(p, sd, it, gA, gB, cbase, sA, sB);
+        if (alignedB) tile_body<Tag, TA, TB, false, true>(p, sd, it, gA, gB, cbase, sA, sB);
+        else tile_body<Tag, TA, TB, false, false>(p, sd, it, gA, gB, cbase, sA, sB);
     }
 }
 
