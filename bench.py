@@ -200,7 +200,7 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from blockedattention_b200 import blockAttnScores, blockGEMM, partition
+    from blockedattention_b200 import blockAttnScores, blockAttnScoresHost, blockGEMM, partition
     from blockedattention_b200.plan import GemmPlan
     from blockedattention_b200.synth import workload
 
@@ -317,6 +317,11 @@ def main():
 
         def e2e_step(i):
             hin = host[i % nh]
+            if w.softmax and not w.d_v:
+                # host operands in, host probabilities out: head groups pipelined over three streams
+                blockAttnScoresHost(hin[0], hin[1], w.M, w.N, w.K, scale=w.scale, out=h_out, out_dtype=w.out_dtype,
+                                    device=dev)
+                return
             q = hin[0].to(dev, non_blocking=True)
             k = hin[1].to(dev, non_blocking=True)
             if w.softmax:
@@ -348,7 +353,9 @@ def main():
         d2h = (h_o2 if w.d_v else h_out).numel() * h_out.element_size()
         e2e = {"value": flops_all / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e_ms,
                "steps": e2e_steps, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-               "api": "blockedattention_b200.blockAttnScores on pinned host tensors (per rank)"}
+               "api": ("blockedattention_b200.blockAttnScoresHost on pinned host tensors (per rank)"
+                       if w.softmax and not w.d_v else
+                       "blockedattention_b200.blockGEMM / blockAttnScores with explicit copies of pinned host tensors")}
     sampler.stop()
 
     gather = None

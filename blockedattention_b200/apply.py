@@ -154,3 +154,93 @@ def blockAttnScores(q: torch.Tensor, k: torch.Tensor, MList, NList, KList, scale
     scores are never written to memory."""
     return blockGEMM(q, k, None, None, None, MList, NList, KList, False, False,
                      scale=scale, out_dtype=out_dtype, softmax=True)
+
+
+class _HostPipe:
+    """Device-side staging of ``blockAttnScoresHost`` for one (lists, H, dtypes, device): a plan for a group of
+    heads, two sets of device buffers and three streams (copy in, compute, copy out)."""
+
+    def __init__(self, M, N, K, H, groups, dtype, odt, softmax, device):
+        self.groups, self.Hg = groups, H // groups
+        self.plan = GemmPlan(M, N, K, self.Hg, dtype, odt, False, False, softmax, device=device)
+        p = self.plan
+        self.bufs = [(torch.empty((self.Hg, p.Dm1), dtype=dtype, device=device),
+                      torch.empty((self.Hg, p.Dm2), dtype=dtype, device=device),
+                      torch.empty((self.Hg, p.Dout), dtype=odt, device=device)) for _ in range(2)]
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(device=device) for _ in range(3))
+
+    def close(self):
+        self.plan.close()
+
+
+def blockAttnScoresHost(q: torch.Tensor, k: torch.Tensor, MList, NList, KList, scale: float = 1.0,
+                        out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+                        device=None, softmax: bool = True, head_groups: Optional[int] = None) -> torch.Tensor:
+    """``blockAttnScores`` for operands and result that live in host memory.
+
+    ``q -> (H, sum m_s*k_s)``, ``k -> (H, sum n_s*k_s)`` and the result ``(H, sum m_s*n_s)`` are host tensors
+    (pinned memory makes the copies asynchronous).  The heads are processed in ``head_groups`` groups (default:
+    one head per group, at most eight groups): while group g is computed, group g+1 is copied to the device and
+    the result of group g-1 is copied back, so the transfer of the result and the arithmetic hide behind the
+    transfer of the operands.  The call is ordered after work already queued on the current stream and the
+    current stream waits for the last copy: synchronise it before reading ``out`` on the host.
+    """
+    for name, t in (("q", q), ("k", k)):
+        if not isinstance(t, torch.Tensor) or t.is_cuda:
+            raise RuntimeError(f"{name} must be a host tensor")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous Tensor")
+    if q.dtype != k.dtype:
+        raise RuntimeError("q and k must have the same dtype")
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    odt = out_dtype if out_dtype is not None else q.dtype
+    M, N, K = _host_i64(MList), _host_i64(NList), _host_i64(KList)
+    Dm1, Dm2, Dout = int((M * K).sum()), int((N * K).sum()), int((M * N).sum())
+    if Dm1 <= 0 or q.numel() % Dm1 or k.numel() != (q.numel() // Dm1) * Dm2:
+        raise RuntimeError("q / k do not match the packed extents of the lists")
+    H = q.numel() // Dm1
+    groups = head_groups if head_groups is not None else next(g for g in range(min(H, 8), 0, -1) if H % g == 0)
+    if groups < 1 or H % groups:
+        raise RuntimeError(f"head_groups = {groups} does not divide H = {H}")
+    if out is None:
+        out = torch.empty((H, Dout), dtype=odt).pin_memory()
+    elif out.is_cuda or not out.is_contiguous() or out.dtype != odt or out.numel() != H * Dout:
+        raise RuntimeError("out must be a contiguous host tensor of the output dtype with H*Dout elements")
+    key = ("hostpipe", M.tobytes(), N.tobytes(), K.tobytes(), H, groups, q.dtype, odt, bool(softmax), str(dev))
+    pipe = _cached(key, lambda: _HostPipe(M, N, K, H, groups, q.dtype, odt, bool(softmax), dev))
+    Hg = pipe.Hg
+    qv, kv, ov = q.reshape(H, Dm1), k.reshape(H, Dm2), out.reshape(H, Dout)
+    cur = torch.cuda.current_stream(dev)
+    start = torch.cuda.Event()
+    start.record(cur)
+    for s in (pipe.s_in, pipe.s_run, pipe.s_out):
+        s.wait_event(start)
+    ran = [None, None]     # per buffer set: event after the kernels that read its operands
+    drained = [None, None]  # per buffer set: event after the copy that read its result
+    for g in range(groups):
+        b = g & 1
+        dq, dk, do = pipe.bufs[b]
+        rows = slice(g * Hg, (g + 1) * Hg)
+        with torch.cuda.stream(pipe.s_in):
+            if ran[b] is not None:
+                pipe.s_in.wait_event(ran[b])
+            dq.copy_(qv[rows], non_blocking=True)
+            dk.copy_(kv[rows], non_blocking=True)
+            loaded = torch.cuda.Event()
+            loaded.record(pipe.s_in)
+        with torch.cuda.stream(pipe.s_run):
+            pipe.s_run.wait_event(loaded)
+            if drained[b] is not None:
+                pipe.s_run.wait_event(drained[b])
+            pipe.plan.run(dq, dk, out=do, scale=scale)
+            ran[b] = torch.cuda.Event()
+            ran[b].record(pipe.s_run)
+        with torch.cuda.stream(pipe.s_out):
+            pipe.s_out.wait_event(ran[b])
+            ov[rows].copy_(do, non_blocking=True)
+            drained[b] = torch.cuda.Event()
+            drained[b].record(pipe.s_out)
+    for ev in drained:
+        if ev is not None:
+            cur.wait_event(ev)
+    return out

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from helpers import O, assert_probs_close, assert_scores_close, packed_inputs
-from blockedattention_b200 import blockAttnScores, blockGEMM, blockSoftmax
+from blockedattention_b200 import blockAttnScores, blockAttnScoresHost, blockGEMM, blockSoftmax
 from blockedattention_b200 import _lib as L
 from blockedattention_b200.plan import GemmPlan
 from blockedattention_b200.synth import workload
@@ -258,6 +258,28 @@ def test_python_surface_matches_upstream_contract(cuda_device):
         blockGEMM(A.to(dev), B.to(dev))                                    # neither lists nor offsets
     with pytest.raises(RuntimeError):
         blockGEMM(A.to(dev)[:, :-1].contiguous(), B.to(dev), None, None, None, M, M, K)
+
+
+@pytest.mark.parametrize("groups", [None, 1, 2, 3])
+def test_host_entry_point_matches_device_call(cuda_device, groups):
+    # host operands in, host result out, head groups pipelined over three streams: same bits as the device call
+    dev = cuda_device
+    rs = np.random.RandomState(5)
+    M = rs.randint(1, 60, size=40); K = np.full(40, 64)
+    H = 6
+    A, B = packed_inputs(M, M, K, H, F16, 3)
+    want = blockAttnScores(A.to(dev), B.to(dev), M, M, K, scale=0.125)
+    for pinned in (True, False):
+        q, k = (A.pin_memory(), B.pin_memory()) if pinned else (A, B)
+        for rep in range(3):  # repeated calls reuse the staging buffers: later groups must wait for earlier copies
+            got = blockAttnScoresHost(q, k, M, M, K, scale=0.125, device=dev, head_groups=groups)
+            torch.cuda.current_stream(dev).synchronize()
+            assert not got.is_cuda and got.shape == want.shape
+            assert torch.equal(got, want.cpu())
+    with pytest.raises(RuntimeError):
+        blockAttnScoresHost(A.to(dev), B, M, M, K, device=dev)              # device operand
+    with pytest.raises(RuntimeError):
+        blockAttnScoresHost(A, B, M, M, K, device=dev, head_groups=4)       # 4 does not divide 6 heads
 
 
 def test_unaligned_pointer_is_handled(cuda_device):
