@@ -13,7 +13,12 @@ Differences from upstream, all at the boundary:
 * the shape checks upstream leaves to ``assert`` raise ``RuntimeError``;
 * ``blockSoftmax`` passes its arguments by name, so ``srcAccum`` reaches the
   offsets parameter (upstream ``apply.py:41`` hands it to ``rowList``);
-* forward only: outputs do not carry autograd history.
+* autograd: both operators record the same backward as upstream
+  (``csrc/sparseBlockedAttention.cpp:52-72``: two blocked GEMMs with permuted
+  lists, offsets and transposition flags; ``:103-114``: the softmax backward
+  kernel); the fused ``blockAttnScores`` chains the two.  As upstream, the
+  operand gradients are laid out (m, k) / (n, k) row-major whatever the
+  forward transposition flags were.
 """
 from __future__ import annotations
 
@@ -72,6 +77,69 @@ def _lists_from_offsets(a1, a2, ao):
     return M, N, K
 
 
+def _gemm_backward(ctx_meta, mat1, mat2, grad_out, scale):
+    """The two launches of upstream sparseBlockedGEMM::backward (csrc/sparseBlockedAttention.cpp:52-72):
+    mat1Grad = blockedGEMM(outGrad, mat2; offsets (out, mat2, mat1); lists (M, K, N); false, !transpose2) and
+    mat2Grad = blockedGEMM(outGrad, mat1; offsets (out, mat1, mat2); lists (N, K, M); true, !transpose1)."""
+    M, N, K, a1, a2, ao, ta, tb, H = ctx_meta
+    g = grad_out.contiguous()
+    m1 = mat1.to(g.dtype)
+    m2 = mat2.to(g.dtype)
+    dev = g.device
+    k1 = ("gemm_bwd1", M.tobytes(), N.tobytes(), K.tobytes(), a1.tobytes(), a2.tobytes(), ao.tobytes(), tb, H, g.dtype, str(dev))
+    p1 = _cached(k1, lambda: GemmPlan(M, K, N, H, g.dtype, g.dtype, False, not tb, False, accum=(ao, a2, a1), device=dev))
+    k2 = ("gemm_bwd2", M.tobytes(), N.tobytes(), K.tobytes(), a1.tobytes(), a2.tobytes(), ao.tobytes(), ta, H, g.dtype, str(dev))
+    p2 = _cached(k2, lambda: GemmPlan(N, K, M, H, g.dtype, g.dtype, True, not ta, False, accum=(ao, a1, a2), device=dev))
+    return p1.run(g, m2, scale=scale), p2.run(g, m1, scale=scale)
+
+
+class _BlockGEMMFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, mat1, mat2, plan, scale, softmax):
+        out = plan.run(mat1, mat2, scale=scale)
+        a1, a2, ao = plan.offsets
+        ctx.meta = (plan.M, plan.N, plan.K, a1, a2, ao, plan.ta, plan.tb, plan.H)
+        ctx.scale, ctx.softmax = scale, softmax
+        ctx.lead = (mat1.shape, mat2.shape)
+        ctx.save_for_backward(mat1, mat2, out if softmax else None)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        mat1, mat2, probs = ctx.saved_tensors
+        M, N, K, a1, a2, ao, ta, tb, H = ctx.meta
+        g = grad_out.contiguous()
+        if ctx.softmax:
+            # d(scores * scale) from d(probabilities), then the GEMM backward carries the scale
+            key = ("smx_bwd_of_gemm", M.tobytes(), N.tobytes(), ao.tobytes(), H, g.dtype, str(g.device))
+            sp = _cached(key, lambda: SoftmaxPlan(M, N, H, g.dtype, accum=ao, device=g.device))
+            g = sp.run_backward(probs.to(g.dtype), g)
+        g1, g2 = _gemm_backward(ctx.meta, mat1, mat2, g, ctx.scale)
+        return g1.reshape(ctx.lead[0]).to(mat1.dtype), g2.reshape(ctx.lead[1]).to(mat2.dtype), None, None, None
+
+
+class _BlockSoftmaxFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, src, plan, scale):
+        out = plan.run(src, scale=scale)
+        ctx.plan, ctx.scale = plan, scale
+        ctx.lead = src.shape
+        ctx.save_for_backward(out)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (out,) = ctx.saved_tensors
+        g = grad_out.contiguous()
+        plan = ctx.plan
+        if g.dtype != plan.dtype:  # upstream converts the saved result to the gradient's dtype
+            key = ("smx_bwd_cast", plan.rows.tobytes(), plan.cols.tobytes(), plan.offsets.tobytes(), plan.H, g.dtype,
+                   str(g.device))
+            plan = _cached(key, lambda: SoftmaxPlan(ctx.plan.rows, ctx.plan.cols, ctx.plan.H, g.dtype,
+                                                    accum=ctx.plan.offsets, device=g.device))
+        return plan.run_backward(out.to(g.dtype), g, scale=ctx.scale).reshape(ctx.lead), None, None
+
+
 def blockGEMM(mat1: torch.Tensor, mat2: torch.Tensor,
               mat1Accum: Optional[torch.Tensor] = None, mat2Accum: Optional[torch.Tensor] = None,
               outAccum: Optional[torch.Tensor] = None,
@@ -119,6 +187,8 @@ def blockGEMM(mat1: torch.Tensor, mat2: torch.Tensor,
     plan = _cached(key, build)
     if mat1.shape[-1] != plan.Dm1 and mat1.numel() != plan.H * plan.Dm1:
         raise RuntimeError(f"mat1.size(-1) = {mat1.shape[-1]} does not match mat1Accum[-1] = {plan.Dm1}")
+    if torch.is_grad_enabled() and (mat1.requires_grad or mat2.requires_grad):
+        return _BlockGEMMFn.apply(mat1, mat2, plan, scale, bool(softmax))
     return plan.run(mat1, mat2, scale=scale)
 
 
@@ -144,6 +214,8 @@ def blockSoftmax(src: torch.Tensor, rowList: torch.Tensor, colList: torch.Tensor
         return SoftmaxPlan(rows, cols, src.numel() // D, src.dtype, accum=srcAccum, device=src.device)
 
     plan = _cached(key, build)
+    if out is None and torch.is_grad_enabled() and src.requires_grad:
+        return _BlockSoftmaxFn.apply(src, plan, scale)
     return plan.run(src, out=out, scale=scale)
 
 

@@ -442,3 +442,36 @@ extern "C" int blk_softmax_run(const blk_plan_t* p, const void* src, void* out, 
     if (e != cudaSuccess) return cuda_fail("softmax launch", e);
     return BLK_OK;
 }
+
+extern "C" int blk_softmax_backward_run(const blk_plan_t* p, const void* out, const void* grad_out, void* grad_src,
+                                        float scale, void* cuda_stream) {
+    if (!p || p->kind != 1) {
+        blk_set_error("blk_softmax_backward_run: not a softmax plan");
+        return BLK_ERR_INVALID;
+    }
+    if (p->device < 0) {
+        blk_set_error("blk_softmax_backward_run: the plan was created without a device");
+        return BLK_ERR_INVALID;
+    }
+    if (p->smx_chunks.empty() || p->H == 0) return BLK_OK;
+    if (!out || !grad_out || !grad_src) {
+        blk_set_error("blk_softmax_backward_run: null buffer");
+        return BLK_ERR_INVALID;
+    }
+    if (!aligned16(out) || !aligned16(grad_out) || !aligned16(grad_src)) {
+        blk_set_error("blk_softmax_backward_run: device pointers must be 16-byte aligned");
+        return BLK_ERR_UNALIGNED;
+    }
+    BlkSmxBwdParams xp{};
+    xp.out = out;
+    xp.grad_out = grad_out;
+    xp.grad_src = grad_src;
+    xp.chunks = p->d_smx_chunks;
+    xp.D = p->Dm1;
+    xp.num_chunks = (int)p->smx_chunks.size();
+    xp.H = (int)p->H;
+    xp.scale = scale;
+    cudaError_t e = blk_launch_softmax_bwd(xp, p->dtype_in, reinterpret_cast<cudaStream_t>(cuda_stream));
+    if (e != cudaSuccess) return cuda_fail("softmax backward launch", e);
+    return BLK_OK;
+}

@@ -83,7 +83,20 @@ struct BlkSmxParams {
     float scale;
 };
 
+// Backward of the row softmax: grad_src = scale * (grad_out - rowsum(out * grad_out)) * out.
+struct BlkSmxBwdParams {
+    const void* out;       // forward result (probabilities)
+    const void* grad_out;  // gradient with respect to the forward result
+    void* grad_src;        // may alias grad_out
+    const BlkSmxChunk* chunks;
+    int64_t D;
+    int num_chunks;
+    int H;
+    float scale;
+};
+
 cudaError_t blk_launch_gemm_tile(const BlkGemmParams& p, int dtype_in, int ta, int tb, cudaStream_t st);
+cudaError_t blk_launch_softmax_bwd(const BlkSmxBwdParams& p, int dtype, cudaStream_t st);
 cudaError_t blk_launch_gemm_simt(const BlkSimtParams& p, cudaStream_t st);
 cudaError_t blk_launch_scores_small(const BlkSmallParams& p, int dtype_in, int K, int bucket, int sms,
                                     cudaStream_t st);

@@ -100,6 +100,7 @@ class GemmPlan(_Plan):
         self.dtype_in = dtype_in
         self.dtype_out = dtype_out if dtype_out is not None else dtype_in
         self.softmax = bool(softmax)
+        self.ta, self.tb = bool(transpose1), bool(transpose2)
         self.device = torch.device(device) if device is not None else None
         a1 = a2 = ao = None
         if accum is not None:
@@ -200,3 +201,29 @@ class SoftmaxPlan(_Plan):
             L.check(L.lib.blk_softmax_run(self._h, C.c_void_p(src.data_ptr()), C.c_void_p(out.data_ptr()),
                                           C.c_float(scale), C.c_void_p(_stream_ptr(src.device))))
         return out
+
+    def run_backward(self, out: torch.Tensor, grad_out: torch.Tensor, grad_src: Optional[torch.Tensor] = None,
+                     scale: float = 1.0) -> torch.Tensor:
+        """``grad_src = scale * (grad_out - rowsum(out * grad_out)) * out`` for the forward result ``out`` of
+        ``run(src, scale=scale)`` (upstream ``sparseBlockedSoftmaxBackwardLaunch``, csrc/cuda/spBlkSoftmax.cu:418-459)."""
+        if self.device is None:
+            raise RuntimeError("this plan was built without a device")
+        for name, t in (("out", out), ("grad_out", grad_out)):
+            if not t.is_cuda or not t.is_contiguous() or t.dtype != self.dtype or t.numel() != self.H * self.D:
+                raise RuntimeError(f"{name} must be a contiguous CUDA tensor of the plan's dtype with H*D elements")
+        if grad_src is None:
+            grad_src = torch.empty((self.H, self.D), dtype=self.dtype, device=out.device)
+        elif (not grad_src.is_cuda or not grad_src.is_contiguous() or grad_src.dtype != self.dtype
+              or grad_src.numel() != out.numel()):
+            raise RuntimeError("grad_src must be a contiguous CUDA tensor shaped like out")
+        if out.data_ptr() % 16:
+            out = out.clone()
+        if grad_out.data_ptr() % 16:
+            grad_out = grad_out.clone()
+        if grad_src.data_ptr() % 16:
+            raise RuntimeError("grad_src must be 16-byte aligned")
+        with torch.cuda.device(out.device):
+            L.check(L.lib.blk_softmax_backward_run(self._h, C.c_void_p(out.data_ptr()), C.c_void_p(grad_out.data_ptr()),
+                                                   C.c_void_p(grad_src.data_ptr()), C.c_float(scale),
+                                                   C.c_void_p(_stream_ptr(out.device))))
+        return grad_src

@@ -134,6 +134,15 @@ BLK_API int blk_softmax_plan_create(blk_plan_t** plan, const int64_t* rows, cons
 BLK_API int blk_softmax_run(const blk_plan_t* plan, const void* src, void* out, float scale,
                     void* cuda_stream);
 
+/* Backward of blk_softmax_run: grad_src = scale * (grad_out - rowsum(out *
+ * grad_out)) * out, with `out` the forward result, fp32 arithmetic, one
+ * rounding to dtype; `plan` is the forward call's plan.  Replaces upstream
+ * sparseBlockedSoftmaxBackwardLaunch, csrc/cuda/spBlkSoftmax.cu:418-459
+ * (declared csrc/sparseBlockedAttention.h:21; upstream has no scale, i.e.
+ * scale = 1).  grad_src may equal grad_out. */
+BLK_API int blk_softmax_backward_run(const blk_plan_t* plan, const void* out, const void* grad_out,
+                             void* grad_src, float scale, void* cuda_stream);
+
 /* The row softmax for callers that cannot allocate device memory when they
  * need it: a host whose runtime owns all device memory through its own arena,
  * a plugin running inside another component's pool, a latency-critical path

@@ -15,7 +15,10 @@ torch check loop, and this file restates that loop:
   and ``:85-91``;
 * lists from offsets (float32 ``sqrt`` formula): ``csrc/sparseBlockedAttention.cpp:30-40``;
 * device addressing the loop must agree with: ``csrc/cuda/spBlkGEMM.cu:141-150``
-  (segment start = head * D + accum[seg]) and ``csrc/cuda/spBlkSoftmax.cu:107``.
+  (segment start = head * D + accum[seg]) and ``csrc/cuda/spBlkSoftmax.cu:107``;
+* backward pair: the argument permutation of ``csrc/sparseBlockedAttention.cpp:52-72`` and
+  the row arithmetic of ``csrc/cuda/spBlkSoftmax.cu:140-180``; these two are additionally
+  checked against torch autograd of the forward restatement (``tests/test_oracle.py``).
 
 Parity pin: the upstream repository holds no golden vectors or known-answer
 files (its only checks are run-time comparisons with torch on unseeded data),
@@ -189,6 +192,47 @@ def block_attention(q, k, v, nList, d: int, scale: float, p_dtype=None,
     Pr = P.to(p_dtype).to(compute_dtype) if p_dtype is not None else P
     O = block_gemm(Pr, v, n, dl, n, transpose2=True, compute_dtype=compute_dtype)
     return P, O
+
+
+def block_softmax_backward(out: torch.Tensor, grad_out: torch.Tensor, rowList, colList, srcAccum=None,
+                           scale: float = 1.0, compute_dtype=torch.float32) -> torch.Tensor:
+    """grad_src = scale * (grad_out - rowsum(out * grad_out)) * out per row of every block: the arithmetic of
+    upstream sparseBlockedSoftmaxBackward_warp (csrc/cuda/spBlkSoftmax.cu:140-180: fp32 dot product of the two
+    rows, then ``(dsrc - sum) * src``), with the forward scale folded in (upstream has none)."""
+    r = np.asarray(rowList, dtype=np.int64); c = np.asarray(colList, dtype=np.int64)
+    acc = softmax_offsets(r, c) if srcAccum is None else np.asarray(srcAccum, dtype=np.int64)
+    P = _as2d(out.detach().cpu(), int(acc[-1])).to(compute_dtype)
+    G = _as2d(grad_out.detach().cpu(), int(acc[-1])).to(compute_dtype)
+    H = P.shape[0]
+    res = torch.zeros_like(P)
+    for s in range(len(r)):
+        rows, cols = int(r[s]), int(c[s])
+        if rows == 0 or cols == 0:
+            continue
+        p = P[:, acc[s]:acc[s] + rows * cols].reshape(H, rows, cols)
+        g = G[:, acc[s]:acc[s] + rows * cols].reshape(H, rows, cols)
+        dot = (p * g).sum(-1, keepdim=True)
+        res[:, acc[s]:acc[s] + rows * cols] = ((g - dot) * p * scale).reshape(H, rows * cols)
+    return res
+
+
+def block_gemm_backward(mat1: torch.Tensor, mat2: torch.Tensor, grad_out: torch.Tensor, MList, NList, KList,
+                        accum1=None, accum2=None, accumOut=None, transpose1: bool = False,
+                        transpose2: bool = False, scale: float = 1.0,
+                        compute_dtype=torch.float32) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The two launches of upstream sparseBlockedGEMM::backward (csrc/sparseBlockedAttention.cpp:52-72), each
+    restated through :func:`block_gemm` with upstream's permuted arguments:
+    mat1Grad = gemm(outGrad, mat2; offsets (out, mat2, mat1); lists (M, K, N); False, not transpose2),
+    mat2Grad = gemm(outGrad, mat1; offsets (out, mat1, mat2); lists (N, K, M); True, not transpose1)."""
+    M = np.asarray(MList, dtype=np.int64); N = np.asarray(NList, dtype=np.int64)
+    K = np.asarray(KList, dtype=np.int64)
+    d1, d2, do = offsets_from_lists(M, N, K)
+    a1 = d1 if accum1 is None else np.asarray(accum1, dtype=np.int64)
+    a2 = d2 if accum2 is None else np.asarray(accum2, dtype=np.int64)
+    ao = do if accumOut is None else np.asarray(accumOut, dtype=np.int64)
+    g1 = block_gemm(grad_out, mat2, M, K, N, ao, a2, a1, False, not transpose2, scale=scale, compute_dtype=compute_dtype)
+    g2 = block_gemm(grad_out, mat1, N, K, M, ao, a1, a2, True, not transpose1, scale=scale, compute_dtype=compute_dtype)
+    return g1, g2
 
 
 # --------------------------------------------------------------------------

@@ -9,7 +9,7 @@
 // (csrc/sparseBlockedAttention.h:10) and which defines a debugging main().
 //
 // Exposed functions take the arguments of the launchers declared at
-// csrc/sparseBlockedAttention.h:18-20 in the same order.
+// csrc/sparseBlockedAttention.h:18-21 in the same order.
 #include "sparseBlockedAttention.h"
 
 PYBIND11_MODULE(blk_ref_ext, m) {
@@ -18,4 +18,6 @@ PYBIND11_MODULE(blk_ref_ext, m) {
           "sparseBlockedGEMMLaunch(mat1, mat2, mat1Accum, mat2Accum, outAccum, MList, NList, KList, transpose1, transpose2)");
     m.def("softmax_launch", &sparseBlockedSoftmaxLaunch,
           "sparseBlockedSoftmaxLaunch(src, accumSrc, rowList, colList)");
+    m.def("softmax_backward_launch", &sparseBlockedSoftmaxBackwardLaunch,
+          "sparseBlockedSoftmaxBackwardLaunch(out, dout, accumSrc, rowList, colList)");
 }

@@ -112,3 +112,55 @@ def test_exact_inverse_where_float32_formula_fails():
     assert ((Mf == M) | ~consistent).all()       # wherever upstream is self-consistent it equals the truth
     with pytest.raises(ValueError):
         O.lists_from_offsets_exact([0, 6], [0, 6], [0, 5])
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False)])
+def test_backward_restatements_against_autograd(ta, tb):
+    # the oracle's backward pair (upstream's permuted launches, upstream's softmax-backward arithmetic) against
+    # torch autograd of the forward restatement, float64
+    rs = np.random.RandomState(3)
+    M = rs.randint(1, 9, size=5); N = rs.randint(1, 9, size=5); K = rs.randint(1, 7, size=5)
+    H = 3
+    A = torch.randn(H, int((M * K).sum()), dtype=torch.float64, requires_grad=True)
+    B = torch.randn(H, int((N * K).sum()), dtype=torch.float64, requires_grad=True)
+
+    def fwd(a, b):
+        outs = []
+        o1 = o2 = 0
+        for m, n, k in zip(M, N, K):
+            m, n, k = int(m), int(n), int(k)
+            x = a[:, o1:o1 + m * k]; y = b[:, o2:o2 + n * k]
+            x = x.reshape(H, k, m).transpose(1, 2) if ta else x.reshape(H, m, k)
+            y = y.reshape(H, k, n).transpose(1, 2) if tb else y.reshape(H, n, k)
+            outs.append((0.7 * x @ y.transpose(1, 2)).reshape(H, m * n))
+            o1 += m * k; o2 += n * k
+        return torch.cat(outs, 1)
+
+    C = fwd(A, B)
+    g = torch.randn_like(C)
+    C.backward(g)
+    g1, g2 = O.block_gemm_backward(A, B, g, M, N, K, transpose1=ta, transpose2=tb, scale=0.7,
+                                   compute_dtype=torch.float64)
+    # upstream lays both gradients out (m, k) / (n, k) row-major whatever the forward flags were
+    def relayout(grad, rows, cols, transposed):
+        if not transposed:
+            return grad
+        parts, o = [], 0
+        for r, c in zip(rows, cols):
+            r, c = int(r), int(c)
+            parts.append(grad[:, o:o + r * c].reshape(H, c, r).transpose(1, 2).reshape(H, r * c)); o += r * c
+        return torch.cat(parts, 1)
+    assert torch.allclose(g1, relayout(A.grad, M, K, ta), atol=1e-10)
+    assert torch.allclose(g2, relayout(B.grad, N, K, tb), atol=1e-10)
+
+    # softmax backward
+    X = torch.randn(H, int((M * N).sum()), dtype=torch.float64, requires_grad=True)
+    outs, o = [], 0
+    for m, n in zip(M, N):
+        m, n = int(m), int(n)
+        outs.append((1.3 * X[:, o:o + m * n].reshape(H, m, n)).softmax(-1).reshape(H, m * n)); o += m * n
+    P = torch.cat(outs, 1)
+    gp = torch.randn_like(P)
+    P.backward(gp)
+    got = O.block_softmax_backward(P, gp, M, N, scale=1.3, compute_dtype=torch.float64)
+    assert torch.allclose(got, X.grad, atol=1e-10)

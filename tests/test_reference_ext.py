@@ -18,6 +18,7 @@ import torch
 
 from helpers import O, ROOT, assert_probs_close, assert_scores_close, packed_inputs
 from blockedattention_b200 import blockGEMM, blockSoftmax
+from blockedattention_b200.plan import SoftmaxPlan
 
 pytestmark = pytest.mark.gpu
 REF_DIR = os.path.join(ROOT, "oracle", "_ref")
@@ -98,6 +99,32 @@ def test_softmax_three_way(cuda_device, ref, dtype, rows, cols, H):
     assert_probs_close(theirs, oracle, "upstream kernels vs oracle")       # pins the oracle
     assert_probs_close(ours, oracle, "new kernels vs oracle")
     assert_probs_close(ours, theirs.float(), "new kernels vs upstream kernels")
+
+
+@pytest.mark.parametrize("dtype,rows,cols,H", [
+    (torch.float32, [33, 99, 64], [64, 64, 64], 16),
+    (torch.float16, [40, 7, 200, 3], [24, 128, 1000, 2], 3),   # at most 1024 columns: upstream's warp kernel
+])
+def test_softmax_backward_three_way(cuda_device, ref, dtype, rows, cols, H):
+    if not hasattr(ref, "softmax_backward_launch"):
+        pytest.skip("oracle/_ref was built before the backward launcher was bound: rerun python oracle/build_ref.py")
+    dev = cuda_device
+    rows = np.asarray(rows, np.int64); cols = np.asarray(cols, np.int64)
+    g = torch.Generator().manual_seed(2)
+    X = torch.randn((H, int((rows * cols).sum())), generator=g)
+    P = O.block_softmax(X, rows, cols).to(dtype)
+    G = torch.randn(P.shape, generator=g).to(dtype)
+    acc = O.softmax_offsets(rows, cols)
+    oracle = O.block_softmax_backward(P, G, rows, cols)
+    tr, tc, ta = dev_lists(dev, rows, cols, acc)
+    theirs = ref.softmax_backward_launch(P.to(dev), G.to(dev), ta, tr, tc)
+    torch.cuda.synchronize()
+    ours = SoftmaxPlan(rows, cols, H, dtype, device=dev).run_backward(P.to(dev), G.to(dev))
+    tol = 1e-5 if dtype == torch.float32 else 4e-3   # upstream multiplies the two 16-bit rows in 16 bits
+    for name, got in (("upstream kernel vs oracle", theirs), ("new kernel vs oracle", ours)):
+        err = float((got.float().cpu() - oracle).abs().max())
+        assert err <= tol, f"{name}: {err}"
+    assert float((ours.float() - theirs.float()).abs().max()) <= tol
 
 
 def test_molecular_chain_three_way(cuda_device, ref):
