@@ -597,16 +597,7 @@ EncodeTiledFn encode_fn() {
 // View of a packed operand as (k, row, head): K contiguous elements per row, D elements per head.
 bool make_map(CUtensorMap* map, const void* base, int bf16, int64_t K, int64_t rows, int64_t H, int64_t D,
               int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)H};
-    const cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)D * 2};
-    const cuuint32_t box[3] = {(cuuint32_t)UM_BK, (cuuint32_t)box_rows, 1};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return blk_make_row_map(map, base, bf16, K, rows, H, D, UM_BK, box_rows);
 }
 
 template <typename Tag, bool OUT32>
@@ -621,6 +612,20 @@ cudaError_t launch(const BlkUmmaParams& p, const CUtensorMap& a, const CUtensorM
 }
 
 }  // namespace
+
+bool blk_make_row_map(CUtensorMap_st* map, const void* base, int bf16, int64_t K, int64_t rows, int64_t H, int64_t D,
+                      int box_k, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)H};
+    const cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)D * 2};
+    const cuuint32_t box[3] = {(cuuint32_t)box_k, (cuuint32_t)box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p, const void* A, const void* B, int64_t Dm1, int64_t Dm2,
                                  int sms, cudaStream_t st) {

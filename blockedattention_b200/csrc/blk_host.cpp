@@ -352,7 +352,12 @@ int blk_build_gemm_schedule(blk_plan* p) {
     // K = 64 with 16-bit output: the small segments run on the pipelined kernel, grouped into packs of
     // consecutive segments whose operands are contiguous in memory (one bulk copy per operand per pack).
     p->small_pipe = 0;
-    if (p->small_K == 64 && p->dtype_out != BLK_F32 && !blk_env_flag("BLK_DISABLE_PIPE") && !small_segs.empty()) {
+    // The pack kernel fetches operands through (64, rows, heads) tensor maps: every small segment and every head
+    // strip must start on a row of that view.
+    bool rows_ok = p->Dm1 % 64 == 0 && p->Dm2 % 64 == 0 && p->Dm1 / 64 < INT32_MAX && p->Dm2 / 64 < INT32_MAX;
+    for (size_t q = 0; rows_ok && q < small_segs.size(); ++q)
+        rows_ok = p->segs[small_segs[q]].offA % 64 == 0 && p->segs[small_segs[q]].offB % 64 == 0;
+    if (p->small_K == 64 && p->dtype_out != BLK_F32 && rows_ok && !blk_env_flag("BLK_DISABLE_PIPE") && !small_segs.empty()) {
         p->small_pipe = 1;
         struct Tmp { BlkPack pk; std::vector<BlkPackBlock> blocks; double cost; };
         std::vector<Tmp> tmp;

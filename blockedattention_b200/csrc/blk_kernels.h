@@ -95,6 +95,13 @@ struct BlkSmxBwdParams {
     float scale;
 };
 
+// Tensor map (128-byte swizzle) over a packed 16-bit operand viewed as (k, row, head): K contiguous elements per
+// row, D elements per head, boxes of box_k x box_rows x 1.  False when the driver's encoder is unavailable or
+// rejects the view.  Defined in blk_gemm_umma.cu.
+struct CUtensorMap_st;
+bool blk_make_row_map(CUtensorMap_st* map, const void* base, int bf16, int64_t K, int64_t rows, int64_t H, int64_t D,
+                      int box_k, int box_rows);
+
 cudaError_t blk_launch_gemm_tile(const BlkGemmParams& p, int dtype_in, int ta, int tb, cudaStream_t st);
 cudaError_t blk_launch_softmax_bwd(const BlkSmxBwdParams& p, int dtype, cudaStream_t st);
 cudaError_t blk_launch_gemm_simt(const BlkSimtParams& p, cudaStream_t st);

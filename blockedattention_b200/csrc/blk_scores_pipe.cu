@@ -6,31 +6,37 @@
 // most 16 blocks of up to 16 first-operand rows of one segment each.  One
 // persistent CTA per SM walks its share of the cost-sorted (pack, head) list:
 //   warp 0      producer: one lane brings each pack into a 4-slot shared-memory
-//               ring with three bulk asynchronous copies (first operands,
-//               second operands, the pack's block records) that complete on
-//               the slot's mbarrier -- few, large copies keep the copy engine
-//               at memory speed, and the latency is paid by the ring instead of
-//               by the registers and occupancy of the arithmetic warps;
-//   warps 1-16  consumers: each takes one block of a pack, computes it as the
-//               register-fed small kernel does (k-permuted 128-bit fragment
-//               reads, here from shared memory; mma.sync.m16n8k16; softmax in
-//               registers; one copy of the tile code for every shape), lays the
-//               result out over the block's own first-operand rows (dead
-//               once their fragments are in registers), and copies it to global
-//               memory as aligned 16-byte vectors, re-aligning on the fly.
-// The consumers claim a pack's blocks through a per-slot counter, heaviest block
-// first, so a warp that finishes early takes more.  Every consumer arrives on
-// every slot's "empty" barrier, so a slot is reused only when all sixteen are
-// done with it; every wait is bounded and reports through the status word.
+//               ring with tiled tensor-map copies (cp.async.bulk.tensor, boxes
+//               of 64 / 32 / 16 rows of the (64, rows, heads) view of each
+//               operand, 128-byte swizzle) plus one bulk copy of the pack's
+//               block records, all completing on the slot's mbarrier -- the
+//               memory latency is paid by the ring instead of by the registers
+//               and occupancy of the arithmetic warps;
+//   warps 1-16  consumers in two groups (a group owns two slots, so a warp
+//               visits every other unit): each claims blocks of the pack
+//               through a per-slot counter, heaviest first, reads mma.sync
+//               fragments with ldmatrix (conflict-free under the swizzle),
+//               does the softmax in registers (only the tile arithmetic is
+//               specialised by tile count, behind one jump per block), lays the
+//               result out over the block's own first-operand rows (dead once
+//               their fragments are in registers) at the output's 16-byte
+//               misalignment, and copies it to global memory as aligned 16-byte
+//               vectors.
+// Every consumer of a group arrives on the "empty" barrier of the group's
+// slots, so a slot is reused only when all eight are done with it; every wait
+// is bounded and reports through the status word.
 //
 // Same arithmetic and the same upstream counterparts as blk_scores_small.cu.
+#include <cuda.h>
+
+#include <type_traits>
+
 #include "blk_device.cuh"
 #include "blk_kernels.h"
 
 namespace {
 
 constexpr int PK = 64;  // contraction length handled here
-constexpr int PKC = PK / 32;
 constexpr int ROWB = PK * 2;  // bytes per operand row
 #ifndef BLK_PIPE_CONSUMERS
 #define BLK_PIPE_CONSUMERS 16
@@ -41,8 +47,10 @@ constexpr int ROWB = PK * 2;  // bytes per operand row
 constexpr int P_CONSUMERS = BLK_PIPE_CONSUMERS;
 constexpr int P_THREADS = 32 * (1 + P_CONSUMERS);
 constexpr int P_OPER_BYTES = BLK_PACK_ROWS * ROWB;  // 24 KB per operand per slot
-constexpr int P_REC_BYTES = BLK_PACK_BLOCKS * (int)sizeof(BlkPackBlock);
+constexpr int P_REC_BYTES = 1024;  // block records, padded so that every slot starts on a swizzle-atom boundary
+static_assert(BLK_PACK_BLOCKS * (int)sizeof(BlkPackBlock) <= P_REC_BYTES, "record area");
 constexpr int P_SLOT_BYTES = 2 * P_OPER_BYTES + P_REC_BYTES;
+static_assert(P_SLOT_BYTES % 1024 == 0 && P_OPER_BYTES % 1024 == 0, "128-byte swizzle needs 1024-byte aligned regions");
 constexpr int P_SLOTS = 4;
 constexpr int P_TAIL_PAD = 1024;  // second-operand rows are read up to 7 rows past a run's end
 constexpr int P_GROUPS = BLK_PIPE_GROUPS;        // consumer groups; unit u belongs to group u % P_GROUPS
@@ -87,6 +95,26 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
+}
+// Tiled tensor-map copy global -> shared of one box at (k = 0, row, head), completing on an mbarrier.
+__device__ __forceinline__ void tma_rows(uint32_t dst, const CUtensorMap* map, uint32_t bar, int row, int head) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(row), "r"(head)
+        : "memory");
+}
+// Brings `rows` rows starting at row `row0` of a head's operand into shared memory at dst as boxes of 64, 32 and
+// 16 rows (each box a whole number of 1024-byte swizzle atoms); returns the bytes that will arrive.
+__device__ __forceinline__ uint32_t tma_run(uint32_t dst, const CUtensorMap* m64, const CUtensorMap* m32,
+                                            const CUtensorMap* m16, uint32_t bar, int row0, int rows, int head) {
+    int r = 0;
+    while (r < rows) {
+        const int rem = rows - r;
+        const int box = rem > 48 ? 64 : (rem > 16 ? 32 : 16);
+        tma_rows(dst + r * ROWB, box == 64 ? m64 : (box == 32 ? m32 : m16), bar, row0 + r, head);
+        r += box;
+    }
+    return (uint32_t)r * ROWB;
 }
 // Shared-memory stores by 32-bit address, and predicated global stores as single instructions.
 __device__ __forceinline__ void sts_b32(uint32_t addr, uint32_t v) {
@@ -147,20 +175,19 @@ __device__ __forceinline__ void pk_mma0<BlkBf16Tag>(float (&d)[4], uint32_t a0, 
 // stores (rows g and g + 8 of the block at shared addresses s0a / s1a).  Columns 8 (NT - 1) + 2 t and + 1 of the
 // last tile exist when last0 / last1; stores that must not land go to `scratch`.
 template <typename Tag, int NT, bool SOFTMAX>
-__device__ __forceinline__ void pack_tiles(const uint32_t (&af)[2 * PKC][4], const unsigned char* lb, float sl, bool last0,
+__device__ __forceinline__ void pack_tiles(const uint32_t (&af)[PK / 16][4], uint32_t b0, uint32_t b1, float sl, bool last0,
                                            bool last1, bool pairs, uint32_t s0a, uint32_t s1a, uint32_t scratch) {
     float acc[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
-#pragma unroll
-        for (int c = 0; c < PKC; ++c) {
-            const uint4 b = *reinterpret_cast<const uint4*>(lb + j * 8 * ROWB + 64 * c);
-            if (c == 0)
-                pk_mma0<Tag>(acc[j], af[0][0], af[0][1], af[0][2], af[0][3], b.x, b.y);
-            else
-                pk_mma<Tag>(acc[j], af[2 * c][0], af[2 * c][1], af[2 * c][2], af[2 * c][3], b.x, b.y);
-            pk_mma<Tag>(acc[j], af[2 * c + 1][0], af[2 * c + 1][1], af[2 * c + 1][2], af[2 * c + 1][3], b.z, b.w);
-        }
+        // rows 8 j .. 8 j + 7 of the second operand: k 0-31 through b0, k 32-63 through b1
+        uint32_t m0[4], m1[4];
+        blk_ldmatrix_x4(m0, b0 + j * 8 * ROWB);
+        blk_ldmatrix_x4(m1, b1 + j * 8 * ROWB);
+        pk_mma0<Tag>(acc[j], af[0][0], af[0][1], af[0][2], af[0][3], m0[0], m0[1]);
+        pk_mma<Tag>(acc[j], af[1][0], af[1][1], af[1][2], af[1][3], m0[2], m0[3]);
+        pk_mma<Tag>(acc[j], af[2][0], af[2][1], af[2][2], af[2][3], m1[0], m1[1]);
+        pk_mma<Tag>(acc[j], af[3][0], af[3][1], af[3][2], af[3][3], m1[2], m1[3]);
     }
     float r0 = sl, r1 = sl;
     if (SOFTMAX) {
@@ -219,26 +246,25 @@ __device__ __forceinline__ void pack_tiles(const uint32_t (&af)[2 * PKC][4], con
 // stored and such columns are masked before the row reduction.  The result is staged over the block's own
 // first-operand rows (M * N * 2 <= M * 128 bytes) and copied to the output at element cbase.
 template <typename Tag, bool SOFTMAX, bool FLIP>
-__device__ __forceinline__ void pack_block(void* C, unsigned char* pA, const unsigned char* pB, int64_t cbase, int M,
-                                           int N, float sl, uint32_t scratch, int lane) {
+__device__ __forceinline__ void pack_block(void* C, unsigned char* pA, uint32_t sA0, uint32_t sB0, int rowA, int rowB,
+                                           int64_t cbase, int M, int N, float sl, uint32_t scratch, int lane) {
     const int g = lane >> 2, t = lane & 3;
     const int nt = (N + 7) >> 3;
 
-    uint32_t af[2 * PKC][4];
+    // Operand rows sit in shared memory under the 128-byte swizzle of the tensor-map copy: the 16-byte chunk c of
+    // row r (row counted from the 1024-byte aligned start of the operand's region) is at chunk c ^ (r & 7).
+    // ldmatrix lane l addresses row l % 16 and k-chunk l / 16 of a 16 x 16 first-operand tile.
+    uint32_t af[PK / 16][4];
     {
-        const unsigned char* la = pA + g * ROWB + 16 * t;
+        const uint32_t ra = (uint32_t)rowA + (lane & 15);
+        const uint32_t base = sA0 + ra * ROWB, x0 = (((uint32_t)lane >> 4) ^ (ra & 7u)) << 4;
 #pragma unroll
-        for (int c = 0; c < PKC; ++c) {
-            const uint4 lo = *reinterpret_cast<const uint4*>(la + 64 * c);
-            const uint4 hi = *reinterpret_cast<const uint4*>(la + 8 * ROWB + 64 * c);
-            af[2 * c][0] = lo.x; af[2 * c][1] = hi.x; af[2 * c][2] = lo.y; af[2 * c][3] = hi.y;
-            af[2 * c + 1][0] = lo.z; af[2 * c + 1][1] = hi.z; af[2 * c + 1][2] = lo.w; af[2 * c + 1][3] = hi.w;
-        }
+        for (int ks = 0; ks < PK / 16; ++ks) blk_ldmatrix_x4(af[ks], base + (x0 ^ (uint32_t)(ks << 5)));
         if (SOFTMAX && FLIP) {  // negative scale: softmax of the negated scores
 #pragma unroll
-            for (int c = 0; c < 2 * PKC; ++c)
+            for (int ks = 0; ks < PK / 16; ++ks)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) af[c][e] ^= 0x80008000u;
+                for (int e = 0; e < 4; ++e) af[ks][e] ^= 0x80008000u;
         }
     }
     // The block's M * N results are contiguous in the output, starting mis bytes into a 16-byte vector.  They
@@ -249,7 +275,10 @@ __device__ __forceinline__ void pack_block(void* C, unsigned char* pA, const uns
     const int mis = (int)(g0 & 15);
     const int so = mis + nbytes <= M * ROWB ? mis : 0;
     {
-        const unsigned char* lb = pB + g * ROWB + 16 * t;
+        // second operand: lane l addresses row l % 8 of an 8-row tile and k-chunk l / 8 (+ 4 for the upper half of k)
+        const uint32_t rb = (uint32_t)rowB + (lane & 7);
+        const uint32_t bx = (((uint32_t)lane >> 3) ^ (rb & 7u)) << 4;
+        const uint32_t b0 = sB0 + rb * ROWB + bx, b1 = sB0 + rb * ROWB + (bx ^ 64u);
         const bool last0 = 8 * (nt - 1) + 2 * t < N, last1 = 8 * (nt - 1) + 2 * t + 1 < N;
         // rows g and g + 8 of the staged block; a row past M is pointed at the scratch area instead
         const uint32_t row0 = blk_smem_u32(pA) + (uint32_t)(so + (g * N + 2 * t) * 2);
@@ -257,14 +286,14 @@ __device__ __forceinline__ void pack_block(void* C, unsigned char* pA, const uns
         const bool pairs = ((N | (so >> 1)) & 1) == 0;
         // one jump to the code for this tile count; only the tile arithmetic is specialised
         switch (nt) {
-            case 1: pack_tiles<Tag, 1, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            case 2: pack_tiles<Tag, 2, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            case 3: pack_tiles<Tag, 3, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            case 4: pack_tiles<Tag, 4, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            case 5: pack_tiles<Tag, 5, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            case 6: pack_tiles<Tag, 6, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            case 7: pack_tiles<Tag, 7, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            default: pack_tiles<Tag, 8, SOFTMAX>(af, lb, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 1: pack_tiles<Tag, 1, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 2: pack_tiles<Tag, 2, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 3: pack_tiles<Tag, 3, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 4: pack_tiles<Tag, 4, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 5: pack_tiles<Tag, 5, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 6: pack_tiles<Tag, 6, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 7: pack_tiles<Tag, 7, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            default: pack_tiles<Tag, 8, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
         }
     }
     __syncwarp();
@@ -303,8 +332,16 @@ __device__ __forceinline__ void pack_block(void* C, unsigned char* pA, const uns
 }
 
 template <typename Tag, bool SOFTMAX, bool FLIP>
-__global__ void __launch_bounds__(P_THREADS, 1) blk_scores_pipe_kernel(const BlkPackParams p) {
-    extern __shared__ __align__(128) unsigned char pipe_smem[];
+__global__ void __launch_bounds__(P_THREADS, 1)
+blk_scores_pipe_kernel(const BlkPackParams p, const __grid_constant__ CUtensorMap mA64,
+                       const __grid_constant__ CUtensorMap mA32, const __grid_constant__ CUtensorMap mA16,
+                       const __grid_constant__ CUtensorMap mB64, const __grid_constant__ CUtensorMap mB32,
+                       const __grid_constant__ CUtensorMap mB16) {
+    extern __shared__ __align__(1024) unsigned char pipe_smem[];  // the swizzled operand regions need this alignment
+    if (blk_smem_u32(pipe_smem) & 1023u) {  // cannot happen with the alignment above; the swizzle relies on it
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, 13);
+        return;
+    }
     unsigned char* ctl = pipe_smem + P_SLOTS * P_SLOT_BYTES + P_TAIL_PAD;
     uint64_t* bars = reinterpret_cast<uint64_t*>(ctl);  // [s] full, [P_SLOTS + s] empty
     volatile int* abort_flag = reinterpret_cast<volatile int*>(ctl + 16 * P_SLOTS);
@@ -347,13 +384,14 @@ __global__ void __launch_bounds__(P_THREADS, 1) blk_scores_pipe_kernel(const Blk
                 if (w + G < total) nxt = p.packs[pack];  // next record in flight during this unit's wait
                 const uint32_t s = u % P_SLOTS;
                 if (!pb_wait(empty_bar(s), ((u / P_SLOTS) & 1u) ^ 1u, abort_flag, p.status, 11)) break;
-                const uint32_t bytesA = (uint32_t)pk.rowsA * ROWB, bytesB = (uint32_t)pk.rowsB * ROWB;
                 const uint32_t bytesR = (uint32_t)pk.nblocks * (uint32_t)sizeof(BlkPackBlock);
                 const uint32_t dst = smem0 + s * P_SLOT_BYTES;
                 *reinterpret_cast<volatile int*>(next_block + s) = 0;  // ordered before the consumers' claims by the barrier
+                // rows are fetched in whole boxes: up to 15 rows past the run's end come along (zeros past the strip)
+                const uint32_t bytesA = (uint32_t)((pk.rowsA + 15) & ~15) * ROWB, bytesB = (uint32_t)((pk.rowsB + 15) & ~15) * ROWB;
                 pb_expect_tx(full_bar(s), bytesA + bytesB + bytesR);
-                bulk_g2s(dst, p.A + ((int64_t)hd_now * p.Dm1 + pk.offA), bytesA, full_bar(s));
-                bulk_g2s(dst + P_OPER_BYTES, p.B + ((int64_t)hd_now * p.Dm2 + pk.offB), bytesB, full_bar(s));
+                tma_run(dst, &mA64, &mA32, &mA16, full_bar(s), (int)(pk.offA / PK), pk.rowsA, (int)hd_now);
+                tma_run(dst + P_OPER_BYTES, &mB64, &mB32, &mB16, full_bar(s), (int)(pk.offB / PK), pk.rowsB, (int)hd_now);
                 bulk_g2s(dst + 2 * P_OPER_BYTES, p.blocks + pk.first_block, bytesR, full_bar(s));
             }
         }
@@ -370,6 +408,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) blk_scores_pipe_kernel(const Blk
             if (hd >= H) hd -= H;
             if (!pb_wait(full_bar(s), (u / P_SLOTS) & 1u, abort_flag, p.status, 12)) break;
             unsigned char* slot = pipe_smem + s * P_SLOT_BYTES;
+            const uint32_t sslot = smem0 + s * P_SLOT_BYTES;
             const BlkPackBlock* recs = reinterpret_cast<const BlkPackBlock*>(slot + 2 * P_OPER_BYTES);
             const int nb = recs[0].nblocks;
             // the group's warps claim the pack's blocks (widest first) one at a time: a warp that finishes early takes more
@@ -379,8 +418,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) blk_scores_pipe_kernel(const Blk
                 b = __shfl_sync(0xffffffffu, b, 0);
                 if (b >= nb) break;
                 const BlkPackBlock r = recs[b];
-                pack_block<Tag, SOFTMAX, FLIP>(p.C, slot + r.rowA * ROWB, slot + P_OPER_BYTES + r.rowB * ROWB, hbase + r.offC, r.M,
-                                               r.N, sl, scratch, lane);
+                pack_block<Tag, SOFTMAX, FLIP>(p.C, slot + r.rowA * ROWB, sslot, sslot + P_OPER_BYTES, r.rowA, r.rowB,
+                                               hbase + r.offC, r.M, r.N, sl, scratch, lane);
             }
             // this warp's reads and writes of the slot are done: order them before the next bulk copy into it
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -399,11 +438,19 @@ template <typename Tag>
 cudaError_t launch_pipe(const BlkPackParams& p, int sms, cudaStream_t st) {
     const int64_t total = (int64_t)p.num_packs * p.H;
     if (total == 0) return cudaSuccess;
+    // both operands as (64, rows, heads) views with boxes of 64, 32 and 16 rows
+    CUtensorMap mA[3], mB[3];
+    const int bf16 = std::is_same<Tag, BlkBf16Tag>::value ? 1 : 0;
+    const int box_rows[3] = {64, 32, 16};
+    for (int i = 0; i < 3; ++i)
+        if (!blk_make_row_map(&mA[i], p.A, bf16, PK, p.Dm1 / PK, p.H, p.Dm1, PK, box_rows[i]) ||
+            !blk_make_row_map(&mB[i], p.B, bf16, PK, p.Dm2 / PK, p.H, p.Dm2, PK, box_rows[i]))
+            return cudaErrorInvalidValue;
     const dim3 grid((unsigned)(total < sms ? total : sms)), block(P_THREADS);
     auto go = [&](auto kern) -> cudaError_t {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        kern<<<grid, block, P_SMEM_BYTES, st>>>(p);
+        kern<<<grid, block, P_SMEM_BYTES, st>>>(p, mA[0], mA[1], mA[2], mB[0], mB[1], mB[2]);
         return cudaGetLastError();
     };
     if (p.epi != BLK_EPI_SOFTMAX) return go(blk_scores_pipe_kernel<Tag, false, false>);
