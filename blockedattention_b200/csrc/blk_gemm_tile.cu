@@ -3,9 +3,11 @@
 // alignment, either operand transposed, fp16/bf16 or fp32 output, scores or
 // fused row softmax).
 //
-// One CTA (4 warps) owns a 64-row block of one segment of one head and a
-// 128-column tile of it; warp w owns rows 16w..16w+15 across all 128 columns,
-// so a row's reduction never leaves a quad.  Operands are staged through
+// One CTA owns a 64-row block of one segment of one head and a 128-column tile
+// of it.  With the softmax epilogue it has 4 warps and warp w owns rows
+// 16w..16w+15 across all 128 columns, so a row's reduction never leaves a quad;
+// for scores only it has 8 warps (each 16 rows x 64 columns), which doubles the
+// resident warps that hide the load latency of short contractions.  Operands are staged through
 // shared memory (register-staged double buffer; per operand, segment and head
 // either plain 16-byte global loads or, for rows that start at odd element
 // offsets, aligned 16-byte loads shifted into place in registers) and fed to
@@ -17,6 +19,8 @@
 //
 // Replaces upstream sparseBlockedHGEMM_half / _bf16 (csrc/cuda/spBlkGEMM.cu:424-817)
 // and, when fused, sparseBlockedSoftmax_warp/_block (csrc/cuda/spBlkSoftmax.cu:88-269).
+#include <type_traits>
+
 #include "blk_device.cuh"
 #include "blk_kernels.h"
 
@@ -61,19 +65,19 @@ __device__ __forceinline__ uint4 ldg8_any(const uint16_t* src, int nvalid) {
 // Register staging of an OUTER x INNER tile of a row-major matrix in units of eight 16-bit elements: one
 // 16-byte load per unit when the matrix is ALIGNED (16-byte aligned base and a pitch that is a multiple of
 // eight elements, so the inner extent is one too), the shifting load above otherwise.
-template <int OUTER, int INNER, bool ALIGNED>
+template <int OUTER, int INNER, bool ALIGNED, int NTHR>
 struct TileStage {
     static constexpr int UPR = INNER / 8;
     static constexpr int UNITS = OUTER * UPR;
-    static constexpr int PT = UNITS / NT;
-    static_assert(UNITS % NT == 0, "tile must divide among the threads");
+    static constexpr int PT = UNITS / NTHR;
+    static_assert(UNITS % NTHR == 0, "tile must divide among the threads");
     uint4 r[PT];
 
     __device__ __forceinline__ void load(const uint16_t* __restrict__ g, int64_t ld, int o0, int i0, int o_lim,
                                          int i_lim, int tid) {
 #pragma unroll
         for (int j = 0; j < PT; ++j) {
-            const int u = tid + j * NT;
+            const int u = tid + j * NTHR;
             const int o = o0 + u / UPR, i = i0 + (u % UPR) * 8;
             const uint16_t* src = g + (int64_t)o * ld + i;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -87,36 +91,37 @@ struct TileStage {
     __device__ __forceinline__ void store(uint16_t* s, int pitch, int tid) const {
 #pragma unroll
         for (int j = 0; j < PT; ++j) {
-            const int u = tid + j * NT;
+            const int u = tid + j * NTHR;
             *reinterpret_cast<uint4*>(s + (u / UPR) * pitch + (u % UPR) * 8) = r[j];
         }
     }
 };
 
-// One BK-deep step of the warp's 16 x 128 block from shared memory.
-template <typename Tag, bool TA, bool TB>
-__device__ __forceinline__ void mma_stage(float (&acc)[NJ][4], const uint16_t* sA, const uint16_t* sB, int warp,
-                                          int lane, int ncols) {
+// One BK-deep step of a warp's 16 x (8 NJW) block from shared memory: rows 16 wrow.., columns wcol0.. of the tile.
+template <typename Tag, bool TA, bool TB, int NJW>
+__device__ __forceinline__ void mma_stage(float (&acc)[NJW][4], const uint16_t* sA, const uint16_t* sB, int wrow,
+                                          int wcol0, int lane, int ncols) {
 #pragma unroll
     for (int ks = 0; ks < BK / 16; ++ks) {
         const int k0 = ks * 16;
         uint32_t a[4];
         if constexpr (!TA) {
-            blk_ldmatrix_x4(a, blk_smem_u32(sA + (warp * 16 + (lane & 15)) * A_PITCH_N + k0 + (lane >> 4) * 8));
+            blk_ldmatrix_x4(a, blk_smem_u32(sA + (wrow * 16 + (lane & 15)) * A_PITCH_N + k0 + (lane >> 4) * 8));
         } else {
             blk_ldmatrix_x4_trans(a, blk_smem_u32(sA + (k0 + (lane & 7) + ((lane >> 4) << 3)) * A_PITCH_T +
-                                                  warp * 16 + ((lane >> 3) & 1) * 8));
+                                                  wrow * 16 + ((lane >> 3) & 1) * 8));
         }
 #pragma unroll
-        for (int jp = 0; jp < NJ / 2; ++jp) {
-            if (jp * 16 < ncols) {
+        for (int jp = 0; jp < NJW / 2; ++jp) {
+            const int c0 = wcol0 + jp * 16;
+            if (c0 < ncols) {
                 uint32_t b[4];
                 if constexpr (!TB) {
-                    blk_ldmatrix_x4(b, blk_smem_u32(sB + (jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * B_PITCH_N + k0 +
+                    blk_ldmatrix_x4(b, blk_smem_u32(sB + (c0 + (lane & 7) + ((lane >> 4) << 3)) * B_PITCH_N + k0 +
                                                     ((lane >> 3) & 1) * 8));
                 } else {
                     blk_ldmatrix_x4_trans(b, blk_smem_u32(sB + (k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * B_PITCH_T +
-                                                          jp * 16 + ((lane >> 4) << 3)));
+                                                          c0 + ((lane >> 4) << 3)));
                 }
                 blk_mma16816<Tag>(acc[2 * jp], a[0], a[1], a[2], a[3], b[0], b[1]);
                 blk_mma16816<Tag>(acc[2 * jp + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
@@ -126,20 +131,23 @@ __device__ __forceinline__ void mma_stage(float (&acc)[NJ][4], const uint16_t* s
 }
 
 // acc = A[m0.., :] * B[n0.., :]^T for the CTA's 64 x 128 tile.
-template <typename Tag, bool TA, bool TB, bool AA, bool AB>
-__device__ __forceinline__ void compute_tile(float (&acc)[NJ][4], const uint16_t* __restrict__ gA,
+// NTHR threads: NTHR / 128 warp columns, each warp 16 rows x (BN / warp columns) columns.
+template <typename Tag, bool TA, bool TB, bool AA, bool AB, int NTHR>
+__device__ __forceinline__ void compute_tile(float (&acc)[NJ * 128 / NTHR][4], const uint16_t* __restrict__ gA,
                                              const uint16_t* __restrict__ gB, int M, int N, int K, int m0, int n0,
                                              uint16_t (*sA)[A_STAGE], uint16_t (*sB)[B_STAGE], int tid) {
+    constexpr int NJW = NJ * 128 / NTHR;
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int j = 0; j < NJW; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     const int nk = (K + BK - 1) / BK;
     if (nk == 0) return;
     const int warp = tid >> 5, lane = tid & 31;
-    const bool active = m0 + warp * 16 < M;
+    const int wrow = warp & 3, wcol0 = (warp >> 2) * (8 * NJW);
     const int ncols = min(N - n0, BN);
+    const bool active = m0 + wrow * 16 < M && wcol0 < ncols;
 
-    TileStage<TA ? BK : BM, TA ? BM : BK, AA> stA;
-    TileStage<TB ? BK : BN, TB ? BN : BK, AB> stB;
+    TileStage<TA ? BK : BM, TA ? BM : BK, AA, NTHR> stA;
+    TileStage<TB ? BK : BN, TB ? BN : BK, AB, NTHR> stB;
     auto loadA = [&](int k0) {
         if constexpr (!TA) stA.load(gA, K, m0, k0, M, K, tid); else stA.load(gA, M, k0, m0, K, M, tid);
     };
@@ -160,7 +168,7 @@ __device__ __forceinline__ void compute_tile(float (&acc)[NJ][4], const uint16_t
             loadA((kt + 1) * BK);
             loadB((kt + 1) * BK);
         }
-        if (active) mma_stage<Tag, TA, TB>(acc, sA[cur], sB[cur], warp, lane, ncols);
+        if (active) mma_stage<Tag, TA, TB, NJW>(acc, sA[cur], sB[cur], wrow, wcol0, lane, ncols);
         if (more) {
             stA.store(sA[cur ^ 1], pA, tid);
             stB.store(sB[cur ^ 1], pB, tid);
@@ -170,11 +178,11 @@ __device__ __forceinline__ void compute_tile(float (&acc)[NJ][4], const uint16_t
 }
 
 // Writes the thread's fragment (rows r0 and r0+8, columns n0 + 8j + 2t, +1).
-template <typename Tag>
-__device__ __forceinline__ void store_frag(void* C, int out_f32, int64_t cbase, const float (&v)[NJ][4], int r0, int M,
+template <typename Tag, int NJW>
+__device__ __forceinline__ void store_frag(void* C, int out_f32, int64_t cbase, const float (&v)[NJW][4], int r0, int M,
                                            int N, int n0, int t, bool pair_ok) {
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
+    for (int j = 0; j < NJW; ++j) {
         const int col = n0 + 8 * j + 2 * t;
         if (col < N) {
 #pragma unroll
@@ -217,23 +225,12 @@ __device__ __forceinline__ void tile_body(const BlkGemmParams& p, const BlkSeg& 
     const bool pair_ok = ((cbase & 1) == 0) && ((N & 1) == 0);
     float acc[NJ][4];
 
-    if (p.epi == BLK_EPI_SCORES) {
-        const int n0 = it.tn * BN;
-        compute_tile<Tag, TA, TB, AA, AB>(acc, gA, gB, M, N, K, m0, n0, sA, sB, tid);
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-            acc[j][0] *= p.scale; acc[j][1] *= p.scale; acc[j][2] *= p.scale; acc[j][3] *= p.scale;
-        }
-        store_frag<Tag>(p.C, p.out_f32, cbase, acc, r0, M, N, n0, t, pair_ok);
-        return;
-    }
-
     // softmax epilogue, base-2 domain
     const float sl = p.scale * BLK_LOG2E;
     float mrun[2] = {-INFINITY, -INFINITY}, lrun[2] = {0.f, 0.f};
     for (int tn = 0; tn < it.ntn; ++tn) {
         const int n0 = tn * BN;
-        compute_tile<Tag, TA, TB, AA, AB>(acc, gA, gB, M, N, K, m0, n0, sA, sB, tid);
+        compute_tile<Tag, TA, TB, AA, AB, NT>(acc, gA, gB, M, N, K, m0, n0, sA, sB, tid);
         float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
@@ -264,7 +261,7 @@ __device__ __forceinline__ void tile_body(const BlkGemmParams& p, const BlkSeg& 
                     acc[j][2 * h + 1] *= inv;
                 }
             }
-            store_frag<Tag>(p.C, p.out_f32, cbase, acc, r0, M, N, 0, t, pair_ok);
+            store_frag<Tag, NJ>(p.C, p.out_f32, cbase, acc, r0, M, N, 0, t, pair_ok);
             return;
         }
 #pragma unroll
@@ -289,18 +286,41 @@ __device__ __forceinline__ void tile_body(const BlkGemmParams& p, const BlkSeg& 
     }
     for (int tn = 0; tn < it.ntn; ++tn) {
         const int n0 = tn * BN;
-        compute_tile<Tag, TA, TB, AA, AB>(acc, gA, gB, M, N, K, m0, n0, sA, sB, tid);
+        compute_tile<Tag, TA, TB, AA, AB, NT>(acc, gA, gB, M, N, K, m0, n0, sA, sB, tid);
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[j][e] = blk_exp2(acc[j][e] * sl - mrun[e >> 1]) * inv[e >> 1];
         }
-        store_frag<Tag>(p.C, p.out_f32, cbase, acc, r0, M, N, n0, t, pair_ok);
+        store_frag<Tag, NJ>(p.C, p.out_f32, cbase, acc, r0, M, N, n0, t, pair_ok);
     }
 }
 
-template <typename Tag, bool TA, bool TB>
-__global__ void __launch_bounds__(NT, 3) blk_gemm_tile_kernel(const BlkGemmParams p) {
+// Scores only: eight warps per tile (four row blocks x two column halves), so twice the warps of the softmax
+// layout are resident per SM to hide the global-load latency of short contractions.
+constexpr int NT_SC = 256;
+template <typename Tag, bool TA, bool TB, bool AA, bool AB>
+__device__ __forceinline__ void scores_body(const BlkGemmParams& p, const BlkSeg& sd, const BlkTileItem& it,
+                                            const uint16_t* gA, const uint16_t* gB, int64_t cbase,
+                                            uint16_t (*sA)[A_STAGE], uint16_t (*sB)[B_STAGE]) {
+    constexpr int NJW = NJ * 128 / NT_SC;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int M = sd.M, N = sd.N, K = sd.K;
+    const int m0 = it.tm * BM, n0 = it.tn * BN;
+    const int r0 = m0 + (warp & 3) * 16 + g;
+    const bool pair_ok = ((cbase & 1) == 0) && ((N & 1) == 0);
+    float acc[NJW][4];
+    compute_tile<Tag, TA, TB, AA, AB, NT_SC>(acc, gA, gB, M, N, K, m0, n0, sA, sB, tid);
+#pragma unroll
+    for (int j = 0; j < NJW; ++j) {
+        acc[j][0] *= p.scale; acc[j][1] *= p.scale; acc[j][2] *= p.scale; acc[j][3] *= p.scale;
+    }
+    store_frag<Tag, NJW>(p.C, p.out_f32, cbase, acc, r0, M, N, n0 + (warp >> 2) * (8 * NJW), t, pair_ok);
+}
+
+// SOFTMAX: the fused two-sweep kernel (four warps); otherwise the scores kernel (eight warps).
+template <typename Tag, bool TA, bool TB, bool SOFTMAX>
+__global__ void __launch_bounds__(SOFTMAX ? NT : NT_SC, 3) blk_gemm_tile_kernel(const BlkGemmParams p) {
     __shared__ __align__(16) uint16_t sA[2][A_STAGE];
     __shared__ __align__(16) uint16_t sB[2][B_STAGE];
     const int64_t bid = blockIdx.x;
@@ -314,25 +334,34 @@ __global__ void __launch_bounds__(NT, 3) blk_gemm_tile_kernel(const BlkGemmParam
     const int64_t pitchA = TA ? sd.M : sd.K, pitchB = TB ? sd.N : sd.K;
     // per operand: plain 16-byte loads when every row of this (segment, head) starts on a 16-byte boundary
     const bool alignedA = ((baseA | pitchA) & 7) == 0, alignedB = ((baseB | pitchB) & 7) == 0;
+    auto body = [&](auto aa, auto ab) {
+        if constexpr (SOFTMAX) tile_body<Tag, TA, TB, decltype(aa)::value, decltype(ab)::value>(p, sd, it, gA, gB, cbase, sA, sB);
+        else scores_body<Tag, TA, TB, decltype(aa)::value, decltype(ab)::value>(p, sd, it, gA, gB, cbase, sA, sB);
+    };
     if (alignedA) {
-        if (alignedB) tile_body<Tag, TA, TB, true, true>(p, sd, it, gA, gB, cbase, sA, sB);
-        else tile_body<Tag, TA, TB, true, false>(p, sd, it, gA, gB, cbase, sA, sB);
+        if (alignedB) body(std::true_type{}, std::true_type{});
+        else body(std::true_type{}, std::false_type{});
     } else {
-        if (alignedB) tile_body<Tag, TA, TB, false, true>(p, sd, it, gA, gB, cbase, sA, sB);
-        else tile_body<Tag, TA, TB, false, false>(p, sd, it, gA, gB, cbase, sA, sB);
+        if (alignedB) body(std::false_type{}, std::true_type{});
+        else body(std::false_type{}, std::false_type{});
     }
+}
+
+template <typename Tag, bool SOFTMAX>
+cudaError_t launch_epi(const BlkGemmParams& p, int ta, int tb, cudaStream_t st) {
+    const int64_t blocks = (int64_t)p.num_items * p.H;
+    const dim3 grid((unsigned)blocks), block(SOFTMAX ? NT : NT_SC);
+    if (!ta && !tb) blk_gemm_tile_kernel<Tag, false, false, SOFTMAX><<<grid, block, 0, st>>>(p);
+    else if (!ta && tb) blk_gemm_tile_kernel<Tag, false, true, SOFTMAX><<<grid, block, 0, st>>>(p);
+    else if (ta && !tb) blk_gemm_tile_kernel<Tag, true, false, SOFTMAX><<<grid, block, 0, st>>>(p);
+    else blk_gemm_tile_kernel<Tag, true, true, SOFTMAX><<<grid, block, 0, st>>>(p);
+    return cudaGetLastError();
 }
 
 template <typename Tag>
 cudaError_t launch_tag(const BlkGemmParams& p, int ta, int tb, cudaStream_t st) {
-    const int64_t blocks = (int64_t)p.num_items * p.H;
-    if (blocks == 0) return cudaSuccess;
-    const dim3 grid((unsigned)blocks), block(NT);
-    if (!ta && !tb) blk_gemm_tile_kernel<Tag, false, false><<<grid, block, 0, st>>>(p);
-    else if (!ta && tb) blk_gemm_tile_kernel<Tag, false, true><<<grid, block, 0, st>>>(p);
-    else if (ta && !tb) blk_gemm_tile_kernel<Tag, true, false><<<grid, block, 0, st>>>(p);
-    else blk_gemm_tile_kernel<Tag, true, true><<<grid, block, 0, st>>>(p);
-    return cudaGetLastError();
+    if ((int64_t)p.num_items * p.H == 0) return cudaSuccess;
+    return p.epi == BLK_EPI_SOFTMAX ? launch_epi<Tag, true>(p, ta, tb, st) : launch_epi<Tag, false>(p, ta, tb, st);
 }
 
 }  // namespace
