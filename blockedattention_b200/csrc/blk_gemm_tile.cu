@@ -178,40 +178,49 @@ __device__ __forceinline__ void compute_tile(float (&acc)[NJ * 128 / NTHR][4], c
 }
 
 // Writes the thread's fragment (rows r0 and r0+8, columns n0 + 8j + 2t, +1).
-template <typename Tag, int NJW>
-__device__ __forceinline__ void store_frag(void* C, int out_f32, int64_t cbase, const float (&v)[NJW][4], int r0, int M,
-                                           int N, int n0, int t, bool pair_ok) {
+template <typename Tag, int NJW, bool F32>
+__device__ __forceinline__ void store_frag_t(void* C, int64_t cbase, const float (&v)[NJW][4], int r0, int M, int N,
+                                             int n0, int t, bool pair_ok) {
+    typedef typename std::conditional<F32, float, uint16_t>::type E;
+    const int c0 = n0 + 2 * t;  // this thread's first column
 #pragma unroll
-    for (int j = 0; j < NJW; ++j) {
-        const int col = n0 + 8 * j + 2 * t;
-        if (col < N) {
+    for (int h = 0; h < 2; ++h) {
+        const int r = r0 + 8 * h;
+        if (r >= M) continue;
+        E* row = reinterpret_cast<E*>(C) + (cbase + (int64_t)r * N + c0);  // columns c0 + 8 j, + 1 at row[8 j], [8 j + 1]
+        if (pair_ok) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int r = r0 + 8 * h;
-                if (r < M) {
-                    const int64_t e = cbase + (int64_t)r * N + col;
-                    const float x = v[j][2 * h], y = v[j][2 * h + 1];
-                    if (out_f32) {
-                        float* c = reinterpret_cast<float*>(C) + e;
-                        if (pair_ok && col + 1 < N) {
-                            *reinterpret_cast<float2*>(c) = make_float2(x, y);
-                        } else {
-                            c[0] = x;
-                            if (col + 1 < N) c[1] = y;
-                        }
-                    } else {
-                        uint16_t* c = reinterpret_cast<uint16_t*>(C) + e;
-                        if (pair_ok && col + 1 < N) {
-                            *reinterpret_cast<uint32_t*>(c) = BlkCvt<Tag>::pack2(x, y);
-                        } else {
-                            c[0] = BlkCvt<Tag>::pack1(x);
-                            if (col + 1 < N) c[1] = BlkCvt<Tag>::pack1(y);
-                        }
-                    }
+            for (int j = 0; j < NJW; ++j) {
+                const float x = v[j][2 * h], y = v[j][2 * h + 1];
+                if (c0 + 8 * j + 1 < N) {
+                    if constexpr (F32) *reinterpret_cast<float2*>(row + 8 * j) = make_float2(x, y);
+                    else *reinterpret_cast<uint32_t*>(row + 8 * j) = BlkCvt<Tag>::pack2(x, y);
+                } else if (c0 + 8 * j < N) {
+                    if constexpr (F32) row[8 * j] = x;
+                    else row[8 * j] = BlkCvt<Tag>::pack1(x);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NJW; ++j) {
+                const float x = v[j][2 * h], y = v[j][2 * h + 1];
+                if (c0 + 8 * j < N) {
+                    if constexpr (F32) row[8 * j] = x;
+                    else row[8 * j] = BlkCvt<Tag>::pack1(x);
+                }
+                if (c0 + 8 * j + 1 < N) {
+                    if constexpr (F32) row[8 * j + 1] = y;
+                    else row[8 * j + 1] = BlkCvt<Tag>::pack1(y);
                 }
             }
         }
     }
+}
+template <typename Tag, int NJW>
+__device__ __forceinline__ void store_frag(void* C, int out_f32, int64_t cbase, const float (&v)[NJW][4], int r0, int M,
+                                           int N, int n0, int t, bool pair_ok) {
+    if (out_f32) store_frag_t<Tag, NJW, true>(C, cbase, v, r0, M, N, n0, t, pair_ok);
+    else store_frag_t<Tag, NJW, false>(C, cbase, v, r0, M, N, n0, t, pair_ok);
 }
 
 template <typename Tag, bool TA, bool TB, bool AA, bool AB>
