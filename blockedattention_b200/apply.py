@@ -228,6 +228,26 @@ def blockAttnScores(q: torch.Tensor, k: torch.Tensor, MList, NList, KList, scale
                      scale=scale, out_dtype=out_dtype, softmax=True)
 
 
+def blockAttnScoresTokenMajor(q: torch.Tensor, k: torch.Tensor, nList, scale: float = 1.0,
+                              out_dtype: Optional[torch.dtype] = None, softmax: bool = True) -> torch.Tensor:
+    """``blockAttnScores`` for the layout attention inputs usually arrive in: ``q, k -> (sum n_s, H, d)``, the tokens
+    of all segments in batch order.  The operands are read in place through strided tensor maps -- no permuted copy
+    into head-major strips is made -- and the result is the packed head-major ``(H, sum n_s^2)`` buffer of
+    ``blockAttnScores``.  Needs 16-bit inputs and ``d`` a multiple of 64 (``d = 64`` when the batch has segments of
+    at most 64 tokens).  Forward only."""
+    _check_operand("q", q)
+    _check_operand("k", k)
+    if q.dim() != 3 or q.shape != k.shape:
+        raise RuntimeError("q and k must both have shape (sum n, H, d)")
+    n = _host_i64(nList)
+    H, d = int(q.shape[1]), int(q.shape[2])
+    odt = out_dtype if out_dtype is not None else q.dtype
+    key = ("tokmajor", n.tobytes(), H, d, q.dtype, odt, bool(softmax), str(q.device))
+    plan = _cached(key, lambda: GemmPlan(n, n, np.full_like(n, d), H, q.dtype, odt, False, False, bool(softmax),
+                                         device=q.device))
+    return plan.run_token_major(q, k, scale=scale)
+
+
 class _HostPipe:
     """Device-side staging of ``blockAttnScoresHost`` for one (lists, H, dtypes, device): a plan for a group of
     heads, two sets of device buffers and three streams (copy in, compute, copy out)."""

@@ -297,8 +297,13 @@ extern "C" int blk_plan_check(const blk_plan_t* p, void* cuda_stream) {
     return BLK_OK;
 }
 
-extern "C" int blk_gemm_run(const blk_plan_t* p, const void* mat1, const void* mat2, void* out, float scale,
-                            void* cuda_stream) {
+// Shared body of blk_gemm_run and blk_gemm_run_strided; layA / layB say where the operands' rows are (null:
+// packed head-major strips, whose row view depends on the contraction length of the kernel that reads them).
+static int gemm_run_impl(const blk_plan* p, const void* mat1, const void* mat2, void* out, float scale,
+                         const BlkOperandLayout* layA, const BlkOperandLayout* layB, void* cuda_stream) {
+    auto layout = [](const BlkOperandLayout* given, int64_t D, int64_t K) {
+        return given ? *given : BlkOperandLayout{D / K, K, D};
+    };
     if (!p || p->kind != 0) {
         blk_set_error("blk_gemm_run: not a GEMM plan");
         return BLK_ERR_INVALID;
@@ -358,6 +363,8 @@ extern "C" int blk_gemm_run(const blk_plan_t* p, const void* mat1, const void* m
         pp.epi = p->epi;
         pp.scale = scale;
         pp.status = p->d_status;
+        pp.layA = layout(layA, p->Dm1, 64);
+        pp.layB = layout(layB, p->Dm2, 64);
         if ((e = blk_launch_scores_pipe(pp, p->dtype_in, p->num_sms, st)) != cudaSuccess)
             return cuda_fail("pipelined small-segment launch", e);
     }
@@ -390,7 +397,8 @@ extern "C" int blk_gemm_run(const blk_plan_t* p, const void* mat1, const void* m
         up.epi = p->epi;
         up.scale = scale;
         up.status = p->d_status;
-        if ((e = blk_launch_gemm_umma(up, mat1, mat2, p->Dm1, p->Dm2, p->num_sms, st)) != cudaSuccess)
+        if ((e = blk_launch_gemm_umma(up, mat1, mat2, layout(layA, p->Dm1, p->umma_K), layout(layB, p->Dm2, p->umma_K),
+                                      p->num_sms, st)) != cudaSuccess)
             return cuda_fail("tcgen05 GEMM launch", e);
     }
     if (!p->tile_items.empty()) {
@@ -410,6 +418,49 @@ extern "C" int blk_gemm_run(const blk_plan_t* p, const void* mat1, const void* m
             return cuda_fail("tile GEMM launch", e);
     }
     return BLK_OK;
+}
+
+extern "C" int blk_gemm_run(const blk_plan_t* p, const void* mat1, const void* mat2, void* out, float scale,
+                            void* cuda_stream) {
+    if (!p || p->kind != 0) {
+        blk_set_error("blk_gemm_run: not a GEMM plan");
+        return BLK_ERR_INVALID;
+    }
+    return gemm_run_impl(p, mat1, mat2, out, scale, nullptr, nullptr, cuda_stream);
+}
+
+extern "C" int blk_gemm_run_strided(const blk_plan_t* p, const void* mat1, int64_t row_stride1, int64_t head_stride1,
+                                    const void* mat2, int64_t row_stride2, int64_t head_stride2, void* out,
+                                    float scale, void* cuda_stream) {
+    if (!p || p->kind != 0) {
+        blk_set_error("blk_gemm_run_strided: not a GEMM plan");
+        return BLK_ERR_INVALID;
+    }
+    if (p->S == 0 || p->H == 0 || p->Dout == 0) return BLK_OK;
+    // Only the kernels that fetch operands through tensor maps take strides: every segment must be on the
+    // pack kernel or the tcgen05 kernel, which also means one contraction length for the whole batch.
+    const bool small_ok = p->small_pipe || small_count(p) == 0;
+    if (!small_ok || !p->tile_items.empty() || !p->simt_items.empty()) {
+        blk_set_error("blk_gemm_run_strided: this batch needs a kernel that reads packed operands only "
+                      "(16-bit inputs, not transposed, packed offsets, one K that is a multiple of 64 are required)");
+        return BLK_ERR_UNSUPPORTED;
+    }
+    const int64_t K = p->small_pipe ? 64 : p->umma_K;
+    if (K <= 0 || (p->small_pipe && p->umma_K > 0 && p->umma_K != 64)) {
+        blk_set_error("blk_gemm_run_strided: the batch does not have one contraction length");
+        return BLK_ERR_UNSUPPORTED;
+    }
+    for (const int64_t v : {row_stride1, head_stride1, row_stride2, head_stride2})
+        if (v <= 0 || v % 8) {
+            blk_set_error("blk_gemm_run_strided: strides must be positive multiples of 8 elements");
+            return BLK_ERR_INVALID;
+        }
+    if (row_stride1 < K || row_stride2 < K) {
+        blk_set_error("blk_gemm_run_strided: a row stride is shorter than the contraction length");
+        return BLK_ERR_INVALID;
+    }
+    const BlkOperandLayout layA{p->Dm1 / K, row_stride1, head_stride1}, layB{p->Dm2 / K, row_stride2, head_stride2};
+    return gemm_run_impl(p, mat1, mat2, out, scale, &layA, &layB, cuda_stream);
 }
 
 extern "C" int blk_softmax_run(const blk_plan_t* p, const void* src, void* out, float scale, void* cuda_stream) {

@@ -317,8 +317,12 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                             if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
                             const uint32_t sA = smem_u32 + stage * UM_STAGE_BYTES, sB = sA + UM_A_BYTES;
                             mbar_expect_tx(full_bar(stage), UM_STAGE_BYTES);
-                            tma_load_3d(sA, &mapA, full_bar(stage), kb * UM_BK, wk.it.rowA, wk.head);
-                            tma_load_3d(sB, &mapB, full_bar(stage), kb * UM_BK, wk.it.rowB + ch * UM_BN, wk.head);
+                            // coordinates (k, row, head), or (k, head, row) for a token-major operand
+                            const int rA = wk.it.rowA, rB = wk.it.rowB + ch * UM_BN;
+                            tma_load_3d(sA, &mapA, full_bar(stage), kb * UM_BK, p.head_firstA ? wk.head : rA,
+                                        p.head_firstA ? rA : wk.head);
+                            tma_load_3d(sB, &mapB, full_bar(stage), kb * UM_BK, p.head_firstB ? wk.head : rB,
+                                        p.head_firstB ? rB : wk.head);
                             if (++stage == UM_STAGES) { stage = 0; phase ^= 1u; }
                         }
             }
@@ -594,12 +598,6 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// View of a packed operand as (k, row, head): K contiguous elements per row, D elements per head.
-bool make_map(CUtensorMap* map, const void* base, int bf16, int64_t K, int64_t rows, int64_t H, int64_t D,
-              int box_rows) {
-    return blk_make_row_map(map, base, bf16, K, rows, H, D, UM_BK, box_rows);
-}
-
 template <typename Tag, bool OUT32>
 cudaError_t launch(const BlkUmmaParams& p, const CUtensorMap& a, const CUtensorMap& b, int sms, cudaStream_t st) {
     auto kern = blk_gemm_umma_kernel<Tag, OUT32>;
@@ -613,13 +611,17 @@ cudaError_t launch(const BlkUmmaParams& p, const CUtensorMap& a, const CUtensorM
 
 }  // namespace
 
-bool blk_make_row_map(CUtensorMap_st* map, const void* base, int bf16, int64_t K, int64_t rows, int64_t H, int64_t D,
-                      int box_k, int box_rows) {
+bool blk_make_row_map(CUtensorMap_st* map, const void* base, int bf16, int64_t K, int64_t H, const BlkOperandLayout& lay,
+                      int box_k, int box_rows, int* head_first) {
     EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)H};
-    const cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)D * 2};
-    const cuuint32_t box[3] = {(cuuint32_t)box_k, (cuuint32_t)box_rows, 1};
+    if (!fn || lay.rows <= 0 || H <= 0) return false;
+    if (lay.row_stride % 8 || lay.head_stride % 8 || lay.row_stride < K) return false;  // 16-byte strides
+    const bool hf = lay.head_stride < lay.row_stride;  // token-major: heads are the closer dimension
+    *head_first = hf ? 1 : 0;
+    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)(hf ? H : lay.rows), (cuuint64_t)(hf ? lay.rows : H)};
+    const cuuint64_t strides[2] = {(cuuint64_t)(hf ? lay.head_stride : lay.row_stride) * 2,
+                                   (cuuint64_t)(hf ? lay.row_stride : lay.head_stride) * 2};
+    const cuuint32_t box[3] = {(cuuint32_t)box_k, (cuuint32_t)(hf ? 1 : box_rows), (cuuint32_t)(hf ? box_rows : 1)};
     const cuuint32_t estr[3] = {1, 1, 1};
     return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
               const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -627,13 +629,13 @@ bool blk_make_row_map(CUtensorMap_st* map, const void* base, int bf16, int64_t K
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p, const void* A, const void* B, int64_t Dm1, int64_t Dm2,
-                                 int sms, cudaStream_t st) {
-    if ((int64_t)p.num_items * p.H == 0) return cudaSuccess;
+cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p_in, const void* A, const void* B, const BlkOperandLayout& layA,
+                                 const BlkOperandLayout& layB, int sms, cudaStream_t st) {
+    if ((int64_t)p_in.num_items * p_in.H == 0) return cudaSuccess;
+    BlkUmmaParams p = p_in;
     CUtensorMap mapA, mapB;
-    // rows of each view: whole rows that fit one head strip
-    if (!make_map(&mapA, A, p.bf16, p.K, Dm1 / p.K, p.H, Dm1, UM_BM) ||
-        !make_map(&mapB, B, p.bf16, p.K, Dm2 / p.K, p.H, Dm2, UM_BN))
+    if (!blk_make_row_map(&mapA, A, p.bf16, p.K, p.H, layA, UM_BK, UM_BM, &p.head_firstA) ||
+        !blk_make_row_map(&mapB, B, p.bf16, p.K, p.H, layB, UM_BK, UM_BN, &p.head_firstB))
         return cudaErrorInvalidValue;
     if (p.bf16) return p.out_f32 ? launch<BlkBf16Tag, true>(p, mapA, mapB, sms, st) : launch<BlkBf16Tag, false>(p, mapA, mapB, sms, st);
     return p.out_f32 ? launch<BlkHalfTag, true>(p, mapA, mapB, sms, st) : launch<BlkHalfTag, false>(p, mapA, mapB, sms, st);

@@ -5,6 +5,15 @@
 
 #include "blk_internal.h"
 
+// Where the rows of one 16-bit operand live: element (head h, row r, k) is at base[r * row_stride +
+// h * head_stride + k].  Packed head-major strips: row_stride = K, head_stride = elements per strip;
+// token-major [rows, H, K]: row_stride = H * K, head_stride = K.
+struct BlkOperandLayout {
+    int64_t rows;         // rows per head
+    int64_t row_stride;   // elements
+    int64_t head_stride;  // elements
+};
+
 struct BlkGemmParams {
     const uint16_t* A;
     const uint16_t* B;
@@ -57,6 +66,7 @@ struct BlkUmmaParams {
     int epi;
     float scale;
     int* status;
+    int head_firstA, head_firstB;  // coordinate order of the operands' tensor maps
 };
 
 struct BlkPackParams {
@@ -71,6 +81,8 @@ struct BlkPackParams {
     int epi;
     float scale;
     int* status;
+    BlkOperandLayout layA, layB;   // where the operands' rows are (filled by the caller)
+    int head_firstA, head_firstB;  // coordinate order of the tensor maps (filled by the launcher)
 };
 
 struct BlkSmxParams {
@@ -95,19 +107,20 @@ struct BlkSmxBwdParams {
     float scale;
 };
 
-// Tensor map (128-byte swizzle) over a packed 16-bit operand viewed as (k, row, head): K contiguous elements per
-// row, D elements per head, boxes of box_k x box_rows x 1.  False when the driver's encoder is unavailable or
-// rejects the view.  Defined in blk_gemm_umma.cu.
+// Tensor map (128-byte swizzle) over such an operand, boxes of box_k x box_rows of one head.  The dimension
+// with the smaller stride comes second: *head_first = 0 means coordinates (k, row, head), 1 means (k, head, row).
+// False when the driver's encoder is unavailable or rejects the view.  Defined in blk_gemm_umma.cu.
 struct CUtensorMap_st;
-bool blk_make_row_map(CUtensorMap_st* map, const void* base, int bf16, int64_t K, int64_t rows, int64_t H, int64_t D,
-                      int box_k, int box_rows);
+bool blk_make_row_map(CUtensorMap_st* map, const void* base, int bf16, int64_t K, int64_t H, const BlkOperandLayout& lay,
+                      int box_k, int box_rows, int* head_first);
 
 cudaError_t blk_launch_gemm_tile(const BlkGemmParams& p, int dtype_in, int ta, int tb, cudaStream_t st);
 cudaError_t blk_launch_softmax_bwd(const BlkSmxBwdParams& p, int dtype, cudaStream_t st);
 cudaError_t blk_launch_gemm_simt(const BlkSimtParams& p, cudaStream_t st);
 cudaError_t blk_launch_scores_small(const BlkSmallParams& p, int dtype_in, int K, int bucket, int sms,
                                     cudaStream_t st);
-cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p, const void* A, const void* B, int64_t Dm1, int64_t Dm2,
+cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p, const void* A, const void* B, const BlkOperandLayout& layA,
+                                 const BlkOperandLayout& layB,
                                  int sms, cudaStream_t st);
 cudaError_t blk_launch_scores_pipe(const BlkPackParams& p, int dtype_in, int sms, cudaStream_t st);
 cudaError_t blk_launch_softmax(const BlkSmxParams& p, int dtype, cudaStream_t st);

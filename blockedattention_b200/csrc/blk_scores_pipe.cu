@@ -96,22 +96,26 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
-// Tiled tensor-map copy global -> shared of one box at (k = 0, row, head), completing on an mbarrier.
-__device__ __forceinline__ void tma_rows(uint32_t dst, const CUtensorMap* map, uint32_t bar, int row, int head) {
+// Tiled tensor-map copy global -> shared of one box at coordinates (k = 0, c1, c2), completing on an mbarrier.
+__device__ __forceinline__ void tma_rows(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c1, int c2) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(row), "r"(head)
+        ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(c1), "r"(c2)
         : "memory");
 }
 // Brings `rows` rows starting at row `row0` of a head's operand into shared memory at dst as boxes of 64, 32 and
 // 16 rows (each box a whole number of 1024-byte swizzle atoms); returns the bytes that will arrive.
+// The map's coordinates are (k, row, head), or (k, head, row) when head_first (token-major operand).
 __device__ __forceinline__ uint32_t tma_run(uint32_t dst, const CUtensorMap* m64, const CUtensorMap* m32,
-                                            const CUtensorMap* m16, uint32_t bar, int row0, int rows, int head) {
+                                            const CUtensorMap* m16, uint32_t bar, int row0, int rows, int head,
+                                            int head_first) {
     int r = 0;
     while (r < rows) {
         const int rem = rows - r;
         const int box = rem > 48 ? 64 : (rem > 16 ? 32 : 16);
-        tma_rows(dst + r * ROWB, box == 64 ? m64 : (box == 32 ? m32 : m16), bar, row0 + r, head);
+        const CUtensorMap* m = box == 64 ? m64 : (box == 32 ? m32 : m16);
+        if (head_first) tma_rows(dst + r * ROWB, m, bar, head, row0 + r);
+        else tma_rows(dst + r * ROWB, m, bar, row0 + r, head);
         r += box;
     }
     return (uint32_t)r * ROWB;
@@ -390,8 +394,8 @@ blk_scores_pipe_kernel(const BlkPackParams p, const __grid_constant__ CUtensorMa
                 // rows are fetched in whole boxes: up to 15 rows past the run's end come along (zeros past the strip)
                 const uint32_t bytesA = (uint32_t)((pk.rowsA + 15) & ~15) * ROWB, bytesB = (uint32_t)((pk.rowsB + 15) & ~15) * ROWB;
                 pb_expect_tx(full_bar(s), bytesA + bytesB + bytesR);
-                tma_run(dst, &mA64, &mA32, &mA16, full_bar(s), (int)(pk.offA / PK), pk.rowsA, (int)hd_now);
-                tma_run(dst + P_OPER_BYTES, &mB64, &mB32, &mB16, full_bar(s), (int)(pk.offB / PK), pk.rowsB, (int)hd_now);
+                tma_run(dst, &mA64, &mA32, &mA16, full_bar(s), (int)(pk.offA / PK), pk.rowsA, (int)hd_now, p.head_firstA);
+                tma_run(dst + P_OPER_BYTES, &mB64, &mB32, &mB16, full_bar(s), (int)(pk.offB / PK), pk.rowsB, (int)hd_now, p.head_firstB);
                 bulk_g2s(dst + 2 * P_OPER_BYTES, p.blocks + pk.first_block, bytesR, full_bar(s));
             }
         }
@@ -435,16 +439,17 @@ blk_scores_pipe_kernel(const BlkPackParams p, const __grid_constant__ CUtensorMa
 }
 
 template <typename Tag>
-cudaError_t launch_pipe(const BlkPackParams& p, int sms, cudaStream_t st) {
-    const int64_t total = (int64_t)p.num_packs * p.H;
+cudaError_t launch_pipe(const BlkPackParams& p_in, int sms, cudaStream_t st) {
+    const int64_t total = (int64_t)p_in.num_packs * p_in.H;
     if (total == 0) return cudaSuccess;
+    BlkPackParams p = p_in;
     // both operands as (64, rows, heads) views with boxes of 64, 32 and 16 rows
     CUtensorMap mA[3], mB[3];
     const int bf16 = std::is_same<Tag, BlkBf16Tag>::value ? 1 : 0;
     const int box_rows[3] = {64, 32, 16};
     for (int i = 0; i < 3; ++i)
-        if (!blk_make_row_map(&mA[i], p.A, bf16, PK, p.Dm1 / PK, p.H, p.Dm1, PK, box_rows[i]) ||
-            !blk_make_row_map(&mB[i], p.B, bf16, PK, p.Dm2 / PK, p.H, p.Dm2, PK, box_rows[i]))
+        if (!blk_make_row_map(&mA[i], p.A, bf16, PK, p.H, p.layA, PK, box_rows[i], &p.head_firstA) ||
+            !blk_make_row_map(&mB[i], p.B, bf16, PK, p.H, p.layB, PK, box_rows[i], &p.head_firstB))
             return cudaErrorInvalidValue;
     const dim3 grid((unsigned)(total < sms ? total : sms)), block(P_THREADS);
     auto go = [&](auto kern) -> cudaError_t {

@@ -153,6 +153,34 @@ class GemmPlan(_Plan):
         return out
 
 
+    def run_token_major(self, mat1: torch.Tensor, mat2: torch.Tensor, out: Optional[torch.Tensor] = None,
+                        scale: float = 1.0) -> torch.Tensor:
+        """Same as :meth:`run` for token-major operands ``mat1 -> (sum m_s, H, d)``, ``mat2 -> (sum n_s, H, d)``
+        (the rows of all segments in batch order); the result is the packed head-major ``(H, Dout)`` buffer.
+        Needs a batch the tensor-map kernels take whole: 16-bit, one ``K = d`` that is a multiple of 64."""
+        if self.device is None:
+            raise RuntimeError("this plan was built without a device")
+        d = int(self.K[0]) if self.S else 0
+        for name, t, rows in (("mat1", mat1, int(self.M.sum())), ("mat2", mat2, int(self.N.sum()))):
+            if not t.is_cuda or not t.is_contiguous() or t.dtype != self.dtype_in:
+                raise RuntimeError(f"{name} must be a contiguous CUDA tensor of the plan's dtype")
+            if t.dim() != 3 or tuple(t.shape) != (rows, self.H, d):
+                raise RuntimeError(f"{name} must have shape (rows, H, d) = ({rows}, {self.H}, {d}), got {tuple(t.shape)}")
+            if t.data_ptr() % 16:
+                raise RuntimeError(f"{name} must be 16-byte aligned")
+        if out is None:
+            out = torch.empty((self.H, self.Dout), dtype=self.dtype_out, device=mat1.device)
+        elif (not out.is_cuda or not out.is_contiguous() or out.dtype != self.dtype_out
+              or out.numel() != self.H * self.Dout or out.data_ptr() % 16):
+            raise RuntimeError("out must be a contiguous, 16-byte aligned CUDA tensor of the plan's dtype with H*Dout elements")
+        with torch.cuda.device(mat1.device):
+            L.check(L.lib.blk_gemm_run_strided(self._h, C.c_void_p(mat1.data_ptr()), self.H * d, d,
+                                               C.c_void_p(mat2.data_ptr()), self.H * d, d,
+                                               C.c_void_p(out.data_ptr()), C.c_float(scale),
+                                               C.c_void_p(_stream_ptr(mat1.device))))
+        return out
+
+
 class SoftmaxPlan(_Plan):
     """Schedule for the row softmax of S packed (rows_s, cols_s) blocks per head."""
 

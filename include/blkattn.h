@@ -120,6 +120,21 @@ BLK_API int blk_gemm_plan_create(blk_plan_t** plan,
 BLK_API int blk_gemm_run(const blk_plan_t* plan, const void* mat1, const void* mat2, void* out,
                  float scale, void* cuda_stream);
 
+/* blk_gemm_run for operands that are not packed head-major strips: element
+ * (head h, row r, k) of mat1 is at mat1[r * row_stride1 + h * head_stride1 + k],
+ * r counting the rows of all segments in batch order (same for mat2); strides
+ * in elements, multiples of 8.  A token-major [rows, H, d] tensor, the layout
+ * attention inputs usually have before upstream's callers permute them into
+ * strips, is row_stride = H * d, head_stride = d.  The result is packed
+ * head-major as always.  Only batches whose every segment runs on a kernel
+ * that fetches operands through tensor maps qualify: 16-bit inputs, not
+ * transposed, packed offsets, one contraction length d that is a multiple of
+ * 64 (and d = 64 where the batch has segments with at most 64 rows and
+ * columns); otherwise BLK_ERR_UNSUPPORTED.  No counterpart upstream. */
+BLK_API int blk_gemm_run_strided(const blk_plan_t* plan, const void* mat1, int64_t row_stride1, int64_t head_stride1,
+                         const void* mat2, int64_t row_stride2, int64_t head_stride2, void* out, float scale,
+                         void* cuda_stream);
+
 /* ---- varlen row softmax ---------------------------------------------------- */
 
 /* Replaces the per-row host table at upstream csrc/cuda/spBlkSoftmax.cu:358-373

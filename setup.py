@@ -1,0 +1,34 @@
+"""Install of the same two import names the upstream package provides (upstream setup.py:15-31):
+``blockedAttention`` (operators ``blockGEMM`` / ``blockSoftmax``) and the extension-module name
+``blockAttention`` (``sparseBlockedGEMM`` / ``sparseBlockedSoftmax``), both thin aliases of
+``blockedattention_b200``, whose C-ABI library ``lib/libblkattn.so`` is built with nvcc for sm_100a
+by ``blockedattention_b200/build.py`` during ``build_py`` and shipped as package data.
+
+    python setup.py build_py          # or: pip install --no-build-isolation .
+"""
+import os
+import runpy
+
+from setuptools import setup
+from setuptools.command.build_py import build_py
+
+ROOT = os.path.dirname(os.path.realpath(__file__))
+
+
+class BuildWithLibrary(build_py):
+    def run(self):
+        # the build script runs without importing the package (which would look for the library it is about to make)
+        runpy.run_path(os.path.join(ROOT, "blockedattention_b200", "build.py"))["build"]()
+        super().run()
+
+
+setup(
+    name="blockedAttention",
+    version="0.1.0",
+    description="Varlen blocked GEMM and row softmax for NVIDIA B200 (sm_100a) behind the blockedAttention operator API",
+    python_requires=">=3.9",
+    install_requires=[],
+    packages=["blockedattention_b200", "blockedAttention", "blockAttention"],
+    package_data={"blockedattention_b200": ["lib/libblkattn.so"]},
+    cmdclass={"build_py": BuildWithLibrary},
+)

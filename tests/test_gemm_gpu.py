@@ -7,7 +7,8 @@ import pytest
 import torch
 
 from helpers import O, assert_probs_close, assert_scores_close, packed_inputs
-from blockedattention_b200 import blockAttnScores, blockAttnScoresHost, blockGEMM, blockSoftmax
+from blockedattention_b200 import (blockAttnScores, blockAttnScoresHost, blockAttnScoresTokenMajor, blockGEMM,
+                                   blockSoftmax)
 from blockedattention_b200 import _lib as L
 from blockedattention_b200.plan import GemmPlan
 from blockedattention_b200.synth import workload
@@ -280,6 +281,40 @@ def test_host_entry_point_matches_device_call(cuda_device, groups):
         blockAttnScoresHost(A.to(dev), B, M, M, K, device=dev)              # device operand
     with pytest.raises(RuntimeError):
         blockAttnScoresHost(A, B, M, M, K, device=dev, head_groups=4)       # 4 does not divide 6 heads
+
+
+@pytest.mark.parametrize("dtype,d,lo,hi", [(F16, 64, 2, 64), (BF16, 64, 2, 300), (F16, 128, 65, 400)])
+def test_token_major_entry_matches_head_major(cuda_device, dtype, d, lo, hi):
+    # (sum n, H, d) operands read in place through strided tensor maps: same bits as permuting into strips first
+    dev = cuda_device
+    rs = np.random.RandomState(d + hi)
+    n = rs.randint(lo, hi + 1, size=24)
+    H = 3
+    T = int(n.sum())
+    g = torch.Generator().manual_seed(4)
+    q = torch.randn((T, H, d), generator=g).to(dtype).to(dev)
+    k = torch.randn((T, H, d), generator=g).to(dtype).to(dev)
+    got = blockAttnScoresTokenMajor(q, k, n, scale=0.1)
+    qs = q.permute(1, 0, 2).reshape(H, T * d).contiguous(); ks = k.permute(1, 0, 2).reshape(H, T * d).contiguous()
+    want = blockAttnScores(qs, ks, n, n, np.full_like(n, d), scale=0.1)
+    assert got.shape == want.shape and torch.equal(got, want)
+    assert_probs_close(got, O.block_scores(qs.cpu(), ks.cpu(), n, n, np.full_like(n, d), scale=0.1), "token-major vs oracle")
+    # scores only through the same path
+    got_s = blockAttnScoresTokenMajor(q, k, n, scale=0.1, softmax=False)
+    assert torch.equal(got_s, blockGEMM(qs, ks, None, None, None, n, n, np.full_like(n, d), scale=0.1))
+
+
+def test_token_major_entry_refuses_what_it_cannot_take(cuda_device):
+    dev = cuda_device
+    n = np.array([5, 9, 70])
+    q = torch.randn((int(n.sum()), 2, 32), device=dev).half()       # d = 32: no tensor-map kernel takes it
+    with pytest.raises(RuntimeError):
+        blockAttnScoresTokenMajor(q, q, n)
+    q = torch.randn((int(n.sum()), 2, 128), device=dev).half()      # d = 128 with small segments: register-fed kernel
+    with pytest.raises(RuntimeError):
+        blockAttnScoresTokenMajor(q, q, n)
+    with pytest.raises(RuntimeError):
+        blockAttnScoresTokenMajor(q[:, :, :64], q[:, :, :64], n)    # not contiguous
 
 
 def test_unaligned_pointer_is_handled(cuda_device):
