@@ -64,6 +64,7 @@ int upload_plan(blk_plan* p) {
     if ((rc = upload(p->packs, &p->d_packs, "upload packs")) != BLK_OK) return rc;
     if ((rc = upload(p->pack_blocks, &p->d_pack_blocks, "upload pack blocks")) != BLK_OK) return rc;
     if ((rc = upload(p->smx_chunks, &p->d_smx_chunks, "upload softmax chunks")) != BLK_OK) return rc;
+    if ((rc = upload(p->smx_windows, &p->d_smx_windows, "upload softmax windows")) != BLK_OK) return rc;
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&p->d_status), 2 * sizeof(int));
     if (e != cudaSuccess) return cuda_fail("allocate status word", e);
     e = cudaMemset(p->d_status, 0, 2 * sizeof(int));
@@ -217,6 +218,7 @@ extern "C" void blk_plan_destroy(blk_plan_t* p) {
         cudaFree(p->d_packs);
         cudaFree(p->d_pack_blocks);
         cudaFree(p->d_smx_chunks);
+        cudaFree(p->d_smx_windows);
         cudaFree(p->d_status);
     }
     delete p;
@@ -481,15 +483,18 @@ extern "C" int blk_softmax_run(const blk_plan_t* p, const void* src, void* out, 
         blk_set_error("blk_softmax_run: device pointers must be 16-byte aligned");
         return BLK_ERR_UNALIGNED;
     }
-    BlkSmxParams xp{};
-    xp.src = src;
-    xp.dst = out;
-    xp.chunks = p->d_smx_chunks;
+    BlkSmxPipeParams xp{};
+    xp.in0 = src;
+    xp.in1 = nullptr;
+    xp.out = out;
+    xp.windows = p->d_smx_windows;
+    xp.pieces = p->d_smx_chunks;
     xp.D = p->Dm1;
-    xp.num_chunks = (int)p->smx_chunks.size();
+    xp.num_windows = (int)p->smx_windows.size();
     xp.H = (int)p->H;
     xp.scale = scale;
-    cudaError_t e = blk_launch_softmax(xp, p->dtype_in, reinterpret_cast<cudaStream_t>(cuda_stream));
+    xp.status = p->d_status;
+    cudaError_t e = blk_launch_softmax_pipe(xp, p->dtype_in, 0, p->num_sms, reinterpret_cast<cudaStream_t>(cuda_stream));
     if (e != cudaSuccess) return cuda_fail("softmax launch", e);
     return BLK_OK;
 }
@@ -513,16 +518,18 @@ extern "C" int blk_softmax_backward_run(const blk_plan_t* p, const void* out, co
         blk_set_error("blk_softmax_backward_run: device pointers must be 16-byte aligned");
         return BLK_ERR_UNALIGNED;
     }
-    BlkSmxBwdParams xp{};
-    xp.out = out;
-    xp.grad_out = grad_out;
-    xp.grad_src = grad_src;
-    xp.chunks = p->d_smx_chunks;
+    BlkSmxPipeParams xp{};
+    xp.in0 = out;
+    xp.in1 = grad_out;
+    xp.out = grad_src;
+    xp.windows = p->d_smx_windows;
+    xp.pieces = p->d_smx_chunks;
     xp.D = p->Dm1;
-    xp.num_chunks = (int)p->smx_chunks.size();
+    xp.num_windows = (int)p->smx_windows.size();
     xp.H = (int)p->H;
     xp.scale = scale;
-    cudaError_t e = blk_launch_softmax_bwd(xp, p->dtype_in, reinterpret_cast<cudaStream_t>(cuda_stream));
+    xp.status = p->d_status;
+    cudaError_t e = blk_launch_softmax_pipe(xp, p->dtype_in, 1, p->num_sms, reinterpret_cast<cudaStream_t>(cuda_stream));
     if (e != cudaSuccess) return cuda_fail("softmax backward launch", e);
     return BLK_OK;
 }

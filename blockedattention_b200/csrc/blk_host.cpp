@@ -454,5 +454,26 @@ int blk_build_softmax_schedule(blk_plan* p) {
                     BlkSmxChunk{p->a1[s] + r * cols, (int32_t)std::min(rpc, rows - r), (int32_t)cols});
         }
     }
+    // Windows of the pipelined kernels: consecutive chunks that are contiguous in memory, up to the window size.
+    p->smx_windows.clear();
+    for (size_t c = 0; c < p->smx_chunks.size(); ++c) {
+        const BlkSmxChunk& ch = p->smx_chunks[c];
+        const int64_t nb = (int64_t)ch.rows * ch.cols * es;
+        bool extend = false;
+        if (!p->smx_windows.empty() && nb <= BLK_SMX_WINDOW_BYTES) {
+            const BlkSmxWindow& wd = p->smx_windows.back();
+            extend = wd.nbytes + nb <= BLK_SMX_WINDOW_BYTES && wd.npieces < BLK_SMX_WINDOW_PIECES &&
+                     wd.off + wd.nbytes / es == ch.off;
+        }
+        if (extend) {
+            p->smx_windows.back().nbytes += (int32_t)nb;
+            p->smx_windows.back().npieces += 1;
+        } else {
+            // a one-row piece longer than the window keeps its own window; its byte count only has to exceed the
+            // window size for the kernel to stream it
+            const int64_t capped = std::min<int64_t>(nb, (int64_t)BLK_SMX_WINDOW_BYTES + 1);
+            p->smx_windows.push_back(BlkSmxWindow{ch.off, (int32_t)capped, (int32_t)c, 1, 0});
+        }
+    }
     return BLK_OK;
 }

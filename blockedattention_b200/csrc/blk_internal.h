@@ -66,6 +66,18 @@ struct BlkSmxChunk {
     int32_t cols;
 };
 
+// One window of the pipelined softmax kernels: npieces consecutive chunks (pieces) that are contiguous in
+// memory and together at most BLK_SMX_WINDOW_BYTES long, or a single one-row piece longer than that.
+struct BlkSmxWindow {
+    int64_t off;          // element offset of the first piece inside the head strip
+    int32_t nbytes;       // bytes of all pieces
+    int32_t first_piece;  // index into the chunk table
+    int32_t npieces;
+    int32_t pad;
+};
+static_assert(sizeof(BlkSmxWindow) == 24, "BlkSmxWindow layout");
+constexpr int BLK_SMX_WINDOW_PIECES = 64;  // pieces a window may hold
+
 // Per-CTA tile of the tcgen05 kernel (filled in by blk_gemm_umma.cu's planner).
 struct BlkUmmaItem {
     int32_t seg;
@@ -108,6 +120,7 @@ struct blk_plan {
     std::vector<BlkSmallItem> small_items[BLK_SMALL_BUCKETS];  // packed small-segment kernel, by column count
     std::vector<BlkUmmaItem> umma_items;    // tcgen05 kernel
     std::vector<BlkSmxChunk> smx_chunks;    // softmax kernel (also second pass of fp32 scores)
+    std::vector<BlkSmxWindow> smx_windows;  // pipelined softmax kernels: groups of chunks
     int umma_K = 0;                         // uniform K of the tcgen05 bin
     int small_K = 0;                        // uniform K of the small bin
     int small_pipe = 0;                     // 1: the small segments run as packs on the pipelined kernel
@@ -124,6 +137,7 @@ struct blk_plan {
     int num_sms = 148;
     BlkUmmaItem* d_umma_items = nullptr;
     BlkSmxChunk* d_smx_chunks = nullptr;
+    BlkSmxWindow* d_smx_windows = nullptr;
     int* d_status = nullptr;
     int* d_counter = nullptr;  // persistent-kernel tile counter
 };

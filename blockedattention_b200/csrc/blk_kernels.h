@@ -95,18 +95,6 @@ struct BlkSmxParams {
     float scale;
 };
 
-// Backward of the row softmax: grad_src = scale * (grad_out - rowsum(out * grad_out)) * out.
-struct BlkSmxBwdParams {
-    const void* out;       // forward result (probabilities)
-    const void* grad_out;  // gradient with respect to the forward result
-    void* grad_src;        // may alias grad_out
-    const BlkSmxChunk* chunks;
-    int64_t D;
-    int num_chunks;
-    int H;
-    float scale;
-};
-
 // Tensor map (128-byte swizzle) over such an operand, boxes of box_k x box_rows of one head.  The dimension
 // with the smaller stride comes second: *head_first = 0 means coordinates (k, row, head), 1 means (k, head, row).
 // False when the driver's encoder is unavailable or rejects the view.  Defined in blk_gemm_umma.cu.
@@ -115,7 +103,21 @@ bool blk_make_row_map(CUtensorMap_st* map, const void* base, int bf16, int64_t K
                       int box_k, int box_rows, int* head_first);
 
 cudaError_t blk_launch_gemm_tile(const BlkGemmParams& p, int dtype_in, int ta, int tb, cudaStream_t st);
-cudaError_t blk_launch_softmax_bwd(const BlkSmxBwdParams& p, int dtype, cudaStream_t st);
+// Pipelined softmax kernels (blk_softmax_pipe.cu).  Forward: in0 = src, in1 unused; backward: in0 = forward
+// result, in1 = its gradient (out may alias in1).
+struct BlkSmxPipeParams {
+    const void* in0;
+    const void* in1;
+    void* out;
+    const BlkSmxWindow* windows;
+    const BlkSmxChunk* pieces;
+    int64_t D;
+    int num_windows;
+    int H;
+    float scale;
+    int* status;
+};
+cudaError_t blk_launch_softmax_pipe(const BlkSmxPipeParams& p, int dtype, int backward, int sms, cudaStream_t st);
 cudaError_t blk_launch_gemm_simt(const BlkSimtParams& p, cudaStream_t st);
 cudaError_t blk_launch_scores_small(const BlkSmallParams& p, int dtype_in, int K, int bucket, int sms,
                                     cudaStream_t st);

@@ -50,12 +50,15 @@ def test_noalloc_matches_plan_path_on_two_calls_in_a_row(cuda_device):
         assert call_noalloc(x, out, rows, cols, H, scale) == L.BLK_OK, L.lib.blk_last_error()
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated(dev) == before
-        assert torch.equal(out, ref), "the two entry points run the same kernel on the same chunks"
+        # the plan path runs the pipelined kernel, this entry point the one-window-per-CTA kernel: same fp32
+        # arithmetic up to the order of the row sums, so results agree to a unit in the last place
+        ulp = {torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7, torch.float32: 2.0 ** -21}[dtype]
+        assert float((out.float() - ref.float()).abs().max()) <= ulp
         assert_probs_close(out, O.block_softmax(X, rows, cols, scale=scale), "no-alloc vs oracle")
         # in place as well
         assert call_noalloc(x, x, rows, cols, H, scale) == L.BLK_OK
         torch.cuda.synchronize()
-        assert torch.equal(x, ref)
+        assert torch.equal(x, out), "in place gives the same bits as out of place"
 
 
 def test_noalloc_rejects_what_it_cannot_hold(cuda_device):
