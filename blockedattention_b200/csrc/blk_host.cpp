@@ -288,6 +288,11 @@ int blk_build_gemm_schedule(blk_plan* p) {
         double best = 0;
         for (auto& kv : work)
             if (kv.second > best) { best = kv.second; p->umma_K = (int)kv.first; }
+        // A separate launch pays only if it takes a real share of the batch: when the segments it could take
+        // carry under a tenth of all multiply-adds, they stay with the staged kernel.
+        double all = 0;
+        for (int64_t s = 0; s < S; ++s) all += (double)p->M[s] * (double)p->N[s] * (double)p->K[s];
+        if (best < 0.1 * all && !blk_env_flag("BLK_FORCE_UMMA")) p->umma_K = 0;
     }
     p->segs.resize(S);
     p->flops = p->bytes = 0;
