@@ -114,8 +114,7 @@ __device__ __forceinline__ uint32_t tma_run(uint32_t dst, const CUtensorMap* m64
         const int rem = rows - r;
         const int box = rem > 48 ? 64 : (rem > 16 ? 32 : 16);
         const CUtensorMap* m = box == 64 ? m64 : (box == 32 ? m32 : m16);
-        if (head_first) tma_rows(dst + r * ROWB, m, bar, head, row0 + r);
-        else tma_rows(dst + r * ROWB, m, bar, row0 + r, head);
+        tma_rows(dst + r * ROWB, m, bar, head_first ? head : row0 + r, head_first ? row0 + r : head);
         r += box;
     }
     return (uint32_t)r * ROWB;

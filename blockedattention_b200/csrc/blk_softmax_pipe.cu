@@ -6,7 +6,7 @@
 //   * one thread fetches the next window with a bulk asynchronous copy (cp.async.bulk, completion on the
 //     stage's mbarrier) of the 16-byte aligned range that covers it -- no thread waits for a load it issued;
 //   * all threads do the row arithmetic of the current window out of shared memory (fp32, base-2 exponent,
-//     one rounding): sub-warp groups for short rows; one warp per longer row, which reads and writes the row as
+//     one rounding): one lane per short row (one warp per small segment); one warp per longer row, which reads and writes the row as
 //     16-byte vectors between its first and last 16-byte boundary (the few elements outside go one per lane)
 //     and keeps up to 1024 columns in registers between the maximum, the sum and the normalisation;
 //   * one thread writes the window back with a bulk asynchronous store of the aligned vectors that lie wholly
@@ -130,42 +130,7 @@ __device__ __forceinline__ void sp_bulk_wait_all() { asm volatile("cp.async.bulk
 
 // ---- row arithmetic on a piece that sits in shared memory ---------------------------------------------------
 
-// forward, rows of at most EPL*G columns, G lanes per row, values kept in registers
-template <typename IO, int EPL>
-__device__ __forceinline__ void fwd_rows_in_regs(typename IO::E* srow, int rows, int cols, int G, float sl, int warp,
-                                                 int lane) {
-    const int rpw = 32 / G;
-    const int gl = lane & (G - 1), gi = lane / G;
-    for (int rb = warp * rpw; rb < rows; rb += SP_WARPS * rpw) {
-        const int r = rb + gi;
-        const bool valid = r < rows;
-        typename IO::E* row = srow + (size_t)(valid ? r : 0) * cols;
-        float v[EPL];
-        float mx = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) {
-            const int c = gl + i * G;
-            v[i] = (valid && c < cols) ? IO::ld(row[c]) * sl : -INFINITY;
-            mx = fmaxf(mx, v[i]);
-        }
-        mx = sp_max(mx, G);
-        if (!valid) mx = 0.f;
-        float sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) {
-            v[i] = blk_exp2(v[i] - mx);
-            sum += v[i];
-        }
-        sum = sp_sum(sum, G);
-        const float inv = 1.f / sum;
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) {
-            const int c = gl + i * G;
-            if (valid && c < cols) row[c] = IO::st(v[i] * inv);
-        }
-    }
-}
-// A row of at least 16 vectors' worth of columns, one warp per row: the row starts at an arbitrary element of
+// A row of at least 8 vectors' worth of columns, one warp per row: the row starts at an arbitrary element of
 // shared memory, so it is split into the elements before the first 16-byte boundary (at most VE - 1, one per
 // lane 0..7), whole 16-byte vectors (lane l takes vectors l, l + 32, ...) and the elements after the last
 // whole vector (one per lane 8..15).
@@ -305,13 +270,59 @@ __device__ __forceinline__ void bwd_rows_vec(const typename IO::E* ppiece, typen
     }
 }
 
+// Short rows (fewer columns than eight vectors): one lane per row, one warp per piece, so a window of many
+// small segments keeps every warp busy and no shuffle is needed.  Up to 32 columns stay in registers.
 template <typename IO>
-__device__ __forceinline__ void fwd_piece(typename IO::E* srow, int rows, int cols, float sl, int warp, int lane) {
+__device__ __forceinline__ void fwd_rows_lane(typename IO::E* piece, int rows, int cols, float sl, int lane) {
+    for (int r = lane; r < rows; r += 32) {
+        typename IO::E* row = piece + (size_t)r * cols;
+        if (cols <= 32) {
+            float v[32];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                v[c] = c < cols ? IO::ld(row[c]) * sl : -INFINITY;
+                mx = fmaxf(mx, v[c]);
+            }
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                v[c] = blk_exp2(v[c] - mx);
+                sum += v[c];
+            }
+            const float inv = 1.f / sum;
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+                if (c < cols) row[c] = IO::st(v[c] * inv);
+        } else {
+            float mx = -INFINITY;
+            for (int c = 0; c < cols; ++c) mx = fmaxf(mx, IO::ld(row[c]) * sl);
+            float sum = 0.f;
+            for (int c = 0; c < cols; ++c) sum += blk_exp2(fmaf(IO::ld(row[c]), sl, -mx));
+            const float inv = 1.f / sum;
+            for (int c = 0; c < cols; ++c) row[c] = IO::st(blk_exp2(fmaf(IO::ld(row[c]), sl, -mx)) * inv);
+        }
+    }
+}
+template <typename IO>
+__device__ __forceinline__ void bwd_rows_lane(const typename IO::E* ppiece, typename IO::E* gpiece, int rows, int cols,
+                                              float scale, int lane) {
+    for (int r = lane; r < rows; r += 32) {
+        const typename IO::E* prow = ppiece + (size_t)r * cols;
+        typename IO::E* grow = gpiece + (size_t)r * cols;
+        float dot = 0.f;
+        for (int c = 0; c < cols; ++c) dot = fmaf(IO::ld(prow[c]), IO::ld(grow[c]), dot);
+        for (int c = 0; c < cols; ++c) grow[c] = IO::st((IO::ld(grow[c]) - dot) * IO::ld(prow[c]) * scale);
+    }
+}
+
+// One piece.  Pieces of short rows are dealt out to the warps one piece each (piece index pi); the warps share
+// the rows of a piece of longer rows.
+template <typename IO>
+__device__ __forceinline__ void fwd_piece(typename IO::E* srow, int rows, int cols, float sl, int pi, int warp, int lane) {
     constexpr int VE = IO::VE;
-    if (cols < 16 * VE) {  // short rows: several rows per warp
-        int G = 1;
-        while (G * 4 < cols) G <<= 1;  // G in {1,2,4,8,16,32}
-        fwd_rows_in_regs<IO, 4>(srow, rows, cols, G, sl, warp, lane);
+    if (cols < 8 * VE) {
+        if (pi % SP_WARPS == warp) fwd_rows_lane<IO>(srow, rows, cols, sl, lane);
         return;
     }
     const int nvmax = cols / VE;  // whole vectors of a row never exceed this
@@ -323,26 +334,12 @@ __device__ __forceinline__ void fwd_piece(typename IO::E* srow, int rows, int co
 // backward: the result overwrites the gradient piece
 template <typename IO>
 __device__ __forceinline__ void bwd_piece(const typename IO::E* prow0, typename IO::E* grow0, int rows, int cols, float scale,
-                                          int warp, int lane) {
-    if (cols >= 16 * IO::VE) {
+                                          int pi, int warp, int lane) {
+    if (cols >= 8 * IO::VE) {
         bwd_rows_vec<IO, SP_WARPS>(prow0, grow0, rows, cols, scale, warp, lane);
         return;
     }
-    int G = 1;
-    while (G * 4 < cols) G <<= 1;  // G in {1,2,4,8,16,32}
-    const int rpw = 32 / G, gl = lane & (G - 1), gi = lane / G;
-    for (int rb = warp * rpw; rb < rows; rb += SP_WARPS * rpw) {
-        const int r = rb + gi;
-        const bool valid = r < rows;
-        const typename IO::E* prow = prow0 + (size_t)(valid ? r : 0) * cols;
-        typename IO::E* grow = grow0 + (size_t)(valid ? r : 0) * cols;
-        float dot = 0.f;
-        if (valid)
-            for (int c = gl; c < cols; c += G) dot += IO::ld(prow[c]) * IO::ld(grow[c]);
-        dot = sp_sum(dot, G);
-        if (valid)
-            for (int c = gl; c < cols; c += G) grow[c] = IO::st((IO::ld(grow[c]) - dot) * IO::ld(prow[c]) * scale);
-    }
+    if (pi % SP_WARPS == warp) bwd_rows_lane<IO>(prow0, grow0, rows, cols, scale, lane);
 }
 
 __device__ __forceinline__ float sp_cta_reduce(float v, bool is_max, float* red, int warp, int lane) {
@@ -445,8 +442,8 @@ __global__ void __launch_bounds__(SP_THREADS, BWD ? 3 : 6) blk_softmax_pipe_kern
             int eo = 0;
             for (int pi = 0; pi < win.npieces; ++pi) {
                 const BlkSmxChunk pc = recs[st][pi];
-                if (!BWD) fwd_piece<IO>(r0 + eo, pc.rows, pc.cols, sl, warp, lane);
-                else bwd_piece<IO>(p0 + eo, r0 + eo, pc.rows, pc.cols, sl, warp, lane);
+                if (!BWD) fwd_piece<IO>(r0 + eo, pc.rows, pc.cols, sl, pi, warp, lane);
+                else bwd_piece<IO>(p0 + eo, r0 + eo, pc.rows, pc.cols, sl, pi, warp, lane);
                 eo += pc.rows * pc.cols;
             }
         }
