@@ -547,7 +547,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                     mx = m;
                     sum = l;
                 }
-                const float nm = -mx * sl, inv = __frcp_rn(sum);
+                const float off = -mx * sl - __log2f(sum);  // exp2(x * sl + off) = exp2((x - max) * sl) / sum: no multiply after the exponential
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
                     const int buf = slot & 1;
                     if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 7)) { ok = false; break; }
@@ -557,7 +557,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                     if (lo < hi)
                         store_cols(ch * UM_BN + lo, ch * UM_BN + hi,
                                    [&](int c) { return (uint32_t)(buf * UM_BN + (c - ch * UM_BN)); },
-                                   [&](float x) { return blk_exp2(fmaf(x, sl, nm)) * inv; }, cbase, M, N);
+                                   [&](float x) { return blk_exp2(fmaf(x, sl, off)); }, cbase, M, N);
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty_bar(buf));
