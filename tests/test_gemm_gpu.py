@@ -232,6 +232,40 @@ def test_long_tail_full_size_properties(cuda_device):
         assert_probs_close(P[:, ao[s]:ao[s + 1]], ref, f"segment {s} (n={n})")
 
 
+def test_output_larger_than_2_to_31_elements(cuda_device):
+    # one head strip of more than 2^31 output elements (upstream truncates such offsets to int,
+    # csrc/cuda/spBlkGEMM.cu:996-998): 64-bit addressing in the tcgen05 kernel, the pack kernel behind it in the
+    # same strip and the pipelined softmax; sampled rows against torch on the device
+    dev = cuda_device
+    n_big, n_small = 46400, 40
+    n = np.array([n_big, n_small]); K = np.array([64, 64])
+    g = torch.Generator(device=dev).manual_seed(3)
+    q = (torch.randn((1, int(n.sum()) * 64), generator=g, device=dev) * 0.5).to(BF16)
+    k = (torch.randn((1, int(n.sum()) * 64), generator=g, device=dev) * 0.5).to(BF16)
+    P = blockAttnScores(q, k, n, n, K, scale=0.125)
+    torch.cuda.synchronize()
+    assert P.numel() == n_big * n_big + n_small * n_small and P.numel() > 2 ** 31
+    qb = q[0, :n_big * 64].reshape(n_big, 64).float(); kb = k[0, :n_big * 64].reshape(n_big, 64).float()
+    for r in (0, 1, 12345, 46271, n_big - 1):
+        want = torch.softmax((qb[r] @ kb.T) * 0.125, dim=-1)
+        got = P[0, r * n_big:(r + 1) * n_big].float()
+        assert float((got - want).abs().max()) <= 2e-3, r
+    # the small segment sits behind the 2^31-th element of the strip
+    off = n_big * n_big
+    qs = q[0, n_big * 64:].reshape(n_small, 64).float(); ks = k[0, n_big * 64:].reshape(n_small, 64).float()
+    want = torch.softmax((qs @ ks.T) * 0.125, dim=-1)
+    got = P[0, off:].reshape(n_small, n_small).float()
+    assert float((got - want).abs().max()) <= 2e-3
+    # standalone softmax over the same strip, in place: a probability row of n equal... rows still sum to one
+    S = blockSoftmax(P, n, n, out=P)
+    torch.cuda.synchronize()
+    for r in (0, 30000, n_big - 1):
+        assert abs(float(S[0, r * n_big:(r + 1) * n_big].float().sum()) - 1.0) < 2e-2
+    assert abs(float(S[0, off:off + n_small].float().sum()) - 1.0) < 2e-2
+    del P, S, q, k
+    torch.cuda.empty_cache()
+
+
 def test_python_surface_matches_upstream_contract(cuda_device):
     dev = cuda_device
     M = torch.tensor([33, 99, 64], device=dev); K = torch.tensor([64, 64, 64], device=dev)
