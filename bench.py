@@ -200,8 +200,8 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from blockedattention_b200 import blockAttnScores, blockAttnScoresHost, blockGEMM, partition
-    from blockedattention_b200.plan import GemmPlan
+    from blockedattention_b200 import blockAttention, blockAttnScores, blockAttnScoresHost, blockGEMM, partition
+    from blockedattention_b200.plan import AttentionPlan, GemmPlan
     from blockedattention_b200.synth import workload
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -224,22 +224,29 @@ def main():
     w = wg.slice(int(bounds[rank]), int(bounds[rank + 1]))
     imb = partition.imbalance(cost, bounds)
 
-    plan = GemmPlan(w.M, w.N, w.K, w.H, w.dtype, w.out_dtype, False, False, w.softmax, device=dev)
+    fused_attn = bool(w.extra.get("fused_attention"))
+    if fused_attn:
+        plan = AttentionPlan(w.M, w.N, w.H, w.dtype, device=dev)
+    else:
+        plan = GemmPlan(w.M, w.N, w.K, w.H, w.dtype, w.out_dtype, False, False, w.softmax, device=dev)
     plan_pv = None
-    if w.d_v:
+    if w.d_v and not fused_attn:
         dv = np.full_like(w.N, w.d_v)
         plan_pv = GemmPlan(w.M, dv, w.N, w.H, w.out_dtype, w.out_dtype, False, True, False, device=dev)
     nbuf = max(1, args.nbuf)
     sets = []
     for i in range(nbuf):
         ins = w.make_inputs(dev, seed=1000 * rank + i + args.seed)
-        out = torch.empty((w.H, plan.Dout), dtype=w.out_dtype, device=dev)
+        out = None if fused_attn else torch.empty((w.H, plan.Dout), dtype=w.out_dtype, device=dev)
         o2 = torch.empty((w.H, int(w.M.sum()) * w.d_v), dtype=w.out_dtype, device=dev) if w.d_v else None
         sets.append((ins, out, o2))
     launches_per_step = plan.summary["launches"] + (plan_pv.summary["launches"] if plan_pv else 0)
 
     def step(i):
         ins, out, o2 = sets[i % nbuf]
+        if fused_attn:
+            plan.run(ins[0], ins[1], ins[2], out=o2, scale=w.scale)
+            return
         plan.run(ins[0], ins[1], out=out, scale=w.scale)
         if plan_pv is not None:
             plan_pv.run(out, ins[2], out=o2)
@@ -311,7 +318,7 @@ def main():
         for i in range(nh):
             ins = sets[i % nbuf][0]
             host.append(tuple(t.cpu().pin_memory() for t in ins))
-        h_out = torch.empty((w.H, plan.Dout), dtype=w.out_dtype).pin_memory()
+        h_out = None if fused_attn else torch.empty((w.H, plan.Dout), dtype=w.out_dtype).pin_memory()
         h_o2 = torch.empty((w.H, int(w.M.sum()) * w.d_v), dtype=w.out_dtype).pin_memory() if w.d_v else None
         dl = np.full_like(w.N, w.d_v) if w.d_v else None
 
@@ -324,6 +331,10 @@ def main():
                 return
             q = hin[0].to(dev, non_blocking=True)
             k = hin[1].to(dev, non_blocking=True)
+            if fused_attn:
+                v = hin[2].to(dev, non_blocking=True)
+                h_o2.copy_(blockAttention(q, k, v, w.M, w.N, scale=w.scale), non_blocking=True)
+                return
             if w.softmax:
                 p = blockAttnScores(q, k, w.M, w.N, w.K, scale=w.scale, out_dtype=w.out_dtype)
             else:
@@ -350,10 +361,11 @@ def main():
             dist.all_reduce(ems, op=dist.ReduceOp.MAX)
         e_ms = float(ems.item()) / e2e_steps
         h2d = sum(t.numel() * t.element_size() for t in host[0])
-        d2h = (h_o2 if w.d_v else h_out).numel() * h_out.element_size()
+        d2h = (h_o2 if w.d_v else h_out).numel() * (h_o2 if w.d_v else h_out).element_size()
         e2e = {"value": flops_all / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e_ms,
                "steps": e2e_steps, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-               "api": ("blockedattention_b200.blockAttnScoresHost on pinned host tensors (per rank)"
+               "api": ("blockedattention_b200.blockAttention with explicit copies of pinned host tensors" if fused_attn else
+                       "blockedattention_b200.blockAttnScoresHost on pinned host tensors (per rank)"
                        if w.softmax and not w.d_v else
                        "blockedattention_b200.blockGEMM / blockAttnScores with explicit copies of pinned host tensors")}
     sampler.stop()

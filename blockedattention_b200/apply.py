@@ -29,7 +29,7 @@ import numpy as np
 import torch
 
 from . import _lib as L
-from .plan import GemmPlan, SoftmaxPlan, _host_i64
+from .plan import AttentionPlan, GemmPlan, SoftmaxPlan, _host_i64
 
 _CACHE: "OrderedDict[tuple, object]" = OrderedDict()
 _CACHE_MAX = 32
@@ -226,6 +226,40 @@ def blockAttnScores(q: torch.Tensor, k: torch.Tensor, MList, NList, KList, scale
     scores are never written to memory."""
     return blockGEMM(q, k, None, None, None, MList, NList, KList, False, False,
                      scale=scale, out_dtype=out_dtype, softmax=True)
+
+
+def blockAttention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, MList, NList, scale: float = 1.0,
+                   d: Optional[int] = None) -> torch.Tensor:
+    """``softmax_rows(scale * Q_s K_s^T) V_s`` per segment: ``q -> (H, sum m_s*d)``, ``k, v -> (H, sum n_s*d)``, result
+    ``(H, sum m_s*d)``, all packed head-major.  Batches of segments with at most 64 rows and columns, ``d = 64`` and
+    16-bit inputs run as one kernel that never stores the probabilities; any other batch is the composition
+    ``blockGEMM(blockAttnScores(q, k), v, transpose2=True)`` of the two operators.  Forward only."""
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _check_operand(name, t)
+    M, N = _host_i64(MList), _host_i64(NList)
+    rows_q, rows_kv = int(M.sum()), int(N.sum())
+    if rows_q <= 0 or rows_kv <= 0:
+        raise RuntimeError("blockAttention needs at least one query row and one key row")
+    if d is None:
+        d = 64 if q.numel() % (rows_q * 64) == 0 and k.numel() == (q.numel() // (rows_q * 64)) * rows_kv * 64 else None
+        if d is None:
+            raise RuntimeError("give the head dimension d (it cannot be told apart from the number of heads)")
+    if q.numel() % (rows_q * d) or k.numel() != (q.numel() // (rows_q * d)) * rows_kv * d or v.numel() != k.numel():
+        raise RuntimeError("q / k / v do not match the packed extents of the lists")
+    H = q.numel() // (rows_q * d)
+    fused = (d == 64 and q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
+             and int(M.max()) <= 64 and int(N.max()) <= 64 and int(N[M > 0].min() if (M > 0).any() else 1) >= 1)
+    if fused:
+        key = ("attn", M.tobytes(), N.tobytes(), H, q.dtype, str(q.device))
+        try:
+            plan = _cached(key, lambda: AttentionPlan(M, N, H, q.dtype, device=q.device))
+            return plan.run(q, k, v, scale=scale)
+        except L.BlkError as e:
+            if e.code != L.BLK_ERR_UNSUPPORTED:
+                raise
+    dl = np.full_like(M, d)
+    p = blockGEMM(q, k, None, None, None, M, N, dl, False, False, scale=scale, softmax=True)
+    return blockGEMM(p, v, None, None, None, M, dl, N, False, True)
 
 
 def blockAttnScoresTokenMajor(q: torch.Tensor, k: torch.Tensor, nList, scale: float = 1.0,

@@ -299,10 +299,122 @@ extern "C" int blk_plan_check(const blk_plan_t* p, void* cuda_stream) {
     return BLK_OK;
 }
 
+extern "C" int blk_attention_plan_create(blk_plan_t** plan, const int64_t* M, const int64_t* N, int64_t S, int64_t H,
+                                         int dtype, int device) {
+    if (!plan) {
+        blk_set_error("blk_attention_plan_create: plan is null");
+        return BLK_ERR_INVALID;
+    }
+    *plan = nullptr;
+    if (S < 0 || H < 0 || (S > 0 && (!M || !N))) {
+        blk_set_error("blk_attention_plan_create: negative count or null list");
+        return BLK_ERR_INVALID;
+    }
+    if (dtype != BLK_F16 && dtype != BLK_BF16) {
+        blk_set_error("blk_attention_plan_create: fp16 or bf16 only");
+        return BLK_ERR_UNSUPPORTED;
+    }
+    for (int64_t s = 0; s < S; ++s)
+        if (M[s] < 0 || N[s] < 0 || M[s] > BLK_SMALL_MAXM || N[s] > BLK_SMALL_MAXN || (M[s] > 0 && N[s] == 0)) {
+            blk_set_error("blk_attention_plan_create: the fused kernel takes segments of 0..64 queries and 1..64 keys "
+                          "(segment " + std::to_string(s) + "); compose the two operators for other batches");
+            return BLK_ERR_UNSUPPORTED;
+        }
+    blk_plan* p = new (std::nothrow) blk_plan();
+    if (!p) return BLK_ERR_NOMEM;
+    p->kind = 0;
+    p->attn = 1;
+    p->S = S;
+    p->H = H;
+    p->dtype_in = p->dtype_out = dtype;
+    p->ta = p->tb = 0;
+    p->epi = BLK_EPI_SOFTMAX;
+    p->device = device;
+    p->M.assign(M, M + S);
+    p->N.assign(N, N + S);
+    p->K.assign((size_t)S, 64);
+    p->a1.assign((size_t)S + 1, 0);
+    p->a2.assign((size_t)S + 1, 0);
+    for (int64_t s = 0; s < S; ++s) {
+        p->a1[s + 1] = p->a1[s] + M[s] * 64;
+        p->a2[s + 1] = p->a2[s] + N[s] * 64;
+    }
+    p->ao = p->a1;  // the result has one row of 64 per query row, laid out like the queries
+    int rc = blk_build_gemm_schedule(p);
+    size_t nonempty = 0;
+    for (int64_t s = 0; s < S; ++s) nonempty += M[s] > 0 && N[s] > 0;
+    if (rc == BLK_OK && nonempty > 0 &&
+        (!p->small_pipe || !p->tile_items.empty() || !p->umma_items.empty() || !p->simt_items.empty())) {
+        blk_set_error("blk_attention_plan_create: the pack kernel cannot take this batch (BLK_DISABLE_PIPE or "
+                      "BLK_DISABLE_SMALL set?)");
+        rc = BLK_ERR_UNSUPPORTED;
+    }
+    if (rc == BLK_OK) {
+        p->flops = p->bytes = 0;
+        for (int64_t s = 0; s < S; ++s) {
+            p->flops += 4.0 * (double)H * (double)M[s] * (double)N[s] * 64.0;
+            p->bytes += (double)H * 2.0 * 64.0 * (double)(2 * M[s] + 2 * N[s]);
+        }
+    }
+    if (rc == BLK_OK && !grid_ok((int64_t)p->packs.size(), H, "attention plan")) rc = BLK_ERR_UNSUPPORTED;
+    if (rc == BLK_OK) rc = upload_plan(p);
+    if (rc != BLK_OK) {
+        blk_plan_destroy(p);
+        return rc;
+    }
+    *plan = p;
+    return BLK_OK;
+}
+
+extern "C" int blk_attention_run(const blk_plan_t* p, const void* q, const void* k, const void* v, void* out,
+                                 float scale, void* cuda_stream) {
+    if (!p || p->kind != 0 || !p->attn) {
+        blk_set_error("blk_attention_run: not an attention plan");
+        return BLK_ERR_INVALID;
+    }
+    if (p->device < 0) {
+        blk_set_error("blk_attention_run: the plan was created without a device");
+        return BLK_ERR_INVALID;
+    }
+    if (p->packs.empty() || p->H == 0) return BLK_OK;
+    if (!q || !k || !v || !out) {
+        blk_set_error("blk_attention_run: null buffer");
+        return BLK_ERR_INVALID;
+    }
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) {
+        blk_set_error("blk_attention_run: device pointers must be 16-byte aligned");
+        return BLK_ERR_UNALIGNED;
+    }
+    if (scale == 0.f) scale = 1.17549435e-38f;  // softmax(0 * S) is the uniform distribution
+    BlkPackParams pp{};
+    pp.A = reinterpret_cast<const uint16_t*>(q);
+    pp.B = reinterpret_cast<const uint16_t*>(k);
+    pp.V = reinterpret_cast<const uint16_t*>(v);
+    pp.C = out;
+    pp.packs = p->d_packs;
+    pp.blocks = p->d_pack_blocks;
+    pp.Dm1 = p->Dm1; pp.Dm2 = p->Dm2; pp.Dout = p->Dm1;
+    pp.num_packs = (int)p->packs.size();
+    pp.H = (int)p->H;
+    pp.epi = BLK_EPI_SOFTMAX;
+    pp.scale = scale;
+    pp.status = p->d_status;
+    pp.layA = BlkOperandLayout{p->Dm1 / 64, 64, p->Dm1};
+    pp.layB = BlkOperandLayout{p->Dm2 / 64, 64, p->Dm2};
+    pp.layV = pp.layB;
+    cudaError_t e = blk_launch_scores_pipe(pp, p->dtype_in, p->num_sms, reinterpret_cast<cudaStream_t>(cuda_stream));
+    if (e != cudaSuccess) return cuda_fail("attention launch", e);
+    return BLK_OK;
+}
+
 // Shared body of blk_gemm_run and blk_gemm_run_strided; layA / layB say where the operands' rows are (null:
 // packed head-major strips, whose row view depends on the contraction length of the kernel that reads them).
 static int gemm_run_impl(const blk_plan* p, const void* mat1, const void* mat2, void* out, float scale,
                          const BlkOperandLayout* layA, const BlkOperandLayout* layB, void* cuda_stream) {
+    if (p && p->attn) {
+        blk_set_error("blk_gemm_run: this is an attention plan, run it with blk_attention_run");
+        return BLK_ERR_INVALID;
+    }
     auto layout = [](const BlkOperandLayout* given, int64_t D, int64_t K) {
         return given ? *given : BlkOperandLayout{D / K, K, D};
     };

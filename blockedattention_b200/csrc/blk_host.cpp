@@ -364,6 +364,7 @@ int blk_build_gemm_schedule(blk_plan* p) {
         rows_ok = p->segs[small_segs[q]].offA % 64 == 0 && p->segs[small_segs[q]].offB % 64 == 0;
     if (p->small_K == 64 && p->dtype_out != BLK_F32 && rows_ok && !blk_env_flag("BLK_DISABLE_PIPE") && !small_segs.empty()) {
         p->small_pipe = 1;
+        const int pack_rows = p->attn ? BLK_PACK_ROWS_ATTN : BLK_PACK_ROWS;
         struct Tmp { BlkPack pk; std::vector<BlkPackBlock> blocks; double cost; };
         std::vector<Tmp> tmp;
         for (size_t q = 0; q < small_segs.size(); ++q) {
@@ -373,7 +374,7 @@ int blk_build_gemm_schedule(blk_plan* p) {
             if (!tmp.empty()) {
                 const Tmp& t = tmp.back();
                 extend = t.pk.offA + (int64_t)t.pk.rowsA * 64 == sd.offA && t.pk.offB + (int64_t)t.pk.rowsB * 64 == sd.offB &&
-                         t.pk.rowsA + sd.M <= BLK_PACK_ROWS && t.pk.rowsB + sd.N <= BLK_PACK_ROWS &&
+                         t.pk.rowsA + sd.M <= pack_rows && t.pk.rowsB + sd.N <= pack_rows &&
                          t.pk.nblocks + mblocks <= BLK_PACK_BLOCKS;
             }
             if (!extend) {
@@ -384,7 +385,8 @@ int blk_build_gemm_schedule(blk_plan* p) {
             }
             Tmp& t = tmp.back();
             for (int32_t mb = 0; mb < mblocks; ++mb)
-                t.blocks.push_back(BlkPackBlock{sd.offC + (int64_t)mb * 16 * sd.N, t.pk.rowsA + 16 * mb, t.pk.rowsB,
+                // output of the block: M x N scores, or for an attention plan M x 64 result rows
+                t.blocks.push_back(BlkPackBlock{sd.offC + (int64_t)mb * 16 * (p->attn ? 64 : sd.N), t.pk.rowsA + 16 * mb, t.pk.rowsB,
                                                 std::min<int32_t>(16, sd.M - 16 * mb), sd.N, 0, 0});
             t.pk.rowsA += sd.M;
             t.pk.rowsB += sd.N;

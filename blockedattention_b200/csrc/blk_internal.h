@@ -100,6 +100,7 @@ constexpr int BLK_SMALL_WARPS = 4;
 constexpr int BLK_SMALL_MAXM = 64;
 constexpr int BLK_SMALL_BUCKETS = 2;  // N <= 32, N <= 64
 constexpr int BLK_PACK_ROWS = 192;    // rows of each operand a pack may hold
+constexpr int BLK_PACK_ROWS_ATTN = 128;  // same for the attention variant, whose slots hold a third operand
 constexpr int BLK_PACK_BLOCKS = 16;   // segments a pack may hold
 constexpr int BLK_SMX_WINDOW_BYTES = 16384;
 constexpr int BLK_UMMA_BM = 128;
@@ -124,6 +125,7 @@ struct blk_plan {
     int umma_K = 0;                         // uniform K of the tcgen05 bin
     int small_K = 0;                        // uniform K of the small bin
     int small_pipe = 0;                     // 1: the small segments run as packs on the pipelined kernel
+    int attn = 0;                           // 1: attention plan (every segment in packs, result = softmax(QK^T) V)
     std::vector<BlkPack> packs;
     std::vector<BlkPackBlock> pack_blocks;
     BlkPack* d_packs = nullptr;

@@ -83,6 +83,10 @@ struct BlkPackParams {
     int* status;
     BlkOperandLayout layA, layB;   // where the operands' rows are (filled by the caller)
     int head_firstA, head_firstB;  // coordinate order of the tensor maps (filled by the launcher)
+    // attention variant (V != null): C receives softmax(scale A B^T) V, 64 columns per first-operand row
+    const uint16_t* V;
+    BlkOperandLayout layV;
+    int head_firstV;
 };
 
 struct BlkSmxParams {

@@ -46,20 +46,29 @@ constexpr int ROWB = PK * 2;  // bytes per operand row
 #endif
 constexpr int P_CONSUMERS = BLK_PIPE_CONSUMERS;
 constexpr int P_THREADS = 32 * (1 + P_CONSUMERS);
-constexpr int P_OPER_BYTES = BLK_PACK_ROWS * ROWB;  // 24 KB per operand per slot
 constexpr int P_REC_BYTES = 1024;  // block records, padded so that every slot starts on a swizzle-atom boundary
 static_assert(BLK_PACK_BLOCKS * (int)sizeof(BlkPackBlock) <= P_REC_BYTES, "record area");
-constexpr int P_SLOT_BYTES = 2 * P_OPER_BYTES + P_REC_BYTES;
-static_assert(P_SLOT_BYTES % 1024 == 0 && P_OPER_BYTES % 1024 == 0, "128-byte swizzle needs 1024-byte aligned regions");
 constexpr int P_SLOTS = 4;
 constexpr int P_TAIL_PAD = 1024;  // second-operand rows are read up to 7 rows past a run's end
 constexpr int P_GROUPS = BLK_PIPE_GROUPS;        // consumer groups; unit u belongs to group u % P_GROUPS
 constexpr int P_GROUP_WARPS = P_CONSUMERS / P_GROUPS;
 constexpr int P_SCRATCH_BYTES = 128;  // target of staging stores that must not land
-constexpr int P_SMEM_BYTES = P_SLOTS * P_SLOT_BYTES + P_TAIL_PAD + 16 * P_SLOTS + 16 + 4 * P_SLOTS + P_SCRATCH_BYTES;
 static_assert(P_SLOTS % P_GROUPS == 0 && P_CONSUMERS % P_GROUPS == 0, "groups own whole slots");
 constexpr uint32_t P_SPIN_LIMIT = 1u << 22;
-static_assert(P_SMEM_BYTES <= 227 * 1024, "shared memory budget");
+// Slot layout: the operand regions (first, second and, for the attention variant, the values), then the records.
+template <bool ATTN>
+struct PL {
+    static constexpr int ROWS = ATTN ? BLK_PACK_ROWS_ATTN : BLK_PACK_ROWS;
+    static constexpr int NOPER = ATTN ? 3 : 2;
+    static constexpr int OPER_BYTES = ROWS * ROWB;
+    // the 16-deep steps of P V read up to 15 value rows past a run's end: a cleared guard keeps them finite
+    static constexpr int GUARD_BYTES = ATTN ? 16 * ROWB : 0;
+    static constexpr int REC_OFF = NOPER * OPER_BYTES + GUARD_BYTES;
+    static constexpr int SLOT_BYTES = REC_OFF + P_REC_BYTES;
+    static constexpr int SMEM_BYTES = P_SLOTS * SLOT_BYTES + P_TAIL_PAD + 16 * P_SLOTS + 16 + 4 * P_SLOTS + P_SCRATCH_BYTES;
+    static_assert(SLOT_BYTES % 1024 == 0 && OPER_BYTES % 1024 == 0, "128-byte swizzle needs 1024-byte aligned regions");
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+};
 
 __device__ __forceinline__ void pb_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
@@ -177,9 +186,14 @@ __device__ __forceinline__ void pk_mma0<BlkBf16Tag>(float (&d)[4], uint32_t a0, 
 // The arithmetic of one block with exactly NT column tiles: products, optional row softmax, and the staging
 // stores (rows g and g + 8 of the block at shared addresses s0a / s1a).  Columns 8 (NT - 1) + 2 t and + 1 of the
 // last tile exist when last0 / last1; stores that must not land go to `scratch`.
-template <typename Tag, int NT, bool SOFTMAX>
+// ATTN: the probabilities are not stored; they become the first operand of P V (the accumulator fragments of two
+// neighbouring score tiles are exactly the first-operand fragment of one 16-deep step), the values' fragments come
+// from shared memory through transposing ldmatrix loads (vb / vx address this lane's rows and swizzle), and the
+// 16 x 64 result is staged at s0a / s1a (rows g and g + 8) with its 16-byte chunks swizzled by the row.
+template <typename Tag, int NT, bool SOFTMAX, bool ATTN>
 __device__ __forceinline__ void pack_tiles(const uint32_t (&af)[PK / 16][4], uint32_t b0, uint32_t b1, float sl, bool last0,
-                                           bool last1, bool pairs, uint32_t s0a, uint32_t s1a, uint32_t scratch) {
+                                           bool last1, bool pairs, uint32_t s0a, uint32_t s1a, uint32_t scratch,
+                                           uint32_t vb, uint32_t vx, int g, int t) {
     float acc[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
@@ -218,6 +232,40 @@ __device__ __forceinline__ void pack_tiles(const uint32_t (&af)[PK / 16][4], uin
         r0 = __frcp_rn(blk_quad_sum(s0));
         r1 = __frcp_rn(blk_quad_sum(s1));
     }
+    if constexpr (ATTN) {
+        constexpr int KK = (NT + 1) / 2;  // 16-deep steps over the columns of the scores = rows of the values
+        float o[PK / 8][4];
+#pragma unroll
+        for (int kk = 0; kk < KK; ++kk) {
+            const uint32_t a0 = BlkCvt<Tag>::pack2(acc[2 * kk][0] * r0, acc[2 * kk][1] * r0);
+            const uint32_t a1 = BlkCvt<Tag>::pack2(acc[2 * kk][2] * r1, acc[2 * kk][3] * r1);
+            uint32_t a2 = 0u, a3 = 0u;  // an odd tile count leaves the upper half of the last step empty
+            if (2 * kk + 1 < NT) {
+                a2 = BlkCvt<Tag>::pack2(acc[2 * kk + 1][0] * r0, acc[2 * kk + 1][1] * r0);
+                a3 = BlkCvt<Tag>::pack2(acc[2 * kk + 1][2] * r1, acc[2 * kk + 1][3] * r1);
+            }
+#pragma unroll
+            for (int nn = 0; nn < PK / 16; ++nn) {
+                // value rows 16 kk .. 16 kk + 15, columns 16 nn .. 16 nn + 15, transposed into second-operand fragments
+                uint32_t m[4];
+                blk_ldmatrix_x4_trans(m, vb + kk * 16 * ROWB + (vx ^ (uint32_t)(nn << 5)));
+                if (kk == 0) {
+                    pk_mma0<Tag>(o[2 * nn], a0, a1, a2, a3, m[0], m[1]);
+                    pk_mma0<Tag>(o[2 * nn + 1], a0, a1, a2, a3, m[2], m[3]);
+                } else {
+                    pk_mma<Tag>(o[2 * nn], a0, a1, a2, a3, m[0], m[1]);
+                    pk_mma<Tag>(o[2 * nn + 1], a0, a1, a2, a3, m[2], m[3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < PK / 8; ++j) {
+            const uint32_t off = (uint32_t)(((j ^ g) << 4) + 4 * t);  // chunk j of a row goes to chunk position j ^ (row & 7)
+            sts_b32(s0a + off, BlkCvt<Tag>::pack2(o[j][0], o[j][1]));
+            sts_b32(s1a + off, BlkCvt<Tag>::pack2(o[j][2], o[j][3]));
+        }
+        return;
+    }
     // Rows that do not exist were given the address of a scratch area by the caller, so only the last tile's
     // columns need a per-store decision; it is made by choosing the address, which keeps the stores unpredicated.
     if (pairs) {  // every staged pair starts on a 4-byte boundary
@@ -248,9 +296,9 @@ __device__ __forceinline__ void pack_tiles(const uint32_t (&af)[PK / 16][4], uin
 // Rows past M and past N are read as whatever follows in shared memory: such rows of the result are never
 // stored and such columns are masked before the row reduction.  The result is staged over the block's own
 // first-operand rows (M * N * 2 <= M * 128 bytes) and copied to the output at element cbase.
-template <typename Tag, bool SOFTMAX, bool FLIP>
-__device__ __forceinline__ void pack_block(void* C, unsigned char* pA, uint32_t sA0, uint32_t sB0, int rowA, int rowB,
-                                           int64_t cbase, int M, int N, float sl, uint32_t scratch, int lane) {
+template <typename Tag, bool SOFTMAX, bool FLIP, bool ATTN>
+__device__ __forceinline__ void pack_block(void* C, unsigned char* pA, uint32_t sA0, uint32_t sB0, uint32_t sV0, int rowA,
+                                           int rowB, int64_t cbase, int M, int N, float sl, uint32_t scratch, int lane) {
     const int g = lane >> 2, t = lane & 3;
     const int nt = (N + 7) >> 3;
 
@@ -283,23 +331,39 @@ __device__ __forceinline__ void pack_block(void* C, unsigned char* pA, uint32_t 
         const uint32_t bx = (((uint32_t)lane >> 3) ^ (rb & 7u)) << 4;
         const uint32_t b0 = sB0 + rb * ROWB + bx, b1 = sB0 + rb * ROWB + (bx ^ 64u);
         const bool last0 = 8 * (nt - 1) + 2 * t < N, last1 = 8 * (nt - 1) + 2 * t + 1 < N;
-        // rows g and g + 8 of the staged block; a row past M is pointed at the scratch area instead
-        const uint32_t row0 = blk_smem_u32(pA) + (uint32_t)(so + (g * N + 2 * t) * 2);
-        const uint32_t s0a = g < M ? row0 : scratch, s1a = g + 8 < M ? row0 + 8 * N * 2 : scratch;
+        // rows g and g + 8 of the staged block; a row past M is pointed at the scratch area instead.  (Attention:
+        // the staged block is the 16 x 64 result, one 128-byte row per first-operand row.)
+        const uint32_t row0 = blk_smem_u32(pA) + (uint32_t)(ATTN ? g * ROWB : so + (g * N + 2 * t) * 2);
+        const uint32_t s0a = g < M ? row0 : scratch, s1a = g + 8 < M ? row0 + 8 * (ATTN ? ROWB : N * 2) : scratch;
         const bool pairs = ((N | (so >> 1)) & 1) == 0;
+        // values: lane l addresses row (l % 8) + 8 ((l / 8) % 2) of a 16-row step and column chunk l / 16 of a pair
+        const uint32_t rv = (uint32_t)rowB + (lane & 7);
+        const uint32_t vb = sV0 + (rv + ((lane >> 3) & 1) * 8) * ROWB, vx = (((uint32_t)lane >> 4) ^ (rv & 7u)) << 4;
         // one jump to the code for this tile count; only the tile arithmetic is specialised
         switch (nt) {
-            case 1: pack_tiles<Tag, 1, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            case 2: pack_tiles<Tag, 2, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            case 3: pack_tiles<Tag, 3, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            case 4: pack_tiles<Tag, 4, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            case 5: pack_tiles<Tag, 5, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            case 6: pack_tiles<Tag, 6, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            case 7: pack_tiles<Tag, 7, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
-            default: pack_tiles<Tag, 8, SOFTMAX>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch); break;
+            case 1: pack_tiles<Tag, 1, SOFTMAX, ATTN>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch, vb, vx, g, t); break;
+            case 2: pack_tiles<Tag, 2, SOFTMAX, ATTN>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch, vb, vx, g, t); break;
+            case 3: pack_tiles<Tag, 3, SOFTMAX, ATTN>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch, vb, vx, g, t); break;
+            case 4: pack_tiles<Tag, 4, SOFTMAX, ATTN>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch, vb, vx, g, t); break;
+            case 5: pack_tiles<Tag, 5, SOFTMAX, ATTN>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch, vb, vx, g, t); break;
+            case 6: pack_tiles<Tag, 6, SOFTMAX, ATTN>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch, vb, vx, g, t); break;
+            case 7: pack_tiles<Tag, 7, SOFTMAX, ATTN>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch, vb, vx, g, t); break;
+            default: pack_tiles<Tag, 8, SOFTMAX, ATTN>(af, b0, b1, sl, last0, last1, pairs, s0a, s1a, scratch, vb, vx, g, t); break;
         }
     }
     __syncwarp();
+    if constexpr (ATTN) {
+        // the staged 16 x 64 result -> global: M rows of 128 bytes, always 16-byte aligned; chunk c of row r sits at
+        // chunk position c ^ (r & 7)
+        unsigned char* dst = reinterpret_cast<unsigned char*>(C) + cbase * 2;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int v = lane + 32 * i, r = v >> 3, c = v & 7;
+            const uint4 q = *reinterpret_cast<const uint4*>(pA + r * ROWB + ((c ^ (r & 7)) << 4));
+            stg_v4_if(dst + r * ROWB + 16 * c, q, r < M);
+        }
+        return;
+    }
     // staged block -> global.  Lane j owns the 16-byte vector j of the block as aligned in global memory.  The
     // ragged first and last vector go out as single elements (lanes 0-7 and 8-15).
     {
@@ -334,12 +398,17 @@ __device__ __forceinline__ void pack_block(void* C, unsigned char* pA, uint32_t 
     }
 }
 
-template <typename Tag, bool SOFTMAX, bool FLIP>
+// The maps of one operand: boxes of 64, 32 and 16 rows.
+struct PackMaps {
+    CUtensorMap m64, m32, m16;
+};
+
+template <typename Tag, bool SOFTMAX, bool FLIP, bool ATTN>
 __global__ void __launch_bounds__(P_THREADS, 1)
-blk_scores_pipe_kernel(const BlkPackParams p, const __grid_constant__ CUtensorMap mA64,
-                       const __grid_constant__ CUtensorMap mA32, const __grid_constant__ CUtensorMap mA16,
-                       const __grid_constant__ CUtensorMap mB64, const __grid_constant__ CUtensorMap mB32,
-                       const __grid_constant__ CUtensorMap mB16) {
+blk_scores_pipe_kernel(const BlkPackParams p, const __grid_constant__ PackMaps mA, const __grid_constant__ PackMaps mB,
+                       const __grid_constant__ PackMaps mV) {
+    constexpr int P_OPER_BYTES = PL<ATTN>::OPER_BYTES, P_SLOT_BYTES = PL<ATTN>::SLOT_BYTES;
+    constexpr int P_REC_OFF = PL<ATTN>::REC_OFF;  // the block records follow the operand regions (and the guard)
     extern __shared__ __align__(1024) unsigned char pipe_smem[];  // the swizzled operand regions need this alignment
     if (blk_smem_u32(pipe_smem) & 1023u) {  // cannot happen with the alignment above; the swizzle relies on it
         if (threadIdx.x == 0) atomicCAS(p.status, 0, 13);
@@ -362,6 +431,16 @@ blk_scores_pipe_kernel(const BlkPackParams p, const __grid_constant__ CUtensorMa
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (ATTN) {
+        // value rows past a segment's end meet probabilities that are exactly zero, but zero times whatever an
+        // unwritten region of shared memory holds need not be zero: clear the value regions and their guards once
+        for (int s = 0; s < P_SLOTS; ++s) {
+            uint4* vreg = reinterpret_cast<uint4*>(pipe_smem + s * P_SLOT_BYTES + 2 * P_OPER_BYTES);
+            for (int i = threadIdx.x; i < (P_OPER_BYTES + PL<ATTN>::GUARD_BYTES) / 16; i += P_THREADS)
+                vreg[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // before the first tensor-map copy lands there
     }
     __syncthreads();
 
@@ -392,10 +471,14 @@ blk_scores_pipe_kernel(const BlkPackParams p, const __grid_constant__ CUtensorMa
                 *reinterpret_cast<volatile int*>(next_block + s) = 0;  // ordered before the consumers' claims by the barrier
                 // rows are fetched in whole boxes: up to 15 rows past the run's end come along (zeros past the strip)
                 const uint32_t bytesA = (uint32_t)((pk.rowsA + 15) & ~15) * ROWB, bytesB = (uint32_t)((pk.rowsB + 15) & ~15) * ROWB;
-                pb_expect_tx(full_bar(s), bytesA + bytesB + bytesR);
-                tma_run(dst, &mA64, &mA32, &mA16, full_bar(s), (int)(pk.offA / PK), pk.rowsA, (int)hd_now, p.head_firstA);
-                tma_run(dst + P_OPER_BYTES, &mB64, &mB32, &mB16, full_bar(s), (int)(pk.offB / PK), pk.rowsB, (int)hd_now, p.head_firstB);
-                bulk_g2s(dst + 2 * P_OPER_BYTES, p.blocks + pk.first_block, bytesR, full_bar(s));
+                pb_expect_tx(full_bar(s), bytesA + (ATTN ? 2 : 1) * bytesB + bytesR);
+                tma_run(dst, &mA.m64, &mA.m32, &mA.m16, full_bar(s), (int)(pk.offA / PK), pk.rowsA, (int)hd_now, p.head_firstA);
+                tma_run(dst + P_OPER_BYTES, &mB.m64, &mB.m32, &mB.m16, full_bar(s), (int)(pk.offB / PK), pk.rowsB, (int)hd_now,
+                        p.head_firstB);
+                if (ATTN)  // the values: one row per second-operand row
+                    tma_run(dst + 2 * P_OPER_BYTES, &mV.m64, &mV.m32, &mV.m16, full_bar(s), (int)(pk.offB / PK), pk.rowsB,
+                            (int)hd_now, p.head_firstV);
+                bulk_g2s(dst + P_REC_OFF, p.blocks + pk.first_block, bytesR, full_bar(s));
             }
         }
     } else {
@@ -412,7 +495,7 @@ blk_scores_pipe_kernel(const BlkPackParams p, const __grid_constant__ CUtensorMa
             if (!pb_wait(full_bar(s), (u / P_SLOTS) & 1u, abort_flag, p.status, 12)) break;
             unsigned char* slot = pipe_smem + s * P_SLOT_BYTES;
             const uint32_t sslot = smem0 + s * P_SLOT_BYTES;
-            const BlkPackBlock* recs = reinterpret_cast<const BlkPackBlock*>(slot + 2 * P_OPER_BYTES);
+            const BlkPackBlock* recs = reinterpret_cast<const BlkPackBlock*>(slot + P_REC_OFF);
             const int nb = recs[0].nblocks;
             // the group's warps claim the pack's blocks (widest first) one at a time: a warp that finishes early takes more
             for (;;) {
@@ -421,8 +504,9 @@ blk_scores_pipe_kernel(const BlkPackParams p, const __grid_constant__ CUtensorMa
                 b = __shfl_sync(0xffffffffu, b, 0);
                 if (b >= nb) break;
                 const BlkPackBlock r = recs[b];
-                pack_block<Tag, SOFTMAX, FLIP>(p.C, slot + r.rowA * ROWB, sslot, sslot + P_OPER_BYTES, r.rowA, r.rowB,
-                                               hbase + r.offC, r.M, r.N, sl, scratch, lane);
+                pack_block<Tag, SOFTMAX, FLIP, ATTN>(p.C, slot + r.rowA * ROWB, sslot, sslot + P_OPER_BYTES,
+                                                     sslot + 2 * P_OPER_BYTES, r.rowA, r.rowB, hbase + r.offC, r.M, r.N, sl,
+                                                     scratch, lane);
             }
             // this warp's reads and writes of the slot are done: order them before the next bulk copy into it
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -442,23 +526,34 @@ cudaError_t launch_pipe(const BlkPackParams& p_in, int sms, cudaStream_t st) {
     const int64_t total = (int64_t)p_in.num_packs * p_in.H;
     if (total == 0) return cudaSuccess;
     BlkPackParams p = p_in;
-    // both operands as (64, rows, heads) views with boxes of 64, 32 and 16 rows
-    CUtensorMap mA[3], mB[3];
+    const bool attn = p.V != nullptr;
+    // the operands as (64, rows, heads) views with boxes of 64, 32 and 16 rows
+    PackMaps mA, mB, mV;
     const int bf16 = std::is_same<Tag, BlkBf16Tag>::value ? 1 : 0;
-    const int box_rows[3] = {64, 32, 16};
-    for (int i = 0; i < 3; ++i)
-        if (!blk_make_row_map(&mA[i], p.A, bf16, PK, p.H, p.layA, PK, box_rows[i], &p.head_firstA) ||
-            !blk_make_row_map(&mB[i], p.B, bf16, PK, p.H, p.layB, PK, box_rows[i], &p.head_firstB))
-            return cudaErrorInvalidValue;
+    auto maps = [&](PackMaps& m, const void* base, const BlkOperandLayout& lay, int* head_first) {
+        return blk_make_row_map(&m.m64, base, bf16, PK, p.H, lay, PK, 64, head_first) &&
+               blk_make_row_map(&m.m32, base, bf16, PK, p.H, lay, PK, 32, head_first) &&
+               blk_make_row_map(&m.m16, base, bf16, PK, p.H, lay, PK, 16, head_first);
+    };
+    if (!maps(mA, p.A, p.layA, &p.head_firstA) || !maps(mB, p.B, p.layB, &p.head_firstB)) return cudaErrorInvalidValue;
+    if (attn) {
+        if (!maps(mV, p.V, p.layV, &p.head_firstV)) return cudaErrorInvalidValue;
+    } else {
+        mV = mB;  // unused
+    }
     const dim3 grid((unsigned)(total < sms ? total : sms)), block(P_THREADS);
-    auto go = [&](auto kern) -> cudaError_t {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+    auto go = [&](auto kern, int smem) -> cudaError_t {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
-        kern<<<grid, block, P_SMEM_BYTES, st>>>(p, mA[0], mA[1], mA[2], mB[0], mB[1], mB[2]);
+        kern<<<grid, block, smem, st>>>(p, mA, mB, mV);
         return cudaGetLastError();
     };
-    if (p.epi != BLK_EPI_SOFTMAX) return go(blk_scores_pipe_kernel<Tag, false, false>);
-    return p.scale < 0.f ? go(blk_scores_pipe_kernel<Tag, true, true>) : go(blk_scores_pipe_kernel<Tag, true, false>);
+    if (attn)
+        return p.scale < 0.f ? go(blk_scores_pipe_kernel<Tag, true, true, true>, PL<true>::SMEM_BYTES)
+                             : go(blk_scores_pipe_kernel<Tag, true, false, true>, PL<true>::SMEM_BYTES);
+    if (p.epi != BLK_EPI_SOFTMAX) return go(blk_scores_pipe_kernel<Tag, false, false, false>, PL<false>::SMEM_BYTES);
+    return p.scale < 0.f ? go(blk_scores_pipe_kernel<Tag, true, true, false>, PL<false>::SMEM_BYTES)
+                         : go(blk_scores_pipe_kernel<Tag, true, false, false>, PL<false>::SMEM_BYTES);
 }
 
 }  // namespace

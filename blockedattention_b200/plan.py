@@ -181,6 +181,44 @@ class GemmPlan(_Plan):
         return out
 
 
+class AttentionPlan(_Plan):
+    """Fused ``softmax(scale * Q_s K_s^T) V_s`` for segments of at most 64 query and 64 key rows, head dimension 64.
+    Raises ``RuntimeError`` (library code BLK_ERR_UNSUPPORTED) for any other batch."""
+
+    def __init__(self, MList, NList, H: int, dtype: torch.dtype, device=None):
+        super().__init__()
+        self.M, self.N = _host_i64(MList), _host_i64(NList)
+        if len(self.M) != len(self.N):
+            raise RuntimeError("MList and NList must have the same length")
+        self.S, self.H, self.dtype = len(self.M), int(H), dtype
+        self.device = torch.device(device) if device is not None else None
+        dev = -1 if self.device is None else (self.device.index if self.device.index is not None
+                                               else torch.cuda.current_device())
+        L.check(L.lib.blk_attention_plan_create(C.byref(self._h), L.i64(self.M), L.i64(self.N), self.S, self.H,
+                                                dtype_code(dtype), dev))
+        self.Dq, self.Dkv = int(self.M.sum()) * 64, int(self.N.sum()) * 64
+
+    def run(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
+            scale: float = 1.0) -> torch.Tensor:
+        if self.device is None:
+            raise RuntimeError("this plan was built without a device")
+        for name, t, D in (("q", q, self.Dq), ("k", k, self.Dkv), ("v", v, self.Dkv)):
+            if not t.is_cuda or not t.is_contiguous() or t.dtype != self.dtype or t.numel() != self.H * D:
+                raise RuntimeError(f"{name} must be a contiguous CUDA tensor of the plan's dtype with H*{D} elements")
+        if out is None:
+            out = torch.empty((self.H, self.Dq), dtype=self.dtype, device=q.device)
+        elif not out.is_cuda or not out.is_contiguous() or out.dtype != self.dtype or out.numel() != self.H * self.Dq:
+            raise RuntimeError("out must be a contiguous CUDA tensor of the plan's dtype with H*sum(M)*64 elements")
+        q, k, v = (t if t.data_ptr() % 16 == 0 else t.clone() for t in (q, k, v))
+        if out.data_ptr() % 16:
+            raise RuntimeError("out must be 16-byte aligned")
+        with torch.cuda.device(q.device):
+            L.check(L.lib.blk_attention_run(self._h, C.c_void_p(q.data_ptr()), C.c_void_p(k.data_ptr()),
+                                            C.c_void_p(v.data_ptr()), C.c_void_p(out.data_ptr()), C.c_float(scale),
+                                            C.c_void_p(_stream_ptr(q.device))))
+        return out
+
+
 class SoftmaxPlan(_Plan):
     """Schedule for the row softmax of S packed (rows_s, cols_s) blocks per head."""
 

@@ -59,6 +59,8 @@ class Workload:
     def bytes(self) -> float:
         ei = torch.empty((), dtype=self.dtype).element_size()
         eo = torch.empty((), dtype=self.out_dtype).element_size()
+        if self.extra.get("fused_attention"):  # q, k, v read, O written; P never exists
+            return self.H * ei * (float(((self.M + self.N) * self.K).sum()) + float((self.N + self.M).sum()) * self.d_v)
         b = self.H * (float(((self.M + self.N) * self.K).sum()) * ei + float((self.M * self.N).sum()) * eo)
         if self.d_v:  # P read, V read, O written
             b += self.H * (float((self.M * self.N).sum()) * eo + float((self.N + self.M).sum()) * self.d_v * ei)
@@ -105,6 +107,13 @@ def workload(name: str, seed: int = 0, segments: Optional[int] = None) -> Worklo
         n = _i64(np.clip(np.rint(rs.normal(25.0, 10.0, size=S)), 2, 128))
         return Workload(name, n, n.copy(), np.full(S, 64, np.int64), 8, torch.float16, torch.float16, 1 / 8.0, True,
                         "normal", note="4096 graphs, n~clip(round(N(25,10)),2,128), 8 heads, d=64, fp16")
+    if name == "molecular_attention":
+        # the molecular batch with graphs capped at 64 nodes, values added: softmax(QK^T) V in one kernel
+        S = segments or 4096
+        n = _i64(np.clip(np.rint(rs.normal(25.0, 10.0, size=S)), 2, 64))
+        return Workload(name, n, n.copy(), np.full(S, 64, np.int64), 8, torch.float16, torch.float16, 1 / 8.0, True,
+                        "normal", d_v=64, note="4096 graphs, n~clip(round(N(25,10)),2,64), 8 heads, d=64, fp16, "
+                        "fused softmax(QK^T)V without materialising P", extra={"fused_attention": True})
     if name == "general_gemm":
         S = segments or 2048
         M = _i64(rs.randint(1, 257, size=S)); N = _i64(rs.randint(1, 257, size=S))
@@ -131,4 +140,4 @@ def workload(name: str, seed: int = 0, segments: Optional[int] = None) -> Worklo
     raise ValueError(f"unknown workload {name!r}")
 
 
-WORKLOADS = ("cpu_plumbing", "molecular", "general_gemm", "long_tail", "full_forward", "large_k")
+WORKLOADS = ("cpu_plumbing", "molecular", "molecular_attention", "general_gemm", "long_tail", "full_forward", "large_k")

@@ -135,6 +135,22 @@ BLK_API int blk_gemm_run_strided(const blk_plan_t* plan, const void* mat1, int64
                          const void* mat2, int64_t row_stride2, int64_t head_stride2, void* out, float scale,
                          void* cuda_stream);
 
+/* ---- fused attention for small segments ------------------------------------- */
+
+/* out_s = softmax_rows(scale * Q_s K_s^T) V_s for segments of at most 64 query
+ * rows and 64 key rows, head dimension 64, fp16 or bf16, in one kernel: the
+ * scores and probabilities stay in registers.  q (H, sum M_s * 64), k and v
+ * (H, sum N_s * 64) and out (H, sum M_s * 64) are packed head-major strips like
+ * the operands of blk_gemm_run.  Equals, up to the rounding of the
+ * probabilities that the two-call form stores in between,
+ *   P = blk_gemm_run(BLK_EPI_SOFTMAX)(q, k);  out = blk_gemm_run(P, v; lists (M, 64, N), transpose2).
+ * Any other batch gets BLK_ERR_UNSUPPORTED from the plan call: compose the two
+ * operators for it.  No counterpart upstream (upstream materialises P). */
+BLK_API int blk_attention_plan_create(blk_plan_t** plan, const int64_t* M, const int64_t* N, int64_t S, int64_t H,
+                              int dtype, int device);
+BLK_API int blk_attention_run(const blk_plan_t* plan, const void* q, const void* k, const void* v, void* out,
+                      float scale, void* cuda_stream);
+
 /* ---- varlen row softmax ---------------------------------------------------- */
 
 /* Replaces the per-row host table at upstream csrc/cuda/spBlkSoftmax.cu:358-373
