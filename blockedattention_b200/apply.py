@@ -262,6 +262,22 @@ def blockAttention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, MList, NLi
     return blockGEMM(p, v, None, None, None, M, dl, N, False, True)
 
 
+def blockAttentionTokenMajor(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, nList, scale: float = 1.0) -> torch.Tensor:
+    """Self-attention over a batch of graphs in the layout attention layers keep their activations in:
+    ``q, k, v -> (sum n_s, H, 64)`` (the nodes of all graphs in batch order), result of the same shape:
+    ``out[rows of s] = softmax(scale * Q_s K_s^T) V_s`` per graph and head.  One kernel, no permuted copies, no
+    probabilities in memory; graphs of at most 64 nodes, 16-bit inputs.  Forward only."""
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _check_operand(name, t)
+    if q.dim() != 3 or q.shape != k.shape or q.shape != v.shape or q.shape[2] != 64:
+        raise RuntimeError("q, k and v must all have shape (sum n, H, 64)")
+    n = _host_i64(nList)
+    H = int(q.shape[1])
+    key = ("attn", n.tobytes(), n.tobytes(), H, q.dtype, str(q.device))
+    plan = _cached(key, lambda: AttentionPlan(n, n, H, q.dtype, device=q.device))
+    return plan.run_token_major(q, k, v, scale=scale)
+
+
 def blockAttnScoresTokenMajor(q: torch.Tensor, k: torch.Tensor, nList, scale: float = 1.0,
                               out_dtype: Optional[torch.dtype] = None, softmax: bool = True) -> torch.Tensor:
     """``blockAttnScores`` for the layout attention inputs usually arrive in: ``q, k -> (sum n_s, H, d)``, the tokens

@@ -366,8 +366,26 @@ extern "C" int blk_attention_plan_create(blk_plan_t** plan, const int64_t* M, co
     return BLK_OK;
 }
 
+// Shared body of blk_attention_run (strides 0: packed head-major strips) and blk_attention_run_strided.
+static int attention_run_impl(const blk_plan* p, const void* q, const void* k, const void* v, void* out,
+                              int64_t row_stride, int64_t head_stride, float scale, void* cuda_stream);
+
 extern "C" int blk_attention_run(const blk_plan_t* p, const void* q, const void* k, const void* v, void* out,
                                  float scale, void* cuda_stream) {
+    return attention_run_impl(p, q, k, v, out, 0, 0, scale, cuda_stream);
+}
+
+extern "C" int blk_attention_run_strided(const blk_plan_t* p, const void* q, const void* k, const void* v, void* out,
+                                         int64_t row_stride, int64_t head_stride, float scale, void* cuda_stream) {
+    if (row_stride < 64 || head_stride <= 0 || row_stride % 8 || head_stride % 8) {
+        blk_set_error("blk_attention_run_strided: strides must be multiples of 8 elements, the row stride at least 64");
+        return BLK_ERR_INVALID;
+    }
+    return attention_run_impl(p, q, k, v, out, row_stride, head_stride, scale, cuda_stream);
+}
+
+static int attention_run_impl(const blk_plan* p, const void* q, const void* k, const void* v, void* out,
+                              int64_t row_stride, int64_t head_stride, float scale, void* cuda_stream) {
     if (!p || p->kind != 0 || !p->attn) {
         blk_set_error("blk_attention_run: not an attention plan");
         return BLK_ERR_INVALID;
@@ -399,9 +417,12 @@ extern "C" int blk_attention_run(const blk_plan_t* p, const void* q, const void*
     pp.epi = BLK_EPI_SOFTMAX;
     pp.scale = scale;
     pp.status = p->d_status;
-    pp.layA = BlkOperandLayout{p->Dm1 / 64, 64, p->Dm1};
-    pp.layB = BlkOperandLayout{p->Dm2 / 64, 64, p->Dm2};
+    const bool packed = row_stride == 0;
+    pp.layA = BlkOperandLayout{p->Dm1 / 64, packed ? 64 : row_stride, packed ? p->Dm1 : head_stride};
+    pp.layB = BlkOperandLayout{p->Dm2 / 64, packed ? 64 : row_stride, packed ? p->Dm2 : head_stride};
     pp.layV = pp.layB;
+    pp.out_row_stride = packed ? 64 : row_stride;
+    pp.out_head_stride = packed ? p->Dm1 : head_stride;
     cudaError_t e = blk_launch_scores_pipe(pp, p->dtype_in, p->num_sms, reinterpret_cast<cudaStream_t>(cuda_stream));
     if (e != cudaSuccess) return cuda_fail("attention launch", e);
     return BLK_OK;

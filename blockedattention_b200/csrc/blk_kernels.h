@@ -87,6 +87,7 @@ struct BlkPackParams {
     const uint16_t* V;
     BlkOperandLayout layV;
     int head_firstV;
+    int64_t out_row_stride, out_head_stride;  // elements; result row r of head h at C[h * head_stride + r * row_stride]
 };
 
 struct BlkSmxParams {

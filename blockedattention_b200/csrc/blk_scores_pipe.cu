@@ -298,7 +298,8 @@ __device__ __forceinline__ void pack_tiles(const uint32_t (&af)[PK / 16][4], uin
 // first-operand rows (M * N * 2 <= M * 128 bytes) and copied to the output at element cbase.
 template <typename Tag, bool SOFTMAX, bool FLIP, bool ATTN>
 __device__ __forceinline__ void pack_block(void* C, unsigned char* pA, uint32_t sA0, uint32_t sB0, uint32_t sV0, int rowA,
-                                           int rowB, int64_t cbase, int M, int N, float sl, uint32_t scratch, int lane) {
+                                           int rowB, int64_t cbase, int64_t out_pitch, int M, int N, float sl,
+                                           uint32_t scratch, int lane) {
     const int g = lane >> 2, t = lane & 3;
     const int nt = (N + 7) >> 3;
 
@@ -353,14 +354,14 @@ __device__ __forceinline__ void pack_block(void* C, unsigned char* pA, uint32_t 
     }
     __syncwarp();
     if constexpr (ATTN) {
-        // the staged 16 x 64 result -> global: M rows of 128 bytes, always 16-byte aligned; chunk c of row r sits at
+        // the staged 16 x 64 result -> global: M rows of 128 bytes, out_pitch bytes apart, always 16-byte aligned; chunk c of row r sits at
         // chunk position c ^ (r & 7)
-        unsigned char* dst = reinterpret_cast<unsigned char*>(C) + cbase * 2;
+        unsigned char* dst = reinterpret_cast<unsigned char*>(C) + cbase * 2;  // row r of the block at dst + r * out_pitch
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int v = lane + 32 * i, r = v >> 3, c = v & 7;
             const uint4 q = *reinterpret_cast<const uint4*>(pA + r * ROWB + ((c ^ (r & 7)) << 4));
-            stg_v4_if(dst + r * ROWB + 16 * c, q, r < M);
+            stg_v4_if(dst + r * out_pitch + 16 * c, q, r < M);
         }
         return;
     }
@@ -489,7 +490,9 @@ blk_scores_pipe_kernel(const BlkPackParams p, const __grid_constant__ PackMaps m
         uint32_t hd = w % H;
         for (uint32_t u = group; w < total; w += step, u += P_GROUPS) {
             const uint32_t s = u % P_SLOTS;
-            const int64_t hbase = (int64_t)hd * p.Dout;
+            // scores: head strip + element offset; attention: result rows with their own row and head strides
+            const int64_t hbase = ATTN ? (int64_t)hd * p.out_head_stride : (int64_t)hd * p.Dout;
+            const int64_t out_pitch = ATTN ? p.out_row_stride * 2 : 0;
             hd += dr;
             if (hd >= H) hd -= H;
             if (!pb_wait(full_bar(s), (u / P_SLOTS) & 1u, abort_flag, p.status, 12)) break;
@@ -505,8 +508,9 @@ blk_scores_pipe_kernel(const BlkPackParams p, const __grid_constant__ PackMaps m
                 if (b >= nb) break;
                 const BlkPackBlock r = recs[b];
                 pack_block<Tag, SOFTMAX, FLIP, ATTN>(p.C, slot + r.rowA * ROWB, sslot, sslot + P_OPER_BYTES,
-                                                     sslot + 2 * P_OPER_BYTES, r.rowA, r.rowB, hbase + r.offC, r.M, r.N, sl,
-                                                     scratch, lane);
+                                                     sslot + 2 * P_OPER_BYTES, r.rowA, r.rowB,
+                                                     ATTN ? hbase + (r.offC / PK) * p.out_row_stride : hbase + r.offC,
+                                                     out_pitch, r.M, r.N, sl, scratch, lane);
             }
             // this warp's reads and writes of the slot are done: order them before the next bulk copy into it
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");

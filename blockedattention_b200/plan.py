@@ -219,6 +219,30 @@ class AttentionPlan(_Plan):
         return out
 
 
+    def run_token_major(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
+                        scale: float = 1.0) -> torch.Tensor:
+        """Same for token-major tensors ``q, out -> (sum m_s, H, 64)``, ``k, v -> (sum n_s, H, 64)``, read and written
+        in place through strided tensor maps (needs ``sum m_s == sum n_s`` only in so far as all four share strides)."""
+        if self.device is None:
+            raise RuntimeError("this plan was built without a device")
+        rq, rkv = int(self.M.sum()), int(self.N.sum())
+        for name, t, rows in (("q", q, rq), ("k", k, rkv), ("v", v, rkv)):
+            if (not t.is_cuda or not t.is_contiguous() or t.dtype != self.dtype or tuple(t.shape) != (rows, self.H, 64)
+                    or t.data_ptr() % 16):
+                raise RuntimeError(f"{name} must be a contiguous, 16-byte aligned CUDA tensor of shape ({rows}, {self.H}, 64)")
+        if out is None:
+            out = torch.empty((rq, self.H, 64), dtype=self.dtype, device=q.device)
+        elif (not out.is_cuda or not out.is_contiguous() or out.dtype != self.dtype or tuple(out.shape) != (rq, self.H, 64)
+              or out.data_ptr() % 16):
+            raise RuntimeError(f"out must be a contiguous, 16-byte aligned CUDA tensor of shape ({rq}, {self.H}, 64)")
+        with torch.cuda.device(q.device):
+            L.check(L.lib.blk_attention_run_strided(self._h, C.c_void_p(q.data_ptr()), C.c_void_p(k.data_ptr()),
+                                                    C.c_void_p(v.data_ptr()), C.c_void_p(out.data_ptr()),
+                                                    self.H * 64, 64, C.c_float(scale),
+                                                    C.c_void_p(_stream_ptr(q.device))))
+        return out
+
+
 class SoftmaxPlan(_Plan):
     """Schedule for the row softmax of S packed (rows_s, cols_s) blocks per head."""
 

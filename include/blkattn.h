@@ -150,6 +150,14 @@ BLK_API int blk_attention_plan_create(blk_plan_t** plan, const int64_t* M, const
                               int dtype, int device);
 BLK_API int blk_attention_run(const blk_plan_t* plan, const void* q, const void* k, const void* v, void* out,
                       float scale, void* cuda_stream);
+/* The same for q, k, v and out that are not packed strips: row r (counted over
+ * all segments in batch order) of head h of each of the four tensors starts at
+ * element r * row_stride + h * head_stride; strides in elements, multiples of 8.
+ * Token-major [rows, H, 64] tensors -- the layout attention layers hold their
+ * activations in -- are row_stride = H * 64, head_stride = 64: no permuted copy
+ * on the way in or out. */
+BLK_API int blk_attention_run_strided(const blk_plan_t* plan, const void* q, const void* k, const void* v, void* out,
+                              int64_t row_stride, int64_t head_stride, float scale, void* cuda_stream);
 
 /* ---- varlen row softmax ---------------------------------------------------- */
 

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from helpers import O, packed_inputs
-from blockedattention_b200 import blockAttention, blockAttnScores, blockGEMM
+from blockedattention_b200 import blockAttention, blockAttentionTokenMajor, blockAttnScores, blockGEMM
 from blockedattention_b200.plan import AttentionPlan
 
 pytestmark = pytest.mark.gpu
@@ -78,3 +78,21 @@ def test_attention_falls_back_to_the_composition(cuda_device):
         AttentionPlan(n, n, H, BF16, device=dev)      # the fused plan itself refuses the batch
     with pytest.raises(RuntimeError):
         blockAttention(q, k.to(dev), v.to(dev), n, n)  # CPU tensor
+
+
+@pytest.mark.parametrize("dtype", [F16, BF16])
+def test_token_major_attention_matches_packed(cuda_device, dtype):
+    # (sum n, H, 64) tensors in and out, read and written in place: same bits as permuting into strips and back
+    dev = cuda_device
+    rs = np.random.RandomState(8)
+    n = rs.randint(1, 65, size=300)
+    H, T = 5, int(n.sum())
+    g = torch.Generator().manual_seed(9)
+    q, k, v = (torch.randn((T, H, 64), generator=g).to(dtype).to(dev) for _ in range(3))
+    got = blockAttentionTokenMajor(q, k, v, n, scale=0.125)
+    assert got.shape == (T, H, 64)
+    strips = [t.permute(1, 0, 2).reshape(H, T * 64).contiguous() for t in (q, k, v)]
+    want = blockAttention(*strips, n, n, scale=0.125).reshape(H, T, 64).permute(1, 0, 2)
+    assert torch.equal(got, want)
+    with pytest.raises(RuntimeError):
+        blockAttentionTokenMajor(q[:, :, :32], k[:, :, :32], v[:, :, :32], n)
