@@ -226,7 +226,7 @@ def main():
 
     fused_attn = bool(w.extra.get("fused_attention"))
     if fused_attn:
-        plan = AttentionPlan(w.M, w.N, w.H, w.dtype, device=dev)
+        plan = AttentionPlan(w.M, w.N, w.H, w.dtype, device=dev, d=int(w.K[0]) if w.S else 64)
     else:
         plan = GemmPlan(w.M, w.N, w.K, w.H, w.dtype, w.out_dtype, False, False, w.softmax, device=dev)
     plan_pv = None
@@ -291,6 +291,8 @@ def main():
     kernel = max(((small_kernel, s["small_items"]), ("blk_gemm_tile_kernel", s["tile_items"]),
                   ("blk_gemm_umma_kernel", s["umma_items"]), ("blk_gemm_simt_kernel", s["simt_items"])),
                  key=lambda kv: kv[1])[0]
+    if fused_attn and not s["packs"]:
+        kernel = "blk_attn_umma_kernel"
     t_hbm = w.bytes() / (peaks["hbm_gbs"] * 1e9)
     t_tc = w.flops() / (peaks["bf16_tflops"] * 1e12)
     if t_tc > t_hbm:

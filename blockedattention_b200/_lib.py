@@ -39,6 +39,8 @@ SIGNATURES = {
     "blk_gemm_run": (C.c_int, [_vp, _vp, _vp, _vp, C.c_float, _vp]),
     "blk_gemm_run_strided": (C.c_int, [_vp, _vp, C.c_int64, C.c_int64, _vp, C.c_int64, C.c_int64, _vp, C.c_float, _vp]),
     "blk_attention_plan_create": (C.c_int, [C.POINTER(_vp), _i64p, _i64p, C.c_int64, C.c_int64, C.c_int, C.c_int]),
+    "blk_attention_plan_create_dim": (C.c_int, [C.POINTER(_vp), _i64p, _i64p, C.c_int64, C.c_int64, C.c_int64, C.c_int,
+                                                C.c_int]),
     "blk_attention_run": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_float, _vp]),
     "blk_attention_run_strided": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int64, C.c_int64, C.c_float, _vp]),
     "blk_softmax_plan_create": (C.c_int, [C.POINTER(_vp), _i64p, _i64p, _i64p, C.c_int64, C.c_int64, C.c_int,

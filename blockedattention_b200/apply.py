@@ -231,8 +231,9 @@ def blockAttnScores(q: torch.Tensor, k: torch.Tensor, MList, NList, KList, scale
 def blockAttention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, MList, NList, scale: float = 1.0,
                    d: Optional[int] = None) -> torch.Tensor:
     """``softmax_rows(scale * Q_s K_s^T) V_s`` per segment: ``q -> (H, sum m_s*d)``, ``k, v -> (H, sum n_s*d)``, result
-    ``(H, sum m_s*d)``, all packed head-major.  Batches of segments with at most 64 rows and columns, ``d = 64`` and
-    16-bit inputs run as one kernel that never stores the probabilities; any other batch is the composition
+    ``(H, sum m_s*d)``, all packed head-major.  With 16-bit inputs and ``d`` 64 or 128 the batch runs as one kernel
+    that never stores the probabilities (the pack kernel when every segment has at most 64 rows and columns and
+    ``d = 64``, the tcgen05 attention kernel otherwise); any other batch is the composition
     ``blockGEMM(blockAttnScores(q, k), v, transpose2=True)`` of the two operators.  Forward only."""
     for name, t in (("q", q), ("k", k), ("v", v)):
         _check_operand(name, t)
@@ -247,12 +248,12 @@ def blockAttention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, MList, NLi
     if q.numel() % (rows_q * d) or k.numel() != (q.numel() // (rows_q * d)) * rows_kv * d or v.numel() != k.numel():
         raise RuntimeError("q / k / v do not match the packed extents of the lists")
     H = q.numel() // (rows_q * d)
-    fused = (d == 64 and q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
-             and int(M.max()) <= 64 and int(N.max()) <= 64 and int(N[M > 0].min() if (M > 0).any() else 1) >= 1)
+    fused = (d in (64, 128) and q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
+             and int(N[M > 0].min() if (M > 0).any() else 1) >= 1)
     if fused:
-        key = ("attn", M.tobytes(), N.tobytes(), H, q.dtype, str(q.device))
+        key = ("attn", M.tobytes(), N.tobytes(), H, d, q.dtype, str(q.device))
         try:
-            plan = _cached(key, lambda: AttentionPlan(M, N, H, q.dtype, device=q.device))
+            plan = _cached(key, lambda: AttentionPlan(M, N, H, q.dtype, device=q.device, d=d))
             return plan.run(q, k, v, scale=scale)
         except L.BlkError as e:
             if e.code != L.BLK_ERR_UNSUPPORTED:
@@ -264,17 +265,17 @@ def blockAttention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, MList, NLi
 
 def blockAttentionTokenMajor(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, nList, scale: float = 1.0) -> torch.Tensor:
     """Self-attention over a batch of graphs in the layout attention layers keep their activations in:
-    ``q, k, v -> (sum n_s, H, 64)`` (the nodes of all graphs in batch order), result of the same shape:
-    ``out[rows of s] = softmax(scale * Q_s K_s^T) V_s`` per graph and head.  One kernel, no permuted copies, no
-    probabilities in memory; graphs of at most 64 nodes, 16-bit inputs.  Forward only."""
+    ``q, k, v -> (sum n_s, H, d)`` (the nodes of all graphs in batch order), ``d`` 64 or 128, result of the same
+    shape: ``out[rows of s] = softmax(scale * Q_s K_s^T) V_s`` per graph and head.  One kernel, no permuted copies,
+    no probabilities in memory; graphs of any size, 16-bit inputs.  Forward only."""
     for name, t in (("q", q), ("k", k), ("v", v)):
         _check_operand(name, t)
-    if q.dim() != 3 or q.shape != k.shape or q.shape != v.shape or q.shape[2] != 64:
-        raise RuntimeError("q, k and v must all have shape (sum n, H, 64)")
+    if q.dim() != 3 or q.shape != k.shape or q.shape != v.shape or q.shape[2] not in (64, 128):
+        raise RuntimeError("q, k and v must all have shape (sum n, H, d), d 64 or 128")
     n = _host_i64(nList)
-    H = int(q.shape[1])
-    key = ("attn", n.tobytes(), n.tobytes(), H, q.dtype, str(q.device))
-    plan = _cached(key, lambda: AttentionPlan(n, n, H, q.dtype, device=q.device))
+    H, d = int(q.shape[1]), int(q.shape[2])
+    key = ("attn", n.tobytes(), n.tobytes(), H, d, q.dtype, str(q.device))
+    plan = _cached(key, lambda: AttentionPlan(n, n, H, q.dtype, device=q.device, d=d))
     return plan.run_token_major(q, k, v, scale=scale)
 
 

@@ -3,6 +3,7 @@
 // schedule at plan creation, kernel launches on the caller's stream.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstring>
 #include <new>
 #include <string>
@@ -61,6 +62,7 @@ int upload_plan(blk_plan* p) {
             p->num_sms = sms;
     }
     if ((rc = upload(p->umma_items, &p->d_umma_items, "upload umma items")) != BLK_OK) return rc;
+    if ((rc = upload(p->flash_items, &p->d_flash_items, "upload attention items")) != BLK_OK) return rc;
     if ((rc = upload(p->packs, &p->d_packs, "upload packs")) != BLK_OK) return rc;
     if ((rc = upload(p->pack_blocks, &p->d_pack_blocks, "upload pack blocks")) != BLK_OK) return rc;
     if ((rc = upload(p->smx_chunks, &p->d_smx_chunks, "upload softmax chunks")) != BLK_OK) return rc;
@@ -215,6 +217,7 @@ extern "C" void blk_plan_destroy(blk_plan_t* p) {
         cudaFree(p->d_simt_items);
         for (int b = 0; b < BLK_SMALL_BUCKETS; ++b) cudaFree(p->d_small_items[b]);
         cudaFree(p->d_umma_items);
+        cudaFree(p->d_flash_items);
         cudaFree(p->d_packs);
         cudaFree(p->d_pack_blocks);
         cudaFree(p->d_smx_chunks);
@@ -248,6 +251,7 @@ extern "C" int blk_plan_offsets(const blk_plan_t* p, int64_t* a1, int64_t* a2, i
 }
 
 static int launches_per_run(const blk_plan* p) {
+    if (p->attn == 2) return p->flash_items.empty() ? 0 : 1;
     int n = (!p->tile_items.empty()) + (!p->simt_items.empty()) + (!p->umma_items.empty()) + (!p->smx_chunks.empty());
     if (p->small_pipe) return n + 1;
     for (const auto& v : p->small_items) n += !v.empty();
@@ -262,7 +266,7 @@ extern "C" int blk_plan_summary(const blk_plan_t* p, int64_t counts[8]) {
     counts[0] = p->S;
     counts[1] = (int64_t)small_count(p);
     counts[2] = (int64_t)p->tile_items.size();
-    counts[3] = (int64_t)p->umma_items.size();
+    counts[3] = (int64_t)(p->attn == 2 ? p->flash_items.size() : p->umma_items.size());
     counts[4] = (int64_t)p->smx_chunks.size();
     counts[5] = p->H > 0 ? launches_per_run(p) : 0;
     counts[6] = (int64_t)p->simt_items.size();
@@ -299,8 +303,28 @@ extern "C" int blk_plan_check(const blk_plan_t* p, void* cuda_stream) {
     return BLK_OK;
 }
 
-extern "C" int blk_attention_plan_create(blk_plan_t** plan, const int64_t* M, const int64_t* N, int64_t S, int64_t H,
-                                         int dtype, int device) {
+// Schedule of the tcgen05 attention kernel: one item per 128-row block of the queries of a segment, longest
+// key/value sweeps first (the persistent CTAs take the items round-robin in this order).
+static int build_flash_items(blk_plan* p) {
+    const int64_t d = p->head_dim;
+    if (p->a1[p->S] / d >= (int64_t)1 << 31 || p->a2[p->S] / d >= (int64_t)1 << 31) {
+        blk_set_error("attention plan: more than 2^31 rows");
+        return BLK_ERR_UNSUPPORTED;
+    }
+    for (int64_t s = 0; s < p->S; ++s) {
+        const int64_t M = p->M[s], N = p->N[s];
+        if (M == 0) continue;
+        for (int64_t tm = 0; tm * BLK_FLASH_BM < M; ++tm)
+            p->flash_items.push_back(BlkFlashItem{(int32_t)(p->a1[s] / d + tm * BLK_FLASH_BM), (int32_t)(p->a2[s] / d),
+                                                  (int32_t)(M - tm * BLK_FLASH_BM), (int32_t)N});
+    }
+    std::stable_sort(p->flash_items.begin(), p->flash_items.end(),
+                     [](const BlkFlashItem& a, const BlkFlashItem& b) { return a.N > b.N; });
+    return BLK_OK;
+}
+
+static int attention_plan_impl(blk_plan_t** plan, const int64_t* M, const int64_t* N, int64_t S, int64_t H,
+                               int64_t head_dim, bool any_length, int dtype, int device) {
     if (!plan) {
         blk_set_error("blk_attention_plan_create: plan is null");
         return BLK_ERR_INVALID;
@@ -314,16 +338,32 @@ extern "C" int blk_attention_plan_create(blk_plan_t** plan, const int64_t* M, co
         blk_set_error("blk_attention_plan_create: fp16 or bf16 only");
         return BLK_ERR_UNSUPPORTED;
     }
-    for (int64_t s = 0; s < S; ++s)
-        if (M[s] < 0 || N[s] < 0 || M[s] > BLK_SMALL_MAXM || N[s] > BLK_SMALL_MAXN || (M[s] > 0 && N[s] == 0)) {
-            blk_set_error("blk_attention_plan_create: the fused kernel takes segments of 0..64 queries and 1..64 keys "
-                          "(segment " + std::to_string(s) + "); compose the two operators for other batches");
+    if (head_dim != 64 && head_dim != 128) {
+        blk_set_error("blk_attention_plan_create: head dimension 64 or 128 only");
+        return BLK_ERR_UNSUPPORTED;
+    }
+    bool small = head_dim == 64;
+    for (int64_t s = 0; s < S; ++s) {
+        if (M[s] < 0 || N[s] < 0) {
+            blk_set_error("blk_attention_plan_create: negative extent in segment " + std::to_string(s));
+            return BLK_ERR_INVALID;
+        }
+        if (M[s] > 0 && N[s] == 0) {
+            blk_set_error("blk_attention_plan_create: segment " + std::to_string(s) + " has queries but no keys");
             return BLK_ERR_UNSUPPORTED;
         }
+        if (M[s] > BLK_SMALL_MAXM || N[s] > BLK_SMALL_MAXN) small = false;
+    }
+    if (!small && !any_length) {
+        blk_set_error("blk_attention_plan_create: the small-segment kernel takes segments of 0..64 queries and 1..64 "
+                      "keys; blk_attention_plan_create_dim takes any batch");
+        return BLK_ERR_UNSUPPORTED;
+    }
     blk_plan* p = new (std::nothrow) blk_plan();
     if (!p) return BLK_ERR_NOMEM;
     p->kind = 0;
     p->attn = 1;
+    p->head_dim = (int)head_dim;
     p->S = S;
     p->H = H;
     p->dtype_in = p->dtype_out = dtype;
@@ -332,31 +372,53 @@ extern "C" int blk_attention_plan_create(blk_plan_t** plan, const int64_t* M, co
     p->device = device;
     p->M.assign(M, M + S);
     p->N.assign(N, N + S);
-    p->K.assign((size_t)S, 64);
+    p->K.assign((size_t)S, head_dim);
     p->a1.assign((size_t)S + 1, 0);
     p->a2.assign((size_t)S + 1, 0);
     for (int64_t s = 0; s < S; ++s) {
-        p->a1[s + 1] = p->a1[s] + M[s] * 64;
-        p->a2[s + 1] = p->a2[s] + N[s] * 64;
+        p->a1[s + 1] = p->a1[s] + M[s] * head_dim;
+        p->a2[s + 1] = p->a2[s] + N[s] * head_dim;
     }
-    p->ao = p->a1;  // the result has one row of 64 per query row, laid out like the queries
-    int rc = blk_build_gemm_schedule(p);
+    p->ao = p->a1;  // the result has one row of head_dim per query row, laid out like the queries
     size_t nonempty = 0;
     for (int64_t s = 0; s < S; ++s) nonempty += M[s] > 0 && N[s] > 0;
-    if (rc == BLK_OK && nonempty > 0 &&
-        (!p->small_pipe || !p->tile_items.empty() || !p->umma_items.empty() || !p->simt_items.empty())) {
-        blk_set_error("blk_attention_plan_create: the pack kernel cannot take this batch (BLK_DISABLE_PIPE or "
-                      "BLK_DISABLE_SMALL set?)");
-        rc = BLK_ERR_UNSUPPORTED;
+    int rc = BLK_OK;
+    if (small) {
+        rc = blk_build_gemm_schedule(p);
+        const bool packs_only = rc == BLK_OK && (nonempty == 0 || (p->small_pipe && p->tile_items.empty() &&
+                                                                   p->umma_items.empty() && p->simt_items.empty()));
+        if (rc == BLK_OK && !packs_only) {
+            if (any_length) {
+                small = false;  // the pack kernel is switched off: the general kernel takes the batch
+            } else {
+                blk_set_error("blk_attention_plan_create: the pack kernel cannot take this batch (BLK_DISABLE_PIPE or "
+                              "BLK_DISABLE_SMALL set?)");
+                rc = BLK_ERR_UNSUPPORTED;
+            }
+        }
+    }
+    if (rc == BLK_OK && !small) {
+        // every segment on the tcgen05 attention kernel; none of the GEMM schedules is used
+        p->attn = 2;
+        p->segs.clear(); p->tile_items.clear(); p->umma_items.clear(); p->simt_items.clear();
+        p->packs.clear(); p->pack_blocks.clear(); p->small_pipe = 0;
+        for (auto& v : p->small_items) v.clear();
+        p->Dm1 = p->Dout = p->a1[S];
+        p->Dm2 = p->a2[S];
+        rc = build_flash_items(p);
+        if (rc == BLK_OK && (int64_t)p->flash_items.size() * H >= ((int64_t)1 << 32)) {
+            blk_set_error("attention plan: more than 2^32 work items");
+            rc = BLK_ERR_UNSUPPORTED;
+        }
     }
     if (rc == BLK_OK) {
         p->flops = p->bytes = 0;
         for (int64_t s = 0; s < S; ++s) {
-            p->flops += 4.0 * (double)H * (double)M[s] * (double)N[s] * 64.0;
-            p->bytes += (double)H * 2.0 * 64.0 * (double)(2 * M[s] + 2 * N[s]);
+            p->flops += 4.0 * (double)H * (double)M[s] * (double)N[s] * (double)head_dim;
+            p->bytes += (double)H * 2.0 * (double)head_dim * (double)(2 * M[s] + 2 * N[s]);
         }
     }
-    if (rc == BLK_OK && !grid_ok((int64_t)p->packs.size(), H, "attention plan")) rc = BLK_ERR_UNSUPPORTED;
+    if (rc == BLK_OK && p->attn == 1 && !grid_ok((int64_t)p->packs.size(), H, "attention plan")) rc = BLK_ERR_UNSUPPORTED;
     if (rc == BLK_OK) rc = upload_plan(p);
     if (rc != BLK_OK) {
         blk_plan_destroy(p);
@@ -364,6 +426,16 @@ extern "C" int blk_attention_plan_create(blk_plan_t** plan, const int64_t* M, co
     }
     *plan = p;
     return BLK_OK;
+}
+
+extern "C" int blk_attention_plan_create(blk_plan_t** plan, const int64_t* M, const int64_t* N, int64_t S, int64_t H,
+                                         int dtype, int device) {
+    return attention_plan_impl(plan, M, N, S, H, 64, false, dtype, device);
+}
+
+extern "C" int blk_attention_plan_create_dim(blk_plan_t** plan, const int64_t* M, const int64_t* N, int64_t S, int64_t H,
+                                             int64_t head_dim, int dtype, int device) {
+    return attention_plan_impl(plan, M, N, S, H, head_dim, true, dtype, device);
 }
 
 // Shared body of blk_attention_run (strides 0: packed head-major strips) and blk_attention_run_strided.
@@ -377,8 +449,9 @@ extern "C" int blk_attention_run(const blk_plan_t* p, const void* q, const void*
 
 extern "C" int blk_attention_run_strided(const blk_plan_t* p, const void* q, const void* k, const void* v, void* out,
                                          int64_t row_stride, int64_t head_stride, float scale, void* cuda_stream) {
-    if (row_stride < 64 || head_stride <= 0 || row_stride % 8 || head_stride % 8) {
-        blk_set_error("blk_attention_run_strided: strides must be multiples of 8 elements, the row stride at least 64");
+    if (row_stride < (p && p->attn ? p->head_dim : 64) || head_stride <= 0 || row_stride % 8 || head_stride % 8) {
+        blk_set_error("blk_attention_run_strided: strides must be multiples of 8 elements, the row stride at least "
+                      "the head dimension");
         return BLK_ERR_INVALID;
     }
     return attention_run_impl(p, q, k, v, out, row_stride, head_stride, scale, cuda_stream);
@@ -394,7 +467,7 @@ static int attention_run_impl(const blk_plan* p, const void* q, const void* k, c
         blk_set_error("blk_attention_run: the plan was created without a device");
         return BLK_ERR_INVALID;
     }
-    if (p->packs.empty() || p->H == 0) return BLK_OK;
+    if ((p->attn == 1 ? p->packs.empty() : p->flash_items.empty()) || p->H == 0) return BLK_OK;
     if (!q || !k || !v || !out) {
         blk_set_error("blk_attention_run: null buffer");
         return BLK_ERR_INVALID;
@@ -404,6 +477,27 @@ static int attention_run_impl(const blk_plan* p, const void* q, const void* k, c
         return BLK_ERR_UNALIGNED;
     }
     if (scale == 0.f) scale = 1.17549435e-38f;  // softmax(0 * S) is the uniform distribution
+    if (p->attn == 2) {
+        const int64_t d = p->head_dim;
+        const bool strips = row_stride == 0;
+        BlkFlashParams fp{};
+        fp.out = out;
+        fp.items = p->d_flash_items;
+        fp.num_items = (int)p->flash_items.size();
+        fp.H = (int)p->H;
+        fp.D = (int)d;
+        fp.bf16 = p->dtype_in == BLK_BF16;
+        fp.scale = scale;
+        fp.status = p->d_status;
+        fp.layQ = BlkOperandLayout{p->Dm1 / d, strips ? d : row_stride, strips ? p->Dm1 : head_stride};
+        fp.layK = BlkOperandLayout{p->Dm2 / d, strips ? d : row_stride, strips ? p->Dm2 : head_stride};
+        fp.layV = fp.layK;
+        fp.out_row_stride = strips ? d : row_stride;
+        fp.out_head_stride = strips ? p->Dm1 : head_stride;
+        cudaError_t e = blk_launch_attn_umma(fp, q, k, v, p->num_sms, reinterpret_cast<cudaStream_t>(cuda_stream));
+        if (e != cudaSuccess) return cuda_fail("attention launch", e);
+        return BLK_OK;
+    }
     BlkPackParams pp{};
     pp.A = reinterpret_cast<const uint16_t*>(q);
     pp.B = reinterpret_cast<const uint16_t*>(k);

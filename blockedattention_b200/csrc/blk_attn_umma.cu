@@ -1,0 +1,473 @@
+// Fused attention for segments of any length on the 5th-generation tensor cores:
+// out_s = softmax(scale * Q_s K_s^T) V_s per segment and head, head dimension 64 or
+// 128, without the probabilities ever leaving the SM.
+//
+// A persistent CTA (one per SM, 10 warps) walks a static list of work items, an item
+// being a 128-row block of the queries of one segment of one head; it sweeps the
+// segment's keys and values in tiles of 128 rows.  Roles:
+//   warp 0    producer: one lane issues tiled TMA loads (128-byte swizzle) of the query
+//             block and, into a ring of stages, of each key tile and value tile;
+//   warp 1    MMA: one lane issues tcgen05.mma.  S = Q K^T (both operands K-major)
+//             goes to one of two 128-column accumulators in tensor memory; O += P V
+//             (P K-major from shared memory, V as loaded, i.e. MN-major) accumulates
+//             in a third region.  The products of tile g+1 are issued before P V of
+//             tile g, across item boundaries, so the tensor pipe works while the
+//             softmax warps are busy with tile g;
+//   warps 2-9 softmax: thread (quarter q, lane) owns row 32 q + lane of the block; the
+//             two warps of a quarter each take 64 of the 128 columns of a tile and
+//             exchange row maxima through shared memory.  Online softmax with a lazy
+//             reference: the running row maximum is only moved (and O rescaled in
+//             tensor memory) when the new maximum exceeds it by more than 8 in the
+//             exponent, so P <= 2^8 and the rescale is rare.  P is rounded to the
+//             input type and written to shared memory in the swizzled K-major layout
+//             the MMA reads.  After the last tile the warps read O, divide by the row
+//             sum and copy the rows out through their part of the P buffer.
+//
+// Rows of the tiles past the end of a segment belong to its neighbour (or are zero
+// past the end of the buffer): extra query rows are never stored, extra key columns
+// are masked before the row maximum, and the value rows of the last partial group of
+// 16 are cleared in shared memory, so nothing outside the segment reaches a result.
+//
+// Every wait is bounded: when the bound is hit the kernel records a status code, all
+// roles leave their loops, tensor memory is released and the kernel returns.
+//
+// Upstream has no fused operator; this replaces the chain blockGEMM -> blockSoftmax ->
+// blockGEMM(P, V) of its two operators (blockedAttention/apply.py:6-41) for the
+// attention use they are built for.
+#include <cuda.h>
+
+#include "blk_device.cuh"
+#include "blk_kernels.h"
+#include "blk_umma_ptx.cuh"
+
+namespace {
+
+constexpr int FA_BM = BLK_FLASH_BM;  // query rows per work item
+constexpr int FA_BN = 128;           // key / value rows per tile
+constexpr int FA_SOFT_WARPS = 8;
+constexpr int FA_THREADS = 64 + 32 * FA_SOFT_WARPS;
+constexpr int FA_BLOCK_BYTES = 128 * 128;  // 128 rows of one 64-column block: 16 KB
+constexpr int FA_O_COL = 256;              // tensor-memory column of the O accumulator
+constexpr float FA_LAZY = 8.f;             // exponent slack before the running maximum moves
+
+template <int D>
+struct FL {
+    static constexpr int NB = D / 64;                       // 64-column blocks of an operand row
+    static constexpr int STAGES = D == 64 ? 4 : 2;          // key/value ring
+    static constexpr int OPER_BYTES = NB * FA_BLOCK_BYTES;  // a 128 x D tile
+    static constexpr int Q_OFF = 0;
+    static constexpr int P_OFF = OPER_BYTES;                // 128 x 128 probabilities: two blocks
+    static constexpr int KV_OFF = P_OFF + 2 * FA_BLOCK_BYTES;
+    static constexpr int STAGE_BYTES = 2 * OPER_BYTES;      // key tile, then value tile
+    static constexpr int XCH_OFF = KV_OFF + STAGES * STAGE_BYTES;
+    static constexpr int XCH_BYTES = 2 * 2 * 128 * 4;       // [exchange parity][half][row]
+    static constexpr int BAR_OFF = XCH_OFF + XCH_BYTES;
+    static constexpr int SMEM_BYTES = BAR_OFF + 256;
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+};
+
+struct FaWork {
+    BlkFlashItem it;
+    int head;
+    int T;  // key/value tiles
+};
+
+__device__ __forceinline__ bool fa_work(const BlkFlashParams& p, uint32_t w, FaWork& wk) {
+    const uint32_t total = (uint32_t)p.num_items * (uint32_t)p.H;
+    if (w >= total) return false;
+    const uint32_t item = w / (uint32_t)p.H;
+    wk.head = (int)(w - item * (uint32_t)p.H);
+    wk.it = p.items[item];
+    wk.T = (wk.it.N + FA_BN - 1) / FA_BN;
+    return true;
+}
+
+__device__ __forceinline__ void fa_sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 fa_lds_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
+template <typename Tag, int D>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap mapQ,
+                     const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
+    using L = FL<D>;
+    constexpr int ST = L::STAGES;
+    extern __shared__ __align__(1024) unsigned char fa_smem_raw[];
+    unsigned char* smem = fa_smem_raw;
+    if (blk_smem_u32(smem) & 1023u) {  // the swizzled tiles rely on a 1024-byte aligned base
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, 29);
+        return;
+    }
+    float* xch = reinterpret_cast<float*>(smem + L::XCH_OFF);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+    // barriers: 0 q_full, 1 q_empty, 2 p_full, 3 pv_done, 4.. s_full[2], 6.. s_empty[2], 8.. k_full[ST],
+    // 12.. v_full[ST], 16.. kv_empty[ST]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 21);
+    volatile uint32_t* pair_base = reinterpret_cast<volatile uint32_t*>(bars + 22);  // 4 counters
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t smem_u32 = blk_smem_u32(smem);
+    const uint32_t bar0 = blk_smem_u32(bars);
+    const uint32_t q_full = bar0, q_empty = bar0 + 8, p_full = bar0 + 16, pv_done = bar0 + 24;
+    auto s_full = [&](int b) { return bar0 + 8u * (4 + b); };
+    auto s_empty = [&](int b) { return bar0 + 8u * (6 + b); };
+    auto k_full = [&](int s) { return bar0 + 8u * (8 + s); };
+    auto v_full = [&](int s) { return bar0 + 8u * (12 + s); };
+    auto kv_empty = [&](int s) { return bar0 + 8u * (16 + s); };
+    const uint32_t sQ = smem_u32 + L::Q_OFF, sP = smem_u32 + L::P_OFF;
+    auto sK = [&](int s) { return smem_u32 + L::KV_OFF + s * L::STAGE_BYTES; };
+    auto sV = [&](int s) { return smem_u32 + L::KV_OFF + s * L::STAGE_BYTES + L::OPER_BYTES; };
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        mbar_init(q_empty, 1);
+        mbar_init(p_full, FA_SOFT_WARPS);
+        mbar_init(pv_done, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(s_full(b), 1);
+            mbar_init(s_empty(b), FA_SOFT_WARPS);
+        }
+        for (int s = 0; s < ST; ++s) {
+            mbar_init(k_full(s), 1);
+            mbar_init(v_full(s), 1);
+            mbar_init(kv_empty(s), 1);
+        }
+        *abort_flag = 0;
+        for (int i = 0; i < 4; ++i) pair_base[i] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(blk_smem_u32(tmem_slot)),
+                     "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            uint32_t g = 0, itc = 0;
+            FaWork wk;
+            bool ok = true;
+            auto load_tile = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int row, int head, int hf) {
+                mbar_expect_tx(bar, L::OPER_BYTES);
+#pragma unroll
+                for (int b = 0; b < L::NB; ++b)  // coordinates (k, row, head), or (k, head, row) for a token-major operand
+                    tma_load_3d(dst + b * FA_BLOCK_BYTES, map, bar, 64 * b, hf ? head : row, hf ? row : head);
+            };
+            for (uint32_t w = blockIdx.x; ok && fa_work(p, w, wk); w += gridDim.x, ++itc) {
+                if (!mbar_wait(q_empty, (itc & 1u) ^ 1u, abort_flag, p.status, 21)) break;
+                load_tile(sQ, &mapQ, q_full, wk.it.rowQ, wk.head, p.head_firstQ);
+                for (int j = 0; j < wk.T; ++j, ++g) {
+                    const int stage = (int)(g % ST);
+                    if (!mbar_wait(kv_empty(stage), ((g / ST) & 1u) ^ 1u, abort_flag, p.status, 22)) { ok = false; break; }
+                    load_tile(sK(stage), &mapK, k_full(stage), wk.it.rowKV + j * FA_BN, wk.head, p.head_firstK);
+                    load_tile(sV(stage), &mapV, v_full(stage), wk.it.rowKV + j * FA_BN, wk.head, p.head_firstV);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            struct Cur {
+                uint32_t w, g, itc;
+                int j;
+                FaWork wk;
+                bool valid;
+            };
+            auto start = [&](Cur& c) { c.valid = fa_work(p, c.w, c.wk); c.j = 0; };
+            auto advance = [&](Cur& c) {
+                ++c.g;
+                if (++c.j == c.wk.T) {
+                    c.w += gridDim.x;
+                    ++c.itc;
+                    start(c);
+                }
+            };
+            const int neg = p.scale < 0.f;
+            const uint32_t idesc_pv = instr_desc(p.bf16, D, 0, 1);
+            bool ok = true;
+            auto issue_qk = [&](const Cur& c) {
+                const int stage = (int)(c.g % ST), buf = (int)(c.g & 1u);
+                if (c.j == 0 && !mbar_wait(q_full, c.itc & 1u, abort_flag, p.status, 23)) { ok = false; return; }
+                if (!mbar_wait(k_full(stage), (c.g / ST) & 1u, abort_flag, p.status, 24)) { ok = false; return; }
+                if (!mbar_wait(s_empty(buf), ((c.g >> 1) & 1u) ^ 1u, abort_flag, p.status, 25)) { ok = false; return; }
+                tc_fence_after();
+                const int ncols = min(c.wk.it.N - c.j * FA_BN, FA_BN);
+                const uint32_t idesc = instr_desc(p.bf16, (ncols + 15) & ~15, neg);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * FA_BN);
+                const uint32_t a0 = sQ, b0 = sK(stage);
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint32_t o = (uint32_t)((k >> 2) * FA_BLOCK_BYTES + 32 * (k & 3));
+                    tc_mma_f16(d_tmem, smem_desc_sw128(a0 + o), smem_desc_sw128(b0 + o), idesc, k != 0);
+                }
+                tc_commit(s_full(buf));
+                if (c.j == c.wk.T - 1) tc_commit(q_empty);  // the query block is free once these products have read it
+            };
+            auto issue_pv = [&](const Cur& c) {
+                const int stage = (int)(c.g % ST);
+                if (!mbar_wait(p_full, c.g & 1u, abort_flag, p.status, 26)) { ok = false; return; }
+                if (!mbar_wait(v_full(stage), (c.g / ST) & 1u, abort_flag, p.status, 27)) { ok = false; return; }
+                tc_fence_after();
+                const int ncols = min(c.wk.it.N - c.j * FA_BN, FA_BN);
+                const int ksteps = (ncols + 15) >> 4;
+                const uint32_t d_tmem = tmem_base + FA_O_COL;
+                const uint32_t b0 = sV(stage);
+                for (int k = 0; k < ksteps; ++k) {
+                    const uint32_t oa = (uint32_t)((k >> 2) * FA_BLOCK_BYTES + 32 * (k & 3));
+                    tc_mma_f16(d_tmem, smem_desc_sw128(sP + oa), smem_desc_sw128_mn(b0 + 2048u * k, FA_BLOCK_BYTES), idesc_pv,
+                               (c.j | k) != 0);
+                }
+                tc_commit(kv_empty(stage));  // key and value tile reusable
+                tc_commit(pv_done);          // P reusable, O up to date
+            };
+            Cur a, b;
+            a.w = b.w = blockIdx.x;
+            a.g = b.g = a.itc = b.itc = 0;
+            start(a);
+            start(b);
+            if (a.valid) {
+                issue_qk(a);
+                advance(a);
+            }
+            while (ok && b.valid) {
+                if (a.valid) {
+                    issue_qk(a);
+                    if (!ok) break;
+                    advance(a);
+                }
+                issue_pv(b);
+                advance(b);
+            }
+        }
+    } else {
+        // ---------------- softmax and output: warps 2..9 ----------------
+        const int q = warp & 3, h = (warp - 2) >> 2;
+        const int row = q * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        const float sl = fabsf(p.scale) * BLK_LOG2E;  // a negative scale is applied by the MMA (negated Q)
+        volatile uint32_t* pair_cnt = pair_base + q;
+        uint32_t pair_target = 0, xc = 0;
+        // Rendezvous of the two warps of a quarter: a shared counter and a bounded spin, so that a warp whose
+        // partner gave up cannot wait for ever.
+        auto pair_sync = [&]() -> bool {
+            pair_target += 2;
+            __threadfence_block();
+            __syncwarp();
+            if (lane == 0) atomicAdd(const_cast<uint32_t*>(pair_cnt), 1u);
+            bool good = false;
+            for (uint32_t i = 0; i < BLK_UMMA_SPIN_LIMIT; ++i) {
+                if ((int32_t)(*pair_cnt - pair_target) >= 0) { good = true; break; }
+                if (i > 64) __nanosleep(32);
+                if ((i & 255u) == 255u && *abort_flag) break;
+            }
+            if (!good) {
+                *abort_flag = 1;
+                atomicCAS(p.status, 0, 28);
+            }
+            __syncwarp();
+            __threadfence_block();
+            return good;
+        };
+        // value a of this row to the partner warp, the partner's value back
+        auto exchange = [&](float a, float& other) -> bool {
+            volatile float* x = xch + (xc & 1u) * 256;
+            ++xc;
+            x[h * 128 + row] = a;
+            if (!pair_sync()) return false;
+            other = x[(h ^ 1) * 128 + row];
+            return true;
+        };
+        const uint32_t my_p = sP + h * FA_BLOCK_BYTES + row * 128;  // this row's 64 probabilities of a tile
+        const uint32_t sw7 = (uint32_t)(row & 7);
+        uint32_t g = 0;
+        FaWork wk;
+        bool ok = true;
+        uint32_t ra[32], rb[32];
+        for (uint32_t w = blockIdx.x; ok && fa_work(p, w, wk); w += gridDim.x) {
+            float m_run = -INFINITY, l_run = 0.f;
+            for (int j = 0; ok && j < wk.T; ++j, ++g) {
+                const int buf = (int)(g & 1u), stage = (int)(g % ST);
+                if (!mbar_wait(s_full(buf), (g >> 1) & 1u, abort_flag, p.status, 30)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t scol = lane_addr + (uint32_t)(buf * FA_BN + 64 * h);
+                tc_ld32(scol, ra);
+                tc_ld32(scol + 32, rb);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_empty(buf));  // the scores are in registers
+                const int ncols = min(wk.it.N - j * FA_BN, FA_BN);
+                const int lim = ncols - 64 * h;  // valid columns of this half
+                if (lim < 64) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (i >= lim) ra[i] = 0xff800000u;  // -inf
+                        if (32 + i >= lim) rb[i] = 0xff800000u;
+                    }
+                }
+                float pm = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    pm = fmaxf(pm, fmaxf(__uint_as_float(ra[i]), __uint_as_float(ra[i + 1])));
+                    pm = fmaxf(pm, fmaxf(__uint_as_float(rb[i]), __uint_as_float(rb[i + 1])));
+                }
+                float other;
+                if (!exchange(pm, other)) { ok = false; break; }
+                pm = fmaxf(pm, other);
+                const float m_new = fmaxf(m_run, pm);
+                const bool move = (m_new - m_run) * sl > FA_LAZY;  // always at the first tile (m_run = -inf)
+                float f = 1.f;
+                if (move) {
+                    f = blk_exp2((m_run - m_new) * sl);
+                    m_run = m_new;
+                }
+                const float nm = -m_run * sl;
+                float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float e0 = blk_exp2(fmaf(__uint_as_float(ra[i]), sl, nm));
+                    const float e1 = blk_exp2(fmaf(__uint_as_float(ra[i + 1]), sl, nm));
+                    s4[i & 3] += e0;
+                    s4[(i + 1) & 3] += e1;
+                    ra[i >> 1] = BlkCvt<Tag>::pack2(e0, e1);
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float e0 = blk_exp2(fmaf(__uint_as_float(rb[i]), sl, nm));
+                    const float e1 = blk_exp2(fmaf(__uint_as_float(rb[i + 1]), sl, nm));
+                    s4[i & 3] += e0;
+                    s4[(i + 1) & 3] += e1;
+                    rb[i >> 1] = BlkCvt<Tag>::pack2(e0, e1);
+                }
+                l_run = l_run * f + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+                if (j > 0) {
+                    // P V of the previous tile done: the P buffer is free and O is at rest
+                    if (!mbar_wait(pv_done, (g - 1u) & 1u, abort_flag, p.status, 31)) { ok = false; break; }
+                    tc_fence_after();
+                    if (__any_sync(0xffffffffu, move)) {
+#pragma unroll 1
+                        for (int c = 0; c < D / 2; c += 32) {
+                            uint32_t o[32];
+                            const uint32_t ocol = lane_addr + (uint32_t)(FA_O_COL + h * (D / 2) + c);
+                            tc_ld32(ocol, o);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                            tc_st32(ocol, o);
+                        }
+                        tc_wait_st();
+                    }
+                }
+                // probabilities of this row, columns [64 h, 64 h + 64): chunk c of the 128-byte row at c ^ (row & 7)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    fa_sts_v4(my_p + (((uint32_t)c ^ sw7) << 4), ra[4 * c], ra[4 * c + 1], ra[4 * c + 2], ra[4 * c + 3]);
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    fa_sts_v4(my_p + (((uint32_t)(4 + c) ^ sw7) << 4), rb[4 * c], rb[4 * c + 1], rb[4 * c + 2], rb[4 * c + 3]);
+                if (ncols & 15) {
+                    // last tile of the segment: clear the value rows between its end and the next multiple of 16
+                    if (!mbar_wait(v_full(stage), (g / ST) & 1u, abort_flag, p.status, 32)) { ok = false; break; }
+                    const int nz = (16 - (ncols & 15)) * L::NB * 8;  // 16-byte pieces to clear
+                    const int t = (warp - 2) * 32 + lane;
+                    if (t < nz) {
+                        const int rr = t / (L::NB * 8), rem = t % (L::NB * 8);
+                        fa_sts_v4(sV(stage) + (rem >> 3) * FA_BLOCK_BYTES + (ncols + rr) * 128 + (rem & 7) * 16, 0u, 0u, 0u, 0u);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy writes before the MMA's reads
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full);
+            }
+            if (!ok) break;
+            // ---- result rows of the item ----
+            if (!mbar_wait(pv_done, (g - 1u) & 1u, abort_flag, p.status, 33)) break;
+            tc_fence_after();
+            float other;
+            if (!exchange(l_run, other)) break;
+            const float inv = __frcp_rn(l_run + other);
+            // this warp's 32 rows x D/2 columns go through its own part of the P buffer (rows of 128 bytes)
+            const uint32_t region = sP + h * FA_BLOCK_BYTES + (q * 32) * 128;
+            constexpr int HB = D;        // bytes of half a result row
+            constexpr int LPR = HB / 16;  // lanes per row in the copy-out
+            constexpr int RPP = 32 / LPR;
+#pragma unroll 1
+            for (int c = 0; c < D / 2; c += 32) {
+                tc_ld32(lane_addr + (uint32_t)(FA_O_COL + h * (D / 2) + c), ra);
+#pragma unroll
+                for (int i = 0; i < 32; i += 2)
+                    ra[i >> 1] = BlkCvt<Tag>::pack2(__uint_as_float(ra[i]) * inv, __uint_as_float(ra[i + 1]) * inv);
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc)
+                    fa_sts_v4(region + lane * 128 + (((uint32_t)(c / 8 + cc) ^ (uint32_t)(lane & 7)) << 4), ra[4 * cc],
+                              ra[4 * cc + 1], ra[4 * cc + 2], ra[4 * cc + 3]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            {
+                const int cc = lane % LPR;
+                uint16_t* out = reinterpret_cast<uint16_t*>(p.out) + (int64_t)wk.head * p.out_head_stride + h * (D / 2) + cc * 8;
+#pragma unroll
+                for (int r0 = 0; r0 < 32; r0 += RPP) {
+                    const int rr = r0 + lane / LPR;
+                    const uint4 v = fa_lds_v4(region + rr * 128 + (((uint32_t)cc ^ (uint32_t)(rr & 7)) << 4));
+                    const int grow = q * 32 + rr;
+                    if (grow < wk.it.M)
+                        *reinterpret_cast<uint4*>(out + (int64_t)(wk.it.rowQ + grow) * p.out_row_stride) = v;
+                }
+            }
+            __syncwarp();
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // a role gave up: let copies that may still be in flight land before the CTA's memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
+    }
+}
+
+template <typename Tag, int D>
+cudaError_t launch(const BlkFlashParams& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, int sms,
+                   cudaStream_t st) {
+    auto kern = blk_attn_umma_kernel<Tag, D>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FL<D>::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    const int64_t total = (int64_t)p.num_items * p.H;
+    const dim3 grid((unsigned)(total < sms ? total : sms)), block(FA_THREADS);
+    kern<<<grid, block, FL<D>::SMEM_BYTES, st>>>(p, mq, mk, mv);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t blk_launch_attn_umma(const BlkFlashParams& p_in, const void* q, const void* k, const void* v, int sms,
+                                 cudaStream_t st) {
+    if ((int64_t)p_in.num_items * p_in.H == 0) return cudaSuccess;
+    if (p_in.D != 64 && p_in.D != 128) return cudaErrorInvalidValue;
+    BlkFlashParams p = p_in;
+    CUtensorMap mq, mk, mv;
+    if (!blk_make_row_map(&mq, q, p.bf16, p.D, p.H, p.layQ, 64, FA_BM, &p.head_firstQ) ||
+        !blk_make_row_map(&mk, k, p.bf16, p.D, p.H, p.layK, 64, FA_BN, &p.head_firstK) ||
+        !blk_make_row_map(&mv, v, p.bf16, p.D, p.H, p.layV, 64, FA_BN, &p.head_firstV))
+        return cudaErrorInvalidValue;
+    if (p.D == 64) return p.bf16 ? launch<BlkBf16Tag, 64>(p, mq, mk, mv, sms, st) : launch<BlkHalfTag, 64>(p, mq, mk, mv, sms, st);
+    return p.bf16 ? launch<BlkBf16Tag, 128>(p, mq, mk, mv, sms, st) : launch<BlkHalfTag, 128>(p, mq, mk, mv, sms, st);
+}

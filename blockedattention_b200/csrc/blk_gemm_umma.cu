@@ -42,6 +42,7 @@
 
 #include "blk_device.cuh"
 #include "blk_kernels.h"
+#include "blk_umma_ptx.cuh"
 
 namespace {
 
@@ -62,93 +63,8 @@ constexpr int UM_STRIP_PITCH = UM_ROWPIECE_BYTES + 20;  // bytes per strip row: 
 constexpr int UM_STRIP_BYTES = 32 * UM_STRIP_PITCH;   // per epilogue warp
 constexpr int UM_XCH_BYTES = 2 * 2 * UM_SPLIT * 128 * 4;  // row statistics exchanged between the two halves, double-buffered
 constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + UM_EPI_WARPS * UM_STRIP_BYTES + UM_XCH_BYTES + 256;
-constexpr uint32_t UM_SPIN_LIMIT = 6u << 20;
 static_assert(UM_SMEM_BYTES <= 227 * 1024, "shared memory budget");
 static_assert(UM_STAGES <= 4, "barrier slots");
-
-// ---- PTX wrappers -------------------------------------------------------------
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n .reg .pred q;\n mbarrier.test_wait.parity.shared::cta.b64 q, [%1], %2;\n selp.u32 %0, 1, 0, q;\n}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false when another role has already given up or when the bound is hit
-// (then the status word and the CTA's abort flag are set).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code) {
-    for (uint32_t i = 0; i < UM_SPIN_LIMIT; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if (i > 128) __nanosleep(64);
-        if ((i & 255u) == 255u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicCAS(status, 0, code);
-    return false;
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
-        : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n .reg .pred q;\n setp.ne.b32 q, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, q;\n}\n"
-        ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc)
-        : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,"
-        "%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,"
-        "%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};\n"
-        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-          "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-          "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
-
-// K-major operand tile, rows of 128 bytes, 128-byte swizzle: 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// kind::f16, fp32 accumulate, both operands K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t instr_desc(int bf16, int n, int negate_a) {
-    return (1u << 4) | ((uint32_t)bf16 << 7) | ((uint32_t)bf16 << 10) | ((uint32_t)negate_a << 13) |
-           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(UM_BM >> 4) << 24);
-}
 
 struct Work {
     BlkUmmaItem it;
@@ -386,7 +302,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
             __syncwarp();
             if (lane == 0) atomicAdd(const_cast<uint32_t*>(pair_cnt), 1u);
             bool good = false;
-            for (uint32_t i = 0; i < UM_SPIN_LIMIT; ++i) {
+            for (uint32_t i = 0; i < BLK_UMMA_SPIN_LIMIT; ++i) {
                 if ((int32_t)(*pair_cnt - pair_target) >= 0) { good = true; break; }
                 if (i > 64) __nanosleep(32);
                 if ((i & 255u) == 255u && *abort_flag) break;

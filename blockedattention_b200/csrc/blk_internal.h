@@ -89,6 +89,15 @@ struct BlkUmmaItem {
 };
 static_assert(sizeof(BlkUmmaItem) == 32, "BlkUmmaItem layout");
 
+// One work item of the fused attention kernel for long segments: a 128-row block of the queries of a segment.
+struct BlkFlashItem {
+    int32_t rowQ;   // first query row of the block in the (rows, d) view of q (and of the result)
+    int32_t rowKV;  // first key / value row of the segment
+    int32_t M;      // query rows of the segment from this block on (the block holds min(M, 128))
+    int32_t N;      // key / value rows of the segment
+};
+static_assert(sizeof(BlkFlashItem) == 16, "BlkFlashItem layout");
+
 // ---- kernel geometry constants the scheduler must agree with ----------------
 constexpr int BLK_TILE_BM = 64;
 constexpr int BLK_TILE_BN = 128;
@@ -104,6 +113,7 @@ constexpr int BLK_PACK_ROWS_ATTN = 128;  // same for the attention variant, whos
 constexpr int BLK_PACK_BLOCKS = 16;   // segments a pack may hold
 constexpr int BLK_SMX_WINDOW_BYTES = 16384;
 constexpr int BLK_UMMA_BM = 128;
+constexpr int BLK_FLASH_BM = 128;
 constexpr int BLK_NOALLOC_MAX_CHUNKS = 65536;  // entries of the built-in chunk table of blk_softmax_noalloc
 
 // ---- the plan ----------------------------------------------------------------
@@ -125,7 +135,11 @@ struct blk_plan {
     int umma_K = 0;                         // uniform K of the tcgen05 bin
     int small_K = 0;                        // uniform K of the small bin
     int small_pipe = 0;                     // 1: the small segments run as packs on the pipelined kernel
-    int attn = 0;                           // 1: attention plan (every segment in packs, result = softmax(QK^T) V)
+    int attn = 0;                           // attention plan (result = softmax(QK^T) V): 1 every segment in packs,
+                                            // 2 every segment on the tcgen05 attention kernel
+    int head_dim = 64;                      // attention plans: columns of q, k, v and result rows
+    std::vector<BlkFlashItem> flash_items;
+    BlkFlashItem* d_flash_items = nullptr;
     std::vector<BlkPack> packs;
     std::vector<BlkPackBlock> pack_blocks;
     BlkPack* d_packs = nullptr;

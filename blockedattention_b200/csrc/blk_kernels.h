@@ -90,6 +90,20 @@ struct BlkPackParams {
     int64_t out_row_stride, out_head_stride;  // elements; result row r of head h at C[h * head_stride + r * row_stride]
 };
 
+struct BlkFlashParams {
+    void* out;
+    const BlkFlashItem* items;
+    int num_items;
+    int H;
+    int D;  // head dimension: 64 or 128
+    int bf16;
+    float scale;
+    int* status;
+    BlkOperandLayout layQ, layK, layV;
+    int head_firstQ, head_firstK, head_firstV;  // coordinate order of the tensor maps (filled by the launcher)
+    int64_t out_row_stride, out_head_stride;    // elements; result row r of head h at out[h * head_stride + r * row_stride]
+};
+
 struct BlkSmxParams {
     const void* src;
     void* dst;
@@ -129,5 +143,7 @@ cudaError_t blk_launch_scores_small(const BlkSmallParams& p, int dtype_in, int K
 cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p, const void* A, const void* B, const BlkOperandLayout& layA,
                                  const BlkOperandLayout& layB,
                                  int sms, cudaStream_t st);
+cudaError_t blk_launch_attn_umma(const BlkFlashParams& p, const void* q, const void* k, const void* v, int sms,
+                                 cudaStream_t st);
 cudaError_t blk_launch_scores_pipe(const BlkPackParams& p, int dtype_in, int sms, cudaStream_t st);
 cudaError_t blk_launch_softmax(const BlkSmxParams& p, int dtype, cudaStream_t st);

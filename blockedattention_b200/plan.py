@@ -182,10 +182,11 @@ class GemmPlan(_Plan):
 
 
 class AttentionPlan(_Plan):
-    """Fused ``softmax(scale * Q_s K_s^T) V_s`` for segments of at most 64 query and 64 key rows, head dimension 64.
-    Raises ``RuntimeError`` (library code BLK_ERR_UNSUPPORTED) for any other batch."""
+    """Fused ``softmax(scale * Q_s K_s^T) V_s``, head dimension ``d`` 64 or 128, fp16 or bf16.  A batch whose every
+    segment has at most 64 query and 64 key rows (``d = 64``) runs on the pack kernel, any other on the tcgen05
+    attention kernel; ``small_only=True`` asks for the pack kernel or ``RuntimeError`` (BLK_ERR_UNSUPPORTED)."""
 
-    def __init__(self, MList, NList, H: int, dtype: torch.dtype, device=None):
+    def __init__(self, MList, NList, H: int, dtype: torch.dtype, device=None, d: int = 64, small_only: bool = False):
         super().__init__()
         self.M, self.N = _host_i64(MList), _host_i64(NList)
         if len(self.M) != len(self.N):
@@ -194,9 +195,16 @@ class AttentionPlan(_Plan):
         self.device = torch.device(device) if device is not None else None
         dev = -1 if self.device is None else (self.device.index if self.device.index is not None
                                                else torch.cuda.current_device())
-        L.check(L.lib.blk_attention_plan_create(C.byref(self._h), L.i64(self.M), L.i64(self.N), self.S, self.H,
-                                                dtype_code(dtype), dev))
-        self.Dq, self.Dkv = int(self.M.sum()) * 64, int(self.N.sum()) * 64
+        self.d = int(d)
+        if small_only:
+            if self.d != 64:
+                raise RuntimeError("the pack kernel needs head dimension 64")
+            L.check(L.lib.blk_attention_plan_create(C.byref(self._h), L.i64(self.M), L.i64(self.N), self.S, self.H,
+                                                    dtype_code(dtype), dev))
+        else:
+            L.check(L.lib.blk_attention_plan_create_dim(C.byref(self._h), L.i64(self.M), L.i64(self.N), self.S, self.H,
+                                                        self.d, dtype_code(dtype), dev))
+        self.Dq, self.Dkv = int(self.M.sum()) * self.d, int(self.N.sum()) * self.d
 
     def run(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
             scale: float = 1.0) -> torch.Tensor:
@@ -208,7 +216,7 @@ class AttentionPlan(_Plan):
         if out is None:
             out = torch.empty((self.H, self.Dq), dtype=self.dtype, device=q.device)
         elif not out.is_cuda or not out.is_contiguous() or out.dtype != self.dtype or out.numel() != self.H * self.Dq:
-            raise RuntimeError("out must be a contiguous CUDA tensor of the plan's dtype with H*sum(M)*64 elements")
+            raise RuntimeError("out must be a contiguous CUDA tensor of the plan's dtype with H*sum(M)*d elements")
         q, k, v = (t if t.data_ptr() % 16 == 0 else t.clone() for t in (q, k, v))
         if out.data_ptr() % 16:
             raise RuntimeError("out must be 16-byte aligned")
@@ -221,24 +229,25 @@ class AttentionPlan(_Plan):
 
     def run_token_major(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
                         scale: float = 1.0) -> torch.Tensor:
-        """Same for token-major tensors ``q, out -> (sum m_s, H, 64)``, ``k, v -> (sum n_s, H, 64)``, read and written
+        """Same for token-major tensors ``q, out -> (sum m_s, H, d)``, ``k, v -> (sum n_s, H, d)``, read and written
         in place through strided tensor maps (needs ``sum m_s == sum n_s`` only in so far as all four share strides)."""
         if self.device is None:
             raise RuntimeError("this plan was built without a device")
         rq, rkv = int(self.M.sum()), int(self.N.sum())
         for name, t, rows in (("q", q, rq), ("k", k, rkv), ("v", v, rkv)):
-            if (not t.is_cuda or not t.is_contiguous() or t.dtype != self.dtype or tuple(t.shape) != (rows, self.H, 64)
-                    or t.data_ptr() % 16):
-                raise RuntimeError(f"{name} must be a contiguous, 16-byte aligned CUDA tensor of shape ({rows}, {self.H}, 64)")
+            if (not t.is_cuda or not t.is_contiguous() or t.dtype != self.dtype
+                    or tuple(t.shape) != (rows, self.H, self.d) or t.data_ptr() % 16):
+                raise RuntimeError(f"{name} must be a contiguous, 16-byte aligned CUDA tensor of shape "
+                                   f"({rows}, {self.H}, {self.d})")
         if out is None:
-            out = torch.empty((rq, self.H, 64), dtype=self.dtype, device=q.device)
-        elif (not out.is_cuda or not out.is_contiguous() or out.dtype != self.dtype or tuple(out.shape) != (rq, self.H, 64)
-              or out.data_ptr() % 16):
-            raise RuntimeError(f"out must be a contiguous, 16-byte aligned CUDA tensor of shape ({rq}, {self.H}, 64)")
+            out = torch.empty((rq, self.H, self.d), dtype=self.dtype, device=q.device)
+        elif (not out.is_cuda or not out.is_contiguous() or out.dtype != self.dtype
+              or tuple(out.shape) != (rq, self.H, self.d) or out.data_ptr() % 16):
+            raise RuntimeError(f"out must be a contiguous, 16-byte aligned CUDA tensor of shape ({rq}, {self.H}, {self.d})")
         with torch.cuda.device(q.device):
             L.check(L.lib.blk_attention_run_strided(self._h, C.c_void_p(q.data_ptr()), C.c_void_p(k.data_ptr()),
                                                     C.c_void_p(v.data_ptr()), C.c_void_p(out.data_ptr()),
-                                                    self.H * 64, 64, C.c_float(scale),
+                                                    self.H * self.d, self.d, C.c_float(scale),
                                                     C.c_void_p(_stream_ptr(q.device))))
         return out
 

@@ -131,6 +131,13 @@ def workload(name: str, seed: int = 0, segments: Optional[int] = None) -> Worklo
         return Workload(name, n, n.copy(), np.full(len(n), 128, np.int64), 16, torch.bfloat16, torch.bfloat16,
                         1 / math.sqrt(128), True, "normal", d_v=128,
                         note="1024 graphs n~U{64..512} + 64 graphs n=1, 16 heads, d=128, bf16, P then P@V")
+    if name in ("long_tail_attention", "full_forward_attention"):
+        # the same batches with the product with V fused in: one kernel, P never stored
+        b = workload(name[:-len("_attention")], seed, segments)
+        dv = int(b.K[0])
+        return Workload(name, b.M, b.N, b.K, b.H, b.dtype, b.dtype, b.scale, True, "normal", std=b.std, d_v=dv,
+                        note=b.note.replace(", P then P@V", "") + ", fused softmax(QK^T)V without materialising P",
+                        extra={"fused_attention": True})
     if name == "large_k":
         S = segments or 64
         n = _i64(rs.randint(1024, 2049, size=S))
@@ -140,4 +147,5 @@ def workload(name: str, seed: int = 0, segments: Optional[int] = None) -> Worklo
     raise ValueError(f"unknown workload {name!r}")
 
 
-WORKLOADS = ("cpu_plumbing", "molecular", "molecular_attention", "general_gemm", "long_tail", "full_forward", "large_k")
+WORKLOADS = ("cpu_plumbing", "molecular", "molecular_attention", "general_gemm", "long_tail", "full_forward", "large_k",
+             "long_tail_attention", "full_forward_attention")

@@ -135,7 +135,7 @@ BLK_API int blk_gemm_run_strided(const blk_plan_t* plan, const void* mat1, int64
                          const void* mat2, int64_t row_stride2, int64_t head_stride2, void* out, float scale,
                          void* cuda_stream);
 
-/* ---- fused attention for small segments ------------------------------------- */
+/* ---- fused attention --------------------------------------------------------- */
 
 /* out_s = softmax_rows(scale * Q_s K_s^T) V_s for segments of at most 64 query
  * rows and 64 key rows, head dimension 64, fp16 or bf16, in one kernel: the
@@ -148,13 +148,25 @@ BLK_API int blk_gemm_run_strided(const blk_plan_t* plan, const void* mat1, int64
  * operators for it.  No counterpart upstream (upstream materialises P). */
 BLK_API int blk_attention_plan_create(blk_plan_t** plan, const int64_t* M, const int64_t* N, int64_t S, int64_t H,
                               int dtype, int device);
+/* The same operator for any batch: segments of any length (M_s >= 0 queries,
+ * N_s >= 1 keys where M_s > 0), head dimension 64 or 128.  A batch the kernel
+ * above can take runs on it; every other batch runs on one tcgen05 kernel that
+ * sweeps a segment's keys and values in tiles of 128 rows with an online
+ * softmax, the scores in tensor memory, the probabilities handed to the second
+ * product through shared memory: neither is ever stored.  q (H, sum M_s * d),
+ * k, v (H, sum N_s * d), out (H, sum M_s * d).  Replaces the upstream chain
+ * blockGEMM -> blockSoftmax -> blockGEMM (blockedAttention/apply.py:6-41,
+ * test/pytest.py:35-38) where its result feeds the product with V.
+ * blk_plan_summary reports this kernel's work items in counts[3]. */
+BLK_API int blk_attention_plan_create_dim(blk_plan_t** plan, const int64_t* M, const int64_t* N, int64_t S, int64_t H,
+                                  int64_t head_dim, int dtype, int device);
 BLK_API int blk_attention_run(const blk_plan_t* plan, const void* q, const void* k, const void* v, void* out,
                       float scale, void* cuda_stream);
 /* The same for q, k, v and out that are not packed strips: row r (counted over
  * all segments in batch order) of head h of each of the four tensors starts at
  * element r * row_stride + h * head_stride; strides in elements, multiples of 8.
- * Token-major [rows, H, 64] tensors -- the layout attention layers hold their
- * activations in -- are row_stride = H * 64, head_stride = 64: no permuted copy
+ * Token-major [rows, H, d] tensors -- the layout attention layers hold their
+ * activations in -- are row_stride = H * d, head_stride = d: no permuted copy
  * on the way in or out. */
 BLK_API int blk_attention_run_strided(const blk_plan_t* plan, const void* q, const void* k, const void* v, void* out,
                               int64_t row_stride, int64_t head_stride, float scale, void* cuda_stream);

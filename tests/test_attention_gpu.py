@@ -38,7 +38,7 @@ def test_fused_attention_every_small_extent(cuda_device, dtype, scale):
     q, k = packed_inputs(M, N, np.full_like(M, 64), H, dtype, 1)
     v = packed_inputs(N, N, np.full_like(M, 64), H, dtype, 2)[0]
     out = torch.full((H, int(M.sum()) * 64), float("nan"), dtype=dtype, device=dev)
-    plan = AttentionPlan(M, N, H, dtype, device=dev)
+    plan = AttentionPlan(M, N, H, dtype, device=dev, small_only=True)
     assert plan.summary["packs"] > 0 and plan.summary["tile_items"] == 0
     plan.run(q.to(dev), k.to(dev), v.to(dev), out=out, scale=scale)
     plan.check()
@@ -66,16 +66,20 @@ def test_fused_attention_molecular_sizes_and_composition(cuda_device):
 
 
 def test_attention_falls_back_to_the_composition(cuda_device):
-    # segments beyond 64 rows, or another head dimension, run as scores + P V; same operator, same result
+    # a head dimension neither fused kernel takes runs as scores + P V; same operator, same result
     dev = cuda_device
     n = np.array([10, 100, 64, 200])
     H = 2
-    q, k = packed_inputs(n, n, np.full_like(n, 64), H, BF16, 5)
-    v = packed_inputs(n, n, np.full_like(n, 64), H, BF16, 6)[0]
-    got = blockAttention(q.to(dev), k.to(dev), v.to(dev), n, n, scale=0.125)
-    close(got, oracle_attention(q, k, v, n, n, 0.125), BF16, "composed attention")
+    q, k = packed_inputs(n, n, np.full_like(n, 32), H, BF16, 5)
+    v = packed_inputs(n, n, np.full_like(n, 32), H, BF16, 6)[0]
+    got = blockAttention(q.to(dev), k.to(dev), v.to(dev), n, n, scale=0.125, d=32)
+    d = np.full_like(n, 32)
+    P = O.block_scores(q, k, n, n, d, scale=0.125)
+    close(got, O.block_gemm(P, v, n, d, n, transpose2=True), BF16, "composed attention")
     with pytest.raises(RuntimeError):
-        AttentionPlan(n, n, H, BF16, device=dev)      # the fused plan itself refuses the batch
+        AttentionPlan(n, n, H, BF16, device=dev, small_only=True)   # the pack kernel refuses segments beyond 64 rows
+    with pytest.raises(RuntimeError):
+        AttentionPlan(n, n, H, BF16, device=dev, d=32)              # and neither kernel has this head dimension
     with pytest.raises(RuntimeError):
         blockAttention(q, k.to(dev), v.to(dev), n, n)  # CPU tensor
 
