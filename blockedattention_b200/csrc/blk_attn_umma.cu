@@ -42,27 +42,32 @@
 
 namespace {
 
+#ifdef FA_X_NOEXP
+#define blk_exp2(x) (x)
+#endif
+
 constexpr int FA_BM = BLK_FLASH_BM;  // query rows per work item
 constexpr int FA_BN = 128;           // key / value rows per tile
 constexpr int FA_SOFT_WARPS = 8;
 constexpr int FA_THREADS = 64 + 32 * FA_SOFT_WARPS;
 constexpr int FA_BLOCK_BYTES = 128 * 128;  // 128 rows of one 64-column block: 16 KB
 constexpr int FA_O_COL = 256;              // tensor-memory column of the O accumulator
+constexpr int FA_P_COL = 384;              // two buffers of 64 columns: the probabilities of a tile, two per column
 constexpr float FA_LAZY = 8.f;             // exponent slack before the running maximum moves
 
 template <int D>
 struct FL {
     static constexpr int NB = D / 64;                       // 64-column blocks of an operand row
-    static constexpr int STAGES = D == 64 ? 4 : 2;          // key/value ring
+    static constexpr int STAGES = D == 64 ? 6 : 3;          // key/value ring
     static constexpr int OPER_BYTES = NB * FA_BLOCK_BYTES;  // a 128 x D tile
     static constexpr int Q_OFF = 0;
-    static constexpr int P_OFF = OPER_BYTES;                // 128 x 128 probabilities: two blocks
-    static constexpr int KV_OFF = P_OFF + 2 * FA_BLOCK_BYTES;
+    static constexpr int KV_OFF = OPER_BYTES;
     static constexpr int STAGE_BYTES = 2 * OPER_BYTES;      // key tile, then value tile
     static constexpr int XCH_OFF = KV_OFF + STAGES * STAGE_BYTES;
     static constexpr int XCH_BYTES = 2 * 2 * 128 * 4;       // [exchange parity][half][row]
     static constexpr int BAR_OFF = XCH_OFF + XCH_BYTES;
-    static constexpr int SMEM_BYTES = BAR_OFF + 256;
+    static constexpr int SMEM_BYTES = BAR_OFF + 512;
+    static_assert(STAGES <= 6, "barrier slots");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
@@ -82,15 +87,29 @@ __device__ __forceinline__ bool fa_work(const BlkFlashParams& p, uint32_t w, FaW
     return true;
 }
 
+// tcgen05.ld of 32 columns without the wait (fa_ld_wait() before the registers are read)
+__device__ __forceinline__ void fa_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,"
+        "%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+// D += A B with the first operand in tensor memory (16-bit elements, two per column, row = lane)
+__device__ __forceinline__ void fa_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n .reg .pred q;\n setp.ne.b32 q, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, q;\n}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(db), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void fa_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void fa_sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-__device__ __forceinline__ uint4 fa_lds_v4(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
-    return v;
-}
-
 template <typename Tag, int D>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap mapQ,
@@ -105,31 +124,38 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
     }
     float* xch = reinterpret_cast<float*>(smem + L::XCH_OFF);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
-    // barriers: 0 q_full, 1 q_empty, 2 p_full, 3 pv_done, 4.. s_full[2], 6.. s_empty[2], 8.. k_full[ST],
-    // 12.. v_full[ST], 16.. kv_empty[ST]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 21);
-    volatile uint32_t* pair_base = reinterpret_cast<volatile uint32_t*>(bars + 22);  // 4 counters
+    // barriers: 0 q_full, 1 q_empty, 2.. p_full[2], 4.. pv_done[2], 6.. s_full[2], 8.. s_empty[2], 10.. one per
+    // accumulator-lane quarter, on which its two softmax warps meet, 14.. k_full[ST], 20.. v_full[ST], 26.. kv_empty[ST]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 33);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef FA_TRACE
+    long long* fa_tr = reinterpret_cast<long long*>(reinterpret_cast<char*>(p.out) + (int64_t)p.H * p.out_head_stride * 2);
+#define FA_STAMP(role, g, k) do { if (blockIdx.x == 0 && (g) < 64u) fa_tr[((role) * 64 + (g)) * 8 + (k)] = clock64(); } while (0)
+#else
+#define FA_STAMP(role, g, k) do {} while (0)
+#endif
     const uint32_t smem_u32 = blk_smem_u32(smem);
     const uint32_t bar0 = blk_smem_u32(bars);
-    const uint32_t q_full = bar0, q_empty = bar0 + 8, p_full = bar0 + 16, pv_done = bar0 + 24;
-    auto s_full = [&](int b) { return bar0 + 8u * (4 + b); };
-    auto s_empty = [&](int b) { return bar0 + 8u * (6 + b); };
-    auto k_full = [&](int s) { return bar0 + 8u * (8 + s); };
-    auto v_full = [&](int s) { return bar0 + 8u * (12 + s); };
-    auto kv_empty = [&](int s) { return bar0 + 8u * (16 + s); };
-    const uint32_t sQ = smem_u32 + L::Q_OFF, sP = smem_u32 + L::P_OFF;
+    const uint32_t q_full = bar0, q_empty = bar0 + 8;
+    auto p_full = [&](int b) { return bar0 + 8u * (2 + b); };
+    auto pv_done = [&](int b) { return bar0 + 8u * (4 + b); };
+    auto s_full = [&](int b) { return bar0 + 8u * (6 + b); };
+    auto s_empty = [&](int b) { return bar0 + 8u * (8 + b); };
+    auto k_full = [&](int s) { return bar0 + 8u * (14 + s); };
+    auto v_full = [&](int s) { return bar0 + 8u * (20 + s); };
+    auto kv_empty = [&](int s) { return bar0 + 8u * (26 + s); };
+    const uint32_t sQ = smem_u32 + L::Q_OFF;
     auto sK = [&](int s) { return smem_u32 + L::KV_OFF + s * L::STAGE_BYTES; };
     auto sV = [&](int s) { return smem_u32 + L::KV_OFF + s * L::STAGE_BYTES + L::OPER_BYTES; };
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         mbar_init(q_empty, 1);
-        mbar_init(p_full, FA_SOFT_WARPS);
-        mbar_init(pv_done, 1);
         for (int b = 0; b < 2; ++b) {
+            mbar_init(p_full(b), FA_SOFT_WARPS);
+            mbar_init(pv_done(b), 1);
             mbar_init(s_full(b), 1);
             mbar_init(s_empty(b), FA_SOFT_WARPS);
         }
@@ -138,8 +164,8 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             mbar_init(v_full(s), 1);
             mbar_init(kv_empty(s), 1);
         }
+        for (int i = 0; i < 4; ++i) mbar_init(bar0 + 8u * (10 + i), 2);
         *abort_flag = 0;
-        for (int i = 0; i < 4; ++i) pair_base[i] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
@@ -169,7 +195,9 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 load_tile(sQ, &mapQ, q_full, wk.it.rowQ, wk.head, p.head_firstQ);
                 for (int j = 0; j < wk.T; ++j, ++g) {
                     const int stage = (int)(g % ST);
+                    FA_STAMP(2, g, 0);
                     if (!mbar_wait(kv_empty(stage), ((g / ST) & 1u) ^ 1u, abort_flag, p.status, 22)) { ok = false; break; }
+                    FA_STAMP(2, g, 1);
                     load_tile(sK(stage), &mapK, k_full(stage), wk.it.rowKV + j * FA_BN, wk.head, p.head_firstK);
                     load_tile(sV(stage), &mapV, v_full(stage), wk.it.rowKV + j * FA_BN, wk.head, p.head_firstV);
                 }
@@ -198,9 +226,12 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             bool ok = true;
             auto issue_qk = [&](const Cur& c) {
                 const int stage = (int)(c.g % ST), buf = (int)(c.g & 1u);
+                FA_STAMP(1, c.g, 0);
                 if (c.j == 0 && !mbar_wait(q_full, c.itc & 1u, abort_flag, p.status, 23)) { ok = false; return; }
                 if (!mbar_wait(k_full(stage), (c.g / ST) & 1u, abort_flag, p.status, 24)) { ok = false; return; }
+                FA_STAMP(1, c.g, 4);
                 if (!mbar_wait(s_empty(buf), ((c.g >> 1) & 1u) ^ 1u, abort_flag, p.status, 25)) { ok = false; return; }
+                FA_STAMP(1, c.g, 1);
                 tc_fence_after();
                 const int ncols = min(c.wk.it.N - c.j * FA_BN, FA_BN);
                 const uint32_t idesc = instr_desc(p.bf16, (ncols + 15) & ~15, neg);
@@ -216,20 +247,21 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             };
             auto issue_pv = [&](const Cur& c) {
                 const int stage = (int)(c.g % ST);
-                if (!mbar_wait(p_full, c.g & 1u, abort_flag, p.status, 26)) { ok = false; return; }
+                FA_STAMP(1, c.g, 2);
+                if (!mbar_wait(p_full((int)(c.g & 1u)), (c.g >> 1) & 1u, abort_flag, p.status, 26)) { ok = false; return; }
                 if (!mbar_wait(v_full(stage), (c.g / ST) & 1u, abort_flag, p.status, 27)) { ok = false; return; }
+                FA_STAMP(1, c.g, 3);
                 tc_fence_after();
                 const int ncols = min(c.wk.it.N - c.j * FA_BN, FA_BN);
                 const int ksteps = (ncols + 15) >> 4;
                 const uint32_t d_tmem = tmem_base + FA_O_COL;
                 const uint32_t b0 = sV(stage);
-                for (int k = 0; k < ksteps; ++k) {
-                    const uint32_t oa = (uint32_t)((k >> 2) * FA_BLOCK_BYTES + 32 * (k & 3));
-                    tc_mma_f16(d_tmem, smem_desc_sw128(sP + oa), smem_desc_sw128_mn(b0 + 2048u * k, FA_BLOCK_BYTES), idesc_pv,
-                               (c.j | k) != 0);
-                }
-                tc_commit(kv_empty(stage));  // key and value tile reusable
-                tc_commit(pv_done);          // P reusable, O up to date
+                const uint32_t a_tmem = tmem_base + (uint32_t)(FA_P_COL + 64 * (int)(c.g & 1u));
+                for (int k = 0; k < ksteps; ++k)  // 16 probabilities of a row are 8 columns
+                    fa_mma_f16_ts(d_tmem, a_tmem + 8u * k, smem_desc_sw128_mn(b0 + 2048u * k, FA_BLOCK_BYTES), idesc_pv,
+                                  (c.j | k) != 0);
+                tc_commit(kv_empty(stage));             // key and value tile reusable
+                tc_commit(pv_done((int)(c.g & 1u)));  // this P buffer reusable, O up to date
             };
             Cur a, b;
             a.w = b.w = blockIdx.x;
@@ -256,40 +288,19 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
         const int row = q * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         const float sl = fabsf(p.scale) * BLK_LOG2E;  // a negative scale is applied by the MMA (negated Q)
-        volatile uint32_t* pair_cnt = pair_base + q;
-        uint32_t pair_target = 0, xc = 0;
-        // Rendezvous of the two warps of a quarter: a shared counter and a bounded spin, so that a warp whose
-        // partner gave up cannot wait for ever.
-        auto pair_sync = [&]() -> bool {
-            pair_target += 2;
-            __threadfence_block();
-            __syncwarp();
-            if (lane == 0) atomicAdd(const_cast<uint32_t*>(pair_cnt), 1u);
-            bool good = false;
-            for (uint32_t i = 0; i < BLK_UMMA_SPIN_LIMIT; ++i) {
-                if ((int32_t)(*pair_cnt - pair_target) >= 0) { good = true; break; }
-                if (i > 64) __nanosleep(32);
-                if ((i & 255u) == 255u && *abort_flag) break;
-            }
-            if (!good) {
-                *abort_flag = 1;
-                atomicCAS(p.status, 0, 28);
-            }
-            __syncwarp();
-            __threadfence_block();
-            return good;
-        };
+        const uint32_t pair_bar = bar0 + 8u * (10 + q);
+        uint32_t xc = 0;
         // value a of this row to the partner warp, the partner's value back
         auto exchange = [&](float a, float& other) -> bool {
             volatile float* x = xch + (xc & 1u) * 256;
-            ++xc;
             x[h * 128 + row] = a;
-            if (!pair_sync()) return false;
-            other = x[(h ^ 1) * 128 + row];
-            return true;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(pair_bar);  // release: the warp's values are visible to whoever sees the phase end
+            const bool good = mbar_wait(pair_bar, xc & 1u, abort_flag, p.status, 28);
+            ++xc;
+            if (good) other = x[(h ^ 1) * 128 + row];
+            return good;
         };
-        const uint32_t my_p = sP + h * FA_BLOCK_BYTES + row * 128;  // this row's 64 probabilities of a tile
-        const uint32_t sw7 = (uint32_t)(row & 7);
         uint32_t g = 0;
         FaWork wk;
         bool ok = true;
@@ -298,11 +309,14 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             float m_run = -INFINITY, l_run = 0.f;
             for (int j = 0; ok && j < wk.T; ++j, ++g) {
                 const int buf = (int)(g & 1u), stage = (int)(g % ST);
+                if (warp == 2 && lane == 0) FA_STAMP(0, g, 0);
                 if (!mbar_wait(s_full(buf), (g >> 1) & 1u, abort_flag, p.status, 30)) { ok = false; break; }
+                if (warp == 2 && lane == 0) FA_STAMP(0, g, 1);
                 tc_fence_after();
                 const uint32_t scol = lane_addr + (uint32_t)(buf * FA_BN + 64 * h);
-                tc_ld32(scol, ra);
-                tc_ld32(scol + 32, rb);
+                fa_ld32_nowait(scol, ra);
+                fa_ld32_nowait(scol + 32, rb);
+                fa_ld_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s_empty(buf));  // the scores are in registers
@@ -315,6 +329,7 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                         if (32 + i >= lim) rb[i] = 0xff800000u;
                     }
                 }
+                if (warp == 2 && lane == 0) FA_STAMP(0, g, 2);
                 float pm = -INFINITY;
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
@@ -322,8 +337,13 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                     pm = fmaxf(pm, fmaxf(__uint_as_float(rb[i]), __uint_as_float(rb[i + 1])));
                 }
                 float other;
+#ifndef FA_X_NOEXCH
                 if (!exchange(pm, other)) { ok = false; break; }
                 pm = fmaxf(pm, other);
+#else
+                other = pm;
+#endif
+                if (warp == 2 && lane == 0) FA_STAMP(0, g, 3);
                 const float m_new = fmaxf(m_run, pm);
                 const bool move = (m_new - m_run) * sl > FA_LAZY;  // always at the first tile (m_run = -inf)
                 float f = 1.f;
@@ -333,13 +353,14 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 }
                 const float nm = -m_run * sl;
                 float s4[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t pk[32];  // the 64 probabilities, two per word
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const float e0 = blk_exp2(fmaf(__uint_as_float(ra[i]), sl, nm));
                     const float e1 = blk_exp2(fmaf(__uint_as_float(ra[i + 1]), sl, nm));
                     s4[i & 3] += e0;
                     s4[(i + 1) & 3] += e1;
-                    ra[i >> 1] = BlkCvt<Tag>::pack2(e0, e1);
+                    pk[i >> 1] = BlkCvt<Tag>::pack2(e0, e1);
                 }
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
@@ -347,33 +368,30 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                     const float e1 = blk_exp2(fmaf(__uint_as_float(rb[i + 1]), sl, nm));
                     s4[i & 3] += e0;
                     s4[(i + 1) & 3] += e1;
-                    rb[i >> 1] = BlkCvt<Tag>::pack2(e0, e1);
+                    pk[16 + (i >> 1)] = BlkCvt<Tag>::pack2(e0, e1);
                 }
                 l_run = l_run * f + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
-                if (j > 0) {
-                    // P V of the previous tile done: the P buffer is free and O is at rest
-                    if (!mbar_wait(pv_done, (g - 1u) & 1u, abort_flag, p.status, 31)) { ok = false; break; }
+                if (warp == 2 && lane == 0) FA_STAMP(0, g, 4);
+                // this tile's P buffer was last read by P V of tile g - 2
+                if (g >= 2u && !mbar_wait(pv_done(buf), ((g >> 1) - 1u) & 1u, abort_flag, p.status, 31)) { ok = false; break; }
+                if (j > 0 && __any_sync(0xffffffffu, move)) {
+                    // a row's reference moved: rescale O, at rest once P V of the previous tile is done
+                    if (!mbar_wait(pv_done(buf ^ 1), ((g - 1u) >> 1) & 1u, abort_flag, p.status, 34)) { ok = false; break; }
                     tc_fence_after();
-                    if (__any_sync(0xffffffffu, move)) {
 #pragma unroll 1
-                        for (int c = 0; c < D / 2; c += 32) {
-                            uint32_t o[32];
-                            const uint32_t ocol = lane_addr + (uint32_t)(FA_O_COL + h * (D / 2) + c);
-                            tc_ld32(ocol, o);
+                    for (int c = 0; c < D / 2; c += 32) {
+                        const uint32_t ocol = lane_addr + (uint32_t)(FA_O_COL + h * (D / 2) + c);
+                        tc_ld32(ocol, ra);
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-                            tc_st32(ocol, o);
-                        }
-                        tc_wait_st();
+                        for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * f);
+                        tc_st32(ocol, ra);
                     }
                 }
-                // probabilities of this row, columns [64 h, 64 h + 64): chunk c of the 128-byte row at c ^ (row & 7)
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    fa_sts_v4(my_p + (((uint32_t)c ^ sw7) << 4), ra[4 * c], ra[4 * c + 1], ra[4 * c + 2], ra[4 * c + 3]);
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    fa_sts_v4(my_p + (((uint32_t)(4 + c) ^ sw7) << 4), rb[4 * c], rb[4 * c + 1], rb[4 * c + 2], rb[4 * c + 3]);
+                if (warp == 2 && lane == 0) FA_STAMP(0, g, 5);
+                tc_fence_after();
+                // probabilities of this row, key columns [64 h, 64 h + 64): 32 columns of the tile's P buffer
+                tc_st32(lane_addr + (uint32_t)(FA_P_COL + 64 * buf + 32 * h), pk);
+                tc_wait_st();
                 if (ncols & 15) {
                     // last tile of the segment: clear the value rows between its end and the next multiple of 16
                     if (!mbar_wait(v_full(stage), (g / ST) & 1u, abort_flag, p.status, 32)) { ok = false; break; }
@@ -383,50 +401,35 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                         const int rr = t / (L::NB * 8), rem = t % (L::NB * 8);
                         fa_sts_v4(sV(stage) + (rem >> 3) * FA_BLOCK_BYTES + (ncols + rr) * 128 + (rem & 7) * 16, 0u, 0u, 0u, 0u);
                     }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy writes before the MMA's reads
                 }
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy writes before the MMA's reads
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(p_full);
+                if (lane == 0) mbar_arrive(p_full(buf));
+                if (warp == 2 && lane == 0) FA_STAMP(0, g, 6);
             }
             if (!ok) break;
             // ---- result rows of the item ----
-            if (!mbar_wait(pv_done, (g - 1u) & 1u, abort_flag, p.status, 33)) break;
+            if (!mbar_wait(pv_done((int)((g - 1u) & 1u)), ((g - 1u) >> 1) & 1u, abort_flag, p.status, 33)) break;
             tc_fence_after();
             float other;
             if (!exchange(l_run, other)) break;
             const float inv = __frcp_rn(l_run + other);
-            // this warp's 32 rows x D/2 columns go through its own part of the P buffer (rows of 128 bytes)
-            const uint32_t region = sP + h * FA_BLOCK_BYTES + (q * 32) * 128;
-            constexpr int HB = D;        // bytes of half a result row
-            constexpr int LPR = HB / 16;  // lanes per row in the copy-out
-            constexpr int RPP = 32 / LPR;
+            // a thread stores its row's D/2 columns, 64 bytes at a time
+            uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (int64_t)wk.head * p.out_head_stride +
+                             (int64_t)(wk.it.rowQ + row) * p.out_row_stride + h * (D / 2);
 #pragma unroll 1
             for (int c = 0; c < D / 2; c += 32) {
                 tc_ld32(lane_addr + (uint32_t)(FA_O_COL + h * (D / 2) + c), ra);
 #pragma unroll
                 for (int i = 0; i < 32; i += 2)
                     ra[i >> 1] = BlkCvt<Tag>::pack2(__uint_as_float(ra[i]) * inv, __uint_as_float(ra[i + 1]) * inv);
+                if (row < wk.it.M) {
+                    uint4* dst = reinterpret_cast<uint4*>(orow + c);
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc)
-                    fa_sts_v4(region + lane * 128 + (((uint32_t)(c / 8 + cc) ^ (uint32_t)(lane & 7)) << 4), ra[4 * cc],
-                              ra[4 * cc + 1], ra[4 * cc + 2], ra[4 * cc + 3]);
-            }
-            tc_fence_before();
-            __syncwarp();
-            {
-                const int cc = lane % LPR;
-                uint16_t* out = reinterpret_cast<uint16_t*>(p.out) + (int64_t)wk.head * p.out_head_stride + h * (D / 2) + cc * 8;
-#pragma unroll
-                for (int r0 = 0; r0 < 32; r0 += RPP) {
-                    const int rr = r0 + lane / LPR;
-                    const uint4 v = fa_lds_v4(region + rr * 128 + (((uint32_t)cc ^ (uint32_t)(rr & 7)) << 4));
-                    const int grow = q * 32 + rr;
-                    if (grow < wk.it.M)
-                        *reinterpret_cast<uint4*>(out + (int64_t)(wk.it.rowQ + grow) * p.out_row_stride) = v;
+                    for (int cc = 0; cc < 4; ++cc) dst[cc] = make_uint4(ra[4 * cc], ra[4 * cc + 1], ra[4 * cc + 2], ra[4 * cc + 3]);
                 }
             }
-            __syncwarp();
         }
     }
 
