@@ -42,32 +42,31 @@
 
 namespace {
 
-#ifdef FA_X_NOEXP
-#define blk_exp2(x) (x)
-#endif
-
 constexpr int FA_BM = BLK_FLASH_BM;  // query rows per work item
 constexpr int FA_BN = 128;           // key / value rows per tile
 constexpr int FA_SOFT_WARPS = 8;
-constexpr int FA_THREADS = 64 + 32 * FA_SOFT_WARPS;
+constexpr int FA_OUT_WARPS = 4;
+constexpr int FA_THREADS = 64 + 32 * (FA_SOFT_WARPS + FA_OUT_WARPS);
 constexpr int FA_BLOCK_BYTES = 128 * 128;  // 128 rows of one 64-column block: 16 KB
-constexpr int FA_O_COL = 256;              // tensor-memory column of the O accumulator
-constexpr int FA_P_COL = 384;              // two buffers of 64 columns: the probabilities of a tile, two per column
+constexpr int FA_O_COL = 256;              // tensor-memory columns of the two result accumulators: 256 and 384
 constexpr float FA_LAZY = 8.f;             // exponent slack before the running maximum moves
 
 template <int D>
 struct FL {
     static constexpr int NB = D / 64;                       // 64-column blocks of an operand row
-    static constexpr int STAGES = D == 64 ? 6 : 3;          // key/value ring
+    static constexpr int KS = D == 64 ? 5 : 3;              // key ring
+    static constexpr int VS = D == 64 ? 5 : 2;              // value ring
     static constexpr int OPER_BYTES = NB * FA_BLOCK_BYTES;  // a 128 x D tile
     static constexpr int Q_OFF = 0;
-    static constexpr int KV_OFF = OPER_BYTES;
-    static constexpr int STAGE_BYTES = 2 * OPER_BYTES;      // key tile, then value tile
-    static constexpr int XCH_OFF = KV_OFF + STAGES * STAGE_BYTES;
-    static constexpr int XCH_BYTES = 2 * 2 * 128 * 4;       // [exchange parity][half][row]
-    static constexpr int BAR_OFF = XCH_OFF + XCH_BYTES;
+    static constexpr int K_OFF = OPER_BYTES;
+    static constexpr int V_OFF = K_OFF + KS * OPER_BYTES;
+    static constexpr int XCH_OFF = V_OFF + VS * OPER_BYTES;
+    static constexpr int XCH_BYTES = 2 * 2 * 128 * 4;       // row maxima: [exchange parity][half][row]
+    static constexpr int LSUM_OFF = XCH_OFF + XCH_BYTES;
+    static constexpr int LSUM_BYTES = 2 * 2 * 128 * 4;      // row sums for the output warps: [result buffer][half][row]
+    static constexpr int BAR_OFF = LSUM_OFF + LSUM_BYTES;
     static constexpr int SMEM_BYTES = BAR_OFF + 512;
-    static_assert(STAGES <= 6, "barrier slots");
+    static_assert(KS <= 6 && VS <= 6, "barrier slots");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
@@ -115,7 +114,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap mapQ,
                      const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
     using L = FL<D>;
-    constexpr int ST = L::STAGES;
+    constexpr int KS = L::KS, VS = L::VS;
     extern __shared__ __align__(1024) unsigned char fa_smem_raw[];
     unsigned char* smem = fa_smem_raw;
     if (blk_smem_u32(smem) & 1023u) {  // the swizzled tiles rely on a 1024-byte aligned base
@@ -123,11 +122,13 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
         return;
     }
     float* xch = reinterpret_cast<float*>(smem + L::XCH_OFF);
+    float* lsum = reinterpret_cast<float*>(smem + L::LSUM_OFF);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
-    // barriers: 0 q_full, 1 q_empty, 2.. p_full[2], 4.. pv_done[2], 6.. s_full[2], 8.. s_empty[2], 10.. one per
-    // accumulator-lane quarter, on which its two softmax warps meet, 14.. k_full[ST], 20.. v_full[ST], 26.. kv_empty[ST]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 33);
+    // barriers: 0 q_full, 1 q_empty, 2.. p_full[2], 4.. pv_done[2], 6.. s_full[2], 8.. o_ready[2], 10.. o_free[2],
+    // 12.. l_ready[2], 14.. one per accumulator-lane quarter, on which its two softmax warps meet, 18.. k_full[KS],
+    // 24.. k_empty[KS], 30.. v_full[VS], 36.. v_empty[VS]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 42);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 43);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef FA_TRACE
@@ -142,13 +143,16 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
     auto p_full = [&](int b) { return bar0 + 8u * (2 + b); };
     auto pv_done = [&](int b) { return bar0 + 8u * (4 + b); };
     auto s_full = [&](int b) { return bar0 + 8u * (6 + b); };
-    auto s_empty = [&](int b) { return bar0 + 8u * (8 + b); };
-    auto k_full = [&](int s) { return bar0 + 8u * (14 + s); };
-    auto v_full = [&](int s) { return bar0 + 8u * (20 + s); };
-    auto kv_empty = [&](int s) { return bar0 + 8u * (26 + s); };
+    auto o_ready = [&](int b) { return bar0 + 8u * (8 + b); };
+    auto o_free = [&](int b) { return bar0 + 8u * (10 + b); };
+    auto l_ready = [&](int b) { return bar0 + 8u * (12 + b); };
+    auto k_full = [&](int s) { return bar0 + 8u * (18 + s); };
+    auto k_empty = [&](int s) { return bar0 + 8u * (24 + s); };
+    auto v_full = [&](int s) { return bar0 + 8u * (30 + s); };
+    auto v_empty = [&](int s) { return bar0 + 8u * (36 + s); };
     const uint32_t sQ = smem_u32 + L::Q_OFF;
-    auto sK = [&](int s) { return smem_u32 + L::KV_OFF + s * L::STAGE_BYTES; };
-    auto sV = [&](int s) { return smem_u32 + L::KV_OFF + s * L::STAGE_BYTES + L::OPER_BYTES; };
+    auto sK = [&](int s) { return smem_u32 + L::K_OFF + s * L::OPER_BYTES; };
+    auto sV = [&](int s) { return smem_u32 + L::V_OFF + s * L::OPER_BYTES; };
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -157,14 +161,19 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             mbar_init(p_full(b), FA_SOFT_WARPS);
             mbar_init(pv_done(b), 1);
             mbar_init(s_full(b), 1);
-            mbar_init(s_empty(b), FA_SOFT_WARPS);
+            mbar_init(o_ready(b), 1);
+            mbar_init(o_free(b), FA_OUT_WARPS);
+            mbar_init(l_ready(b), FA_SOFT_WARPS);
         }
-        for (int s = 0; s < ST; ++s) {
+        for (int i = 0; i < 4; ++i) mbar_init(bar0 + 8u * (14 + i), 2);
+        for (int s = 0; s < KS; ++s) {
             mbar_init(k_full(s), 1);
-            mbar_init(v_full(s), 1);
-            mbar_init(kv_empty(s), 1);
+            mbar_init(k_empty(s), 1);
         }
-        for (int i = 0; i < 4; ++i) mbar_init(bar0 + 8u * (10 + i), 2);
+        for (int s = 0; s < VS; ++s) {
+            mbar_init(v_full(s), 1);
+            mbar_init(v_empty(s), 1);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -194,12 +203,13 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 if (!mbar_wait(q_empty, (itc & 1u) ^ 1u, abort_flag, p.status, 21)) break;
                 load_tile(sQ, &mapQ, q_full, wk.it.rowQ, wk.head, p.head_firstQ);
                 for (int j = 0; j < wk.T; ++j, ++g) {
-                    const int stage = (int)(g % ST);
+                    const int ks = (int)(g % KS), vs = (int)(g % VS);
                     FA_STAMP(2, g, 0);
-                    if (!mbar_wait(kv_empty(stage), ((g / ST) & 1u) ^ 1u, abort_flag, p.status, 22)) { ok = false; break; }
+                    if (!mbar_wait(k_empty(ks), ((g / KS) & 1u) ^ 1u, abort_flag, p.status, 22)) { ok = false; break; }
+                    load_tile(sK(ks), &mapK, k_full(ks), wk.it.rowKV + j * FA_BN, wk.head, p.head_firstK);
+                    if (!mbar_wait(v_empty(vs), ((g / VS) & 1u) ^ 1u, abort_flag, p.status, 20)) { ok = false; break; }
                     FA_STAMP(2, g, 1);
-                    load_tile(sK(stage), &mapK, k_full(stage), wk.it.rowKV + j * FA_BN, wk.head, p.head_firstK);
-                    load_tile(sV(stage), &mapV, v_full(stage), wk.it.rowKV + j * FA_BN, wk.head, p.head_firstV);
+                    load_tile(sV(vs), &mapV, v_full(vs), wk.it.rowKV + j * FA_BN, wk.head, p.head_firstV);
                 }
             }
         }
@@ -224,44 +234,49 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             const int neg = p.scale < 0.f;
             const uint32_t idesc_pv = instr_desc(p.bf16, D, 0, 1);
             bool ok = true;
+            // S = Q K^T of tile c.g into score buffer g & 1.  The buffer is free: its previous user, tile g - 2, was
+            // read by all softmax warps before P V of that tile (issued earlier, executed in order) read the
+            // probabilities that overlay it.
             auto issue_qk = [&](const Cur& c) {
-                const int stage = (int)(c.g % ST), buf = (int)(c.g & 1u);
+                const int ks = (int)(c.g % KS), buf = (int)(c.g & 1u);
                 FA_STAMP(1, c.g, 0);
                 if (c.j == 0 && !mbar_wait(q_full, c.itc & 1u, abort_flag, p.status, 23)) { ok = false; return; }
-                if (!mbar_wait(k_full(stage), (c.g / ST) & 1u, abort_flag, p.status, 24)) { ok = false; return; }
-                FA_STAMP(1, c.g, 4);
-                if (!mbar_wait(s_empty(buf), ((c.g >> 1) & 1u) ^ 1u, abort_flag, p.status, 25)) { ok = false; return; }
+                if (!mbar_wait(k_full(ks), (c.g / KS) & 1u, abort_flag, p.status, 24)) { ok = false; return; }
                 FA_STAMP(1, c.g, 1);
                 tc_fence_after();
                 const int ncols = min(c.wk.it.N - c.j * FA_BN, FA_BN);
                 const uint32_t idesc = instr_desc(p.bf16, (ncols + 15) & ~15, neg);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * FA_BN);
-                const uint32_t a0 = sQ, b0 = sK(stage);
+                const uint32_t a0 = sQ, b0 = sK(ks);
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
                     const uint32_t o = (uint32_t)((k >> 2) * FA_BLOCK_BYTES + 32 * (k & 3));
                     tc_mma_f16(d_tmem, smem_desc_sw128(a0 + o), smem_desc_sw128(b0 + o), idesc, k != 0);
                 }
                 tc_commit(s_full(buf));
+                tc_commit(k_empty(ks));                     // key tile reusable
                 if (c.j == c.wk.T - 1) tc_commit(q_empty);  // the query block is free once these products have read it
             };
+            // O[item & 1] += P V of tile c.g; P sits in the first 64 columns of the tile's score buffer
             auto issue_pv = [&](const Cur& c) {
-                const int stage = (int)(c.g % ST);
+                const int vs = (int)(c.g % VS), buf = (int)(c.g & 1u), ob = (int)(c.itc & 1u);
                 FA_STAMP(1, c.g, 2);
-                if (!mbar_wait(p_full((int)(c.g & 1u)), (c.g >> 1) & 1u, abort_flag, p.status, 26)) { ok = false; return; }
-                if (!mbar_wait(v_full(stage), (c.g / ST) & 1u, abort_flag, p.status, 27)) { ok = false; return; }
+                if (c.j == 0 && !mbar_wait(o_free(ob), ((c.itc >> 1) & 1u) ^ 1u, abort_flag, p.status, 19)) { ok = false; return; }
+                if (!mbar_wait(p_full(buf), (c.g >> 1) & 1u, abort_flag, p.status, 26)) { ok = false; return; }
+                if (!mbar_wait(v_full(vs), (c.g / VS) & 1u, abort_flag, p.status, 27)) { ok = false; return; }
                 FA_STAMP(1, c.g, 3);
                 tc_fence_after();
                 const int ncols = min(c.wk.it.N - c.j * FA_BN, FA_BN);
                 const int ksteps = (ncols + 15) >> 4;
-                const uint32_t d_tmem = tmem_base + FA_O_COL;
-                const uint32_t b0 = sV(stage);
-                const uint32_t a_tmem = tmem_base + (uint32_t)(FA_P_COL + 64 * (int)(c.g & 1u));
+                const uint32_t d_tmem = tmem_base + (uint32_t)(FA_O_COL + 128 * ob);
+                const uint32_t a_tmem = tmem_base + (uint32_t)(buf * FA_BN);
+                const uint32_t b0 = sV(vs);
                 for (int k = 0; k < ksteps; ++k)  // 16 probabilities of a row are 8 columns
                     fa_mma_f16_ts(d_tmem, a_tmem + 8u * k, smem_desc_sw128_mn(b0 + 2048u * k, FA_BLOCK_BYTES), idesc_pv,
                                   (c.j | k) != 0);
-                tc_commit(kv_empty(stage));             // key and value tile reusable
-                tc_commit(pv_done((int)(c.g & 1u)));  // this P buffer reusable, O up to date
+                tc_commit(v_empty(vs));                             // value tile reusable
+                tc_commit(pv_done(buf));                            // O at rest until the next P V
+                if (c.j == c.wk.T - 1) tc_commit(o_ready(ob));     // the item's result is complete
             };
             Cur a, b;
             a.w = b.w = blockIdx.x;
@@ -282,13 +297,13 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 advance(b);
             }
         }
-    } else {
-        // ---------------- softmax and output: warps 2..9 ----------------
+    } else if (warp < 2 + FA_SOFT_WARPS) {
+        // ---------------- softmax: warps 2..9 ----------------
         const int q = warp & 3, h = (warp - 2) >> 2;
         const int row = q * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         const float sl = fabsf(p.scale) * BLK_LOG2E;  // a negative scale is applied by the MMA (negated Q)
-        const uint32_t pair_bar = bar0 + 8u * (10 + q);
+        const uint32_t pair_bar = bar0 + 8u * (14 + q);
         uint32_t xc = 0;
         // value a of this row to the partner warp, the partner's value back
         auto exchange = [&](float a, float& other) -> bool {
@@ -301,14 +316,15 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             if (good) other = x[(h ^ 1) * 128 + row];
             return good;
         };
-        uint32_t g = 0;
+        uint32_t g = 0, itc = 0;
         FaWork wk;
         bool ok = true;
         uint32_t ra[32], rb[32];
-        for (uint32_t w = blockIdx.x; ok && fa_work(p, w, wk); w += gridDim.x) {
+        for (uint32_t w = blockIdx.x; ok && fa_work(p, w, wk); w += gridDim.x, ++itc) {
+            const int ob = (int)(itc & 1u);
             float m_run = -INFINITY, l_run = 0.f;
             for (int j = 0; ok && j < wk.T; ++j, ++g) {
-                const int buf = (int)(g & 1u), stage = (int)(g % ST);
+                const int buf = (int)(g & 1u), vs = (int)(g % VS);
                 if (warp == 2 && lane == 0) FA_STAMP(0, g, 0);
                 if (!mbar_wait(s_full(buf), (g >> 1) & 1u, abort_flag, p.status, 30)) { ok = false; break; }
                 if (warp == 2 && lane == 0) FA_STAMP(0, g, 1);
@@ -317,9 +333,6 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 fa_ld32_nowait(scol, ra);
                 fa_ld32_nowait(scol + 32, rb);
                 fa_ld_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(s_empty(buf));  // the scores are in registers
                 const int ncols = min(wk.it.N - j * FA_BN, FA_BN);
                 const int lim = ncols - 64 * h;  // valid columns of this half
                 if (lim < 64) {
@@ -336,13 +349,11 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                     pm = fmaxf(pm, fmaxf(__uint_as_float(ra[i]), __uint_as_float(ra[i + 1])));
                     pm = fmaxf(pm, fmaxf(__uint_as_float(rb[i]), __uint_as_float(rb[i + 1])));
                 }
+                // after this rendezvous both warps of the quarter have their scores in registers, so the
+                // probabilities may overwrite the first 64 columns of the score buffer
                 float other;
-#ifndef FA_X_NOEXCH
                 if (!exchange(pm, other)) { ok = false; break; }
                 pm = fmaxf(pm, other);
-#else
-                other = pm;
-#endif
                 if (warp == 2 && lane == 0) FA_STAMP(0, g, 3);
                 const float m_new = fmaxf(m_run, pm);
                 const bool move = (m_new - m_run) * sl > FA_LAZY;  // always at the first tile (m_run = -inf)
@@ -372,7 +383,8 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 }
                 l_run = l_run * f + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
                 if (warp == 2 && lane == 0) FA_STAMP(0, g, 4);
-                // this tile's P buffer was last read by P V of tile g - 2
+                // P V of tile g - 2 (long done: the scores of tile g were computed after it); waited for on every
+                // tile so that each warp sees the phases of these two barriers in order
                 if (g >= 2u && !mbar_wait(pv_done(buf), ((g >> 1) - 1u) & 1u, abort_flag, p.status, 31)) { ok = false; break; }
                 if (j > 0 && __any_sync(0xffffffffu, move)) {
                     // a row's reference moved: rescale O, at rest once P V of the previous tile is done
@@ -380,7 +392,7 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                     tc_fence_after();
 #pragma unroll 1
                     for (int c = 0; c < D / 2; c += 32) {
-                        const uint32_t ocol = lane_addr + (uint32_t)(FA_O_COL + h * (D / 2) + c);
+                        const uint32_t ocol = lane_addr + (uint32_t)(FA_O_COL + 128 * ob + h * (D / 2) + c);
                         tc_ld32(ocol, ra);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * f);
@@ -388,18 +400,17 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                     }
                 }
                 if (warp == 2 && lane == 0) FA_STAMP(0, g, 5);
-                tc_fence_after();
-                // probabilities of this row, key columns [64 h, 64 h + 64): 32 columns of the tile's P buffer
-                tc_st32(lane_addr + (uint32_t)(FA_P_COL + 64 * buf + 32 * h), pk);
+                // probabilities of this row, key columns [64 h, 64 h + 64): columns [32 h, 32 h + 32) of the score buffer
+                tc_st32(lane_addr + (uint32_t)(buf * FA_BN + 32 * h), pk);
                 tc_wait_st();
                 if (ncols & 15) {
                     // last tile of the segment: clear the value rows between its end and the next multiple of 16
-                    if (!mbar_wait(v_full(stage), (g / ST) & 1u, abort_flag, p.status, 32)) { ok = false; break; }
+                    if (!mbar_wait(v_full(vs), (g / VS) & 1u, abort_flag, p.status, 32)) { ok = false; break; }
                     const int nz = (16 - (ncols & 15)) * L::NB * 8;  // 16-byte pieces to clear
                     const int t = (warp - 2) * 32 + lane;
                     if (t < nz) {
                         const int rr = t / (L::NB * 8), rem = t % (L::NB * 8);
-                        fa_sts_v4(sV(stage) + (rem >> 3) * FA_BLOCK_BYTES + (ncols + rr) * 128 + (rem & 7) * 16, 0u, 0u, 0u, 0u);
+                        fa_sts_v4(sV(vs) + (rem >> 3) * FA_BLOCK_BYTES + (ncols + rr) * 128 + (rem & 7) * 16, 0u, 0u, 0u, 0u);
                     }
                     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy writes before the MMA's reads
                 }
@@ -409,27 +420,45 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 if (warp == 2 && lane == 0) FA_STAMP(0, g, 6);
             }
             if (!ok) break;
-            // ---- result rows of the item ----
-            if (!mbar_wait(pv_done((int)((g - 1u) & 1u)), ((g - 1u) >> 1) & 1u, abort_flag, p.status, 33)) break;
+            // row sums to the output warps; the slot is free once they have stored the item two before this one
+            if (!mbar_wait(o_free(ob), ((itc >> 1) & 1u) ^ 1u, abort_flag, p.status, 33)) break;
+            lsum[(ob * 2 + h) * 128 + row] = l_run;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(l_ready(ob));
+        }
+    } else {
+        // ---------------- output: warps 10..13 ----------------
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        uint32_t itc = 0;
+        FaWork wk;
+        uint32_t r[32];
+        for (uint32_t w = blockIdx.x; fa_work(p, w, wk); w += gridDim.x, ++itc) {
+            const int ob = (int)(itc & 1u);
+            const uint32_t par = (itc >> 1) & 1u;
+            if (!mbar_wait(l_ready(ob), par, abort_flag, p.status, 35)) break;
+            if (!mbar_wait(o_ready(ob), par, abort_flag, p.status, 36)) break;
             tc_fence_after();
-            float other;
-            if (!exchange(l_run, other)) break;
-            const float inv = __frcp_rn(l_run + other);
-            // a thread stores its row's D/2 columns, 64 bytes at a time
+            const float inv = __frcp_rn(lsum[(ob * 2) * 128 + row] + lsum[(ob * 2 + 1) * 128 + row]);
+            // a thread stores its row, 64 bytes at a time
             uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (int64_t)wk.head * p.out_head_stride +
-                             (int64_t)(wk.it.rowQ + row) * p.out_row_stride + h * (D / 2);
+                             (int64_t)(wk.it.rowQ + row) * p.out_row_stride;
 #pragma unroll 1
-            for (int c = 0; c < D / 2; c += 32) {
-                tc_ld32(lane_addr + (uint32_t)(FA_O_COL + h * (D / 2) + c), ra);
+            for (int c = 0; c < D; c += 32) {
+                tc_ld32(lane_addr + (uint32_t)(FA_O_COL + 128 * ob + c), r);
 #pragma unroll
                 for (int i = 0; i < 32; i += 2)
-                    ra[i >> 1] = BlkCvt<Tag>::pack2(__uint_as_float(ra[i]) * inv, __uint_as_float(ra[i + 1]) * inv);
+                    r[i >> 1] = BlkCvt<Tag>::pack2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
                 if (row < wk.it.M) {
                     uint4* dst = reinterpret_cast<uint4*>(orow + c);
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) dst[cc] = make_uint4(ra[4 * cc], ra[4 * cc + 1], ra[4 * cc + 2], ra[4 * cc + 3]);
+                    for (int cc = 0; cc < 4; ++cc) dst[cc] = make_uint4(r[4 * cc], r[4 * cc + 1], r[4 * cc + 2], r[4 * cc + 3]);
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(o_free(ob));  // result buffer and row-sum slot reusable
         }
     }
 
