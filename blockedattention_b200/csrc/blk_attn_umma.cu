@@ -2,26 +2,31 @@
 // out_s = softmax(scale * Q_s K_s^T) V_s per segment and head, head dimension 64 or
 // 128, without the probabilities ever leaving the SM.
 //
-// A persistent CTA (one per SM, 10 warps) walks a static list of work items, an item
+// A persistent CTA (one per SM, 14 warps) walks a static list of work items, an item
 // being a 128-row block of the queries of one segment of one head; it sweeps the
 // segment's keys and values in tiles of 128 rows.  Roles:
-//   warp 0    producer: one lane issues tiled TMA loads (128-byte swizzle) of the query
-//             block and, into a ring of stages, of each key tile and value tile;
-//   warp 1    MMA: one lane issues tcgen05.mma.  S = Q K^T (both operands K-major)
-//             goes to one of two 128-column accumulators in tensor memory; O += P V
-//             (P K-major from shared memory, V as loaded, i.e. MN-major) accumulates
-//             in a third region.  The products of tile g+1 are issued before P V of
-//             tile g, across item boundaries, so the tensor pipe works while the
-//             softmax warps are busy with tile g;
-//   warps 2-9 softmax: thread (quarter q, lane) owns row 32 q + lane of the block; the
-//             two warps of a quarter each take 64 of the 128 columns of a tile and
-//             exchange row maxima through shared memory.  Online softmax with a lazy
-//             reference: the running row maximum is only moved (and O rescaled in
-//             tensor memory) when the new maximum exceeds it by more than 8 in the
-//             exponent, so P <= 2^8 and the rescale is rare.  P is rounded to the
-//             input type and written to shared memory in the swizzled K-major layout
-//             the MMA reads.  After the last tile the warps read O, divide by the row
-//             sum and copy the rows out through their part of the P buffer.
+//   warp 0      producer: one lane issues tiled TMA loads (128-byte swizzle) of the query
+//               block and, into two rings of stages, of the key tiles and value tiles;
+//   warp 1      MMA: one lane issues tcgen05.mma.  S = Q K^T (both operands K-major from
+//               shared memory) goes to one of two 128-column score buffers in tensor
+//               memory; O += P V takes P from tensor memory (first operand [tmem], two
+//               16-bit elements per column, row = lane) and V from shared memory as
+//               loaded, i.e. MN-major, and accumulates in one of two result buffers
+//               (items alternate).  The products of tile g+1 are issued before P V of
+//               tile g, across item boundaries, so the tensor pipe has work while the
+//               softmax warps are busy with tile g;
+//   warps 2-9   softmax: thread (quarter q, lane) owns row 32 q + lane of the block; the
+//               two warps of a quarter each take 64 of the 128 columns of a tile and meet
+//               on an mbarrier to exchange row maxima.  Online softmax with a lazy
+//               reference: the running row maximum is only moved (and O rescaled in
+//               tensor memory) when the new maximum exceeds it by more than 8 in the
+//               exponent, so P <= 2^8 and the rescale is rare.  P, rounded to the input
+//               type, overwrites the first 64 columns of the tile's score buffer (Q K^T
+//               of tile g+2 is issued after P V of tile g and overwrites it in pipe
+//               order).  After an item's last tile the warps leave the row sums in shared
+//               memory and go on to the next item;
+//   warps 10-13 output: wait for the item's last P V and the row sums, read O, divide and
+//               store the rows, then hand the result buffer back.
 //
 // Rows of the tiles past the end of a segment belong to its neighbour (or are zero
 // past the end of the buffer): extra query rows are never stored, extra key columns
@@ -55,7 +60,7 @@ template <int D>
 struct FL {
     static constexpr int NB = D / 64;                       // 64-column blocks of an operand row
     static constexpr int KS = D == 64 ? 5 : 3;              // key ring
-    static constexpr int VS = D == 64 ? 5 : 2;              // value ring
+    static constexpr int VS = D == 64 ? 5 : 2;              // value ring (a deeper one measured slower)
     static constexpr int OPER_BYTES = NB * FA_BLOCK_BYTES;  // a 128 x D tile
     static constexpr int Q_OFF = 0;
     static constexpr int K_OFF = OPER_BYTES;
@@ -131,12 +136,6 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 43);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef FA_TRACE
-    long long* fa_tr = reinterpret_cast<long long*>(reinterpret_cast<char*>(p.out) + (int64_t)p.H * p.out_head_stride * 2);
-#define FA_STAMP(role, g, k) do { if (blockIdx.x == 0 && (g) < 64u) fa_tr[((role) * 64 + (g)) * 8 + (k)] = clock64(); } while (0)
-#else
-#define FA_STAMP(role, g, k) do {} while (0)
-#endif
     const uint32_t smem_u32 = blk_smem_u32(smem);
     const uint32_t bar0 = blk_smem_u32(bars);
     const uint32_t q_full = bar0, q_empty = bar0 + 8;
@@ -204,11 +203,9 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 load_tile(sQ, &mapQ, q_full, wk.it.rowQ, wk.head, p.head_firstQ);
                 for (int j = 0; j < wk.T; ++j, ++g) {
                     const int ks = (int)(g % KS), vs = (int)(g % VS);
-                    FA_STAMP(2, g, 0);
                     if (!mbar_wait(k_empty(ks), ((g / KS) & 1u) ^ 1u, abort_flag, p.status, 22)) { ok = false; break; }
                     load_tile(sK(ks), &mapK, k_full(ks), wk.it.rowKV + j * FA_BN, wk.head, p.head_firstK);
                     if (!mbar_wait(v_empty(vs), ((g / VS) & 1u) ^ 1u, abort_flag, p.status, 20)) { ok = false; break; }
-                    FA_STAMP(2, g, 1);
                     load_tile(sV(vs), &mapV, v_full(vs), wk.it.rowKV + j * FA_BN, wk.head, p.head_firstV);
                 }
             }
@@ -233,25 +230,26 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             };
             const int neg = p.scale < 0.f;
             const uint32_t idesc_pv = instr_desc(p.bf16, D, 0, 1);
+            const uint64_t desc_q = smem_desc_sw128(sQ);
             bool ok = true;
             // S = Q K^T of tile c.g into score buffer g & 1.  The buffer is free: its previous user, tile g - 2, was
             // read by all softmax warps before P V of that tile (issued earlier, executed in order) read the
             // probabilities that overlay it.
             auto issue_qk = [&](const Cur& c) {
                 const int ks = (int)(c.g % KS), buf = (int)(c.g & 1u);
-                FA_STAMP(1, c.g, 0);
                 if (c.j == 0 && !mbar_wait(q_full, c.itc & 1u, abort_flag, p.status, 23)) { ok = false; return; }
                 if (!mbar_wait(k_full(ks), (c.g / KS) & 1u, abort_flag, p.status, 24)) { ok = false; return; }
-                FA_STAMP(1, c.g, 1);
                 tc_fence_after();
                 const int ncols = min(c.wk.it.N - c.j * FA_BN, FA_BN);
                 const uint32_t idesc = instr_desc(p.bf16, (ncols + 15) & ~15, neg);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * FA_BN);
-                const uint32_t a0 = sQ, b0 = sK(ks);
+                // descriptors of the k-th step: the start-address field (16-byte units) moves by 2 per 32 bytes
+                // inside a 64-column block and by 1024 per block
+                const uint64_t da0 = desc_q, db0 = smem_desc_sw128(sK(ks));
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
-                    const uint32_t o = (uint32_t)((k >> 2) * FA_BLOCK_BYTES + 32 * (k & 3));
-                    tc_mma_f16(d_tmem, smem_desc_sw128(a0 + o), smem_desc_sw128(b0 + o), idesc, k != 0);
+                    const uint64_t o = (uint64_t)((k >> 2) * (FA_BLOCK_BYTES >> 4) + 2 * (k & 3));
+                    tc_mma_f16(d_tmem, da0 + o, db0 + o, idesc, k != 0);
                 }
                 tc_commit(s_full(buf));
                 tc_commit(k_empty(ks));                     // key tile reusable
@@ -260,20 +258,19 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             // O[item & 1] += P V of tile c.g; P sits in the first 64 columns of the tile's score buffer
             auto issue_pv = [&](const Cur& c) {
                 const int vs = (int)(c.g % VS), buf = (int)(c.g & 1u), ob = (int)(c.itc & 1u);
-                FA_STAMP(1, c.g, 2);
                 if (c.j == 0 && !mbar_wait(o_free(ob), ((c.itc >> 1) & 1u) ^ 1u, abort_flag, p.status, 19)) { ok = false; return; }
                 if (!mbar_wait(p_full(buf), (c.g >> 1) & 1u, abort_flag, p.status, 26)) { ok = false; return; }
                 if (!mbar_wait(v_full(vs), (c.g / VS) & 1u, abort_flag, p.status, 27)) { ok = false; return; }
-                FA_STAMP(1, c.g, 3);
                 tc_fence_after();
                 const int ncols = min(c.wk.it.N - c.j * FA_BN, FA_BN);
                 const int ksteps = (ncols + 15) >> 4;
                 const uint32_t d_tmem = tmem_base + (uint32_t)(FA_O_COL + 128 * ob);
                 const uint32_t a_tmem = tmem_base + (uint32_t)(buf * FA_BN);
-                const uint32_t b0 = sV(vs);
-                for (int k = 0; k < ksteps; ++k)  // 16 probabilities of a row are 8 columns
-                    fa_mma_f16_ts(d_tmem, a_tmem + 8u * k, smem_desc_sw128_mn(b0 + 2048u * k, FA_BLOCK_BYTES), idesc_pv,
-                                  (c.j | k) != 0);
+                const uint64_t db0 = smem_desc_sw128_mn(sV(vs), FA_BLOCK_BYTES);
+#pragma unroll
+                for (int k = 0; k < FA_BN / 16; ++k)  // 16 probabilities of a row are 8 columns; 16 value rows are 2048 bytes
+                    if (k < ksteps)
+                        fa_mma_f16_ts(d_tmem, a_tmem + 8u * k, db0 + (uint64_t)(128 * k), idesc_pv, (c.j | k) != 0);
                 tc_commit(v_empty(vs));                             // value tile reusable
                 tc_commit(pv_done(buf));                            // O at rest until the next P V
                 if (c.j == c.wk.T - 1) tc_commit(o_ready(ob));     // the item's result is complete
@@ -325,9 +322,7 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             float m_run = -INFINITY, l_run = 0.f;
             for (int j = 0; ok && j < wk.T; ++j, ++g) {
                 const int buf = (int)(g & 1u), vs = (int)(g % VS);
-                if (warp == 2 && lane == 0) FA_STAMP(0, g, 0);
                 if (!mbar_wait(s_full(buf), (g >> 1) & 1u, abort_flag, p.status, 30)) { ok = false; break; }
-                if (warp == 2 && lane == 0) FA_STAMP(0, g, 1);
                 tc_fence_after();
                 const uint32_t scol = lane_addr + (uint32_t)(buf * FA_BN + 64 * h);
                 fa_ld32_nowait(scol, ra);
@@ -342,7 +337,6 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                         if (32 + i >= lim) rb[i] = 0xff800000u;
                     }
                 }
-                if (warp == 2 && lane == 0) FA_STAMP(0, g, 2);
                 float pm = -INFINITY;
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
@@ -354,7 +348,6 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 float other;
                 if (!exchange(pm, other)) { ok = false; break; }
                 pm = fmaxf(pm, other);
-                if (warp == 2 && lane == 0) FA_STAMP(0, g, 3);
                 const float m_new = fmaxf(m_run, pm);
                 const bool move = (m_new - m_run) * sl > FA_LAZY;  // always at the first tile (m_run = -inf)
                 float f = 1.f;
@@ -382,7 +375,6 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                     pk[16 + (i >> 1)] = BlkCvt<Tag>::pack2(e0, e1);
                 }
                 l_run = l_run * f + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
-                if (warp == 2 && lane == 0) FA_STAMP(0, g, 4);
                 // P V of tile g - 2 (long done: the scores of tile g were computed after it); waited for on every
                 // tile so that each warp sees the phases of these two barriers in order
                 if (g >= 2u && !mbar_wait(pv_done(buf), ((g >> 1) - 1u) & 1u, abort_flag, p.status, 31)) { ok = false; break; }
@@ -399,7 +391,6 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                         tc_st32(ocol, ra);
                     }
                 }
-                if (warp == 2 && lane == 0) FA_STAMP(0, g, 5);
                 // probabilities of this row, key columns [64 h, 64 h + 64): columns [32 h, 32 h + 32) of the score buffer
                 tc_st32(lane_addr + (uint32_t)(buf * FA_BN + 32 * h), pk);
                 tc_wait_st();
@@ -417,7 +408,6 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full(buf));
-                if (warp == 2 && lane == 0) FA_STAMP(0, g, 6);
             }
             if (!ok) break;
             // row sums to the output warps; the slot is free once they have stored the item two before this one
