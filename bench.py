@@ -44,6 +44,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="molecular")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--segments", type=int, default=0,
+                    help="segments per GPU (default: the workload's own count); a smaller batch for profiler captures")
     ap.add_argument("--nbuf", type=int, default=3, help="input/output buffer sets rotated between steps")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -163,7 +165,7 @@ def run_reference(args):
         return 0
     import torch
     from blockedattention_b200.synth import workload
-    w = workload(args.workload, seed=args.seed)
+    w = workload(args.workload, seed=args.seed, segments=args.segments or None)
     threads = os.cpu_count() or 1
     # bounded sample per step: at most 1024 segments or ~2e10 flop of the workload
     budget = 2e10
@@ -216,8 +218,8 @@ def main():
     peaks = load_peaks()
 
     # ---- workload and this rank's shard -----------------------------------
-    base = workload(args.workload, seed=args.seed)
-    seg_per_gpu = base.S
+    base = workload(args.workload, seed=args.seed, segments=args.segments or None)
+    seg_per_gpu = args.segments or base.S
     wg = workload(args.workload, seed=args.seed, segments=seg_per_gpu * world) if world > 1 else base
     cost = partition.segment_cost(wg.M, wg.N, wg.K, wg.H)
     bounds = partition.partition_contiguous(cost, world)
