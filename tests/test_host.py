@@ -11,7 +11,7 @@ import torch
 from helpers import O, ROOT
 from blockedattention_b200 import _lib as L
 from blockedattention_b200 import partition as P
-from blockedattention_b200.plan import GemmPlan, SoftmaxPlan
+from blockedattention_b200.plan import AttentionPlan, GemmPlan, SoftmaxPlan
 from blockedattention_b200.synth import WORKLOADS, workload
 
 
@@ -87,6 +87,34 @@ def test_softmax_offsets():
 
 
 # ---- scheduler ---------------------------------------------------------------
+def test_attention_schedule_picks_the_kernel_by_batch():
+    # graphs of at most 64 nodes with d = 64: packs of the small-segment kernel, one launch
+    w = workload("molecular_attention")
+    p = AttentionPlan(w.M, w.N, w.H, w.dtype, d=64)
+    s = p.summary
+    assert s["packs"] > 0 and s["umma_items"] == 0 and s["launches"] == 1
+    assert p.work[0] == pytest.approx(w.flops()) and p.work[1] == pytest.approx(w.bytes())
+    # any longer segment, or d = 128: one item per 128-row block of queries on the tcgen05 attention kernel
+    for name in ("long_tail_attention", "full_forward_attention"):
+        w = workload(name)
+        p = AttentionPlan(w.M, w.N, w.H, w.dtype, d=int(w.K[0]))
+        s = p.summary
+        assert s["packs"] == 0 and s["tile_items"] == 0 and s["launches"] == 1
+        assert s["umma_items"] == int(np.ceil(w.M / 128).sum())
+        assert p.work[0] == pytest.approx(w.flops()) and p.work[1] == pytest.approx(w.bytes())
+        assert p.extents[0] == int(w.M.sum()) * int(w.K[0]) and p.extents[2] == p.extents[0]
+    # what neither kernel takes
+    with pytest.raises(RuntimeError):
+        AttentionPlan([4], [4], 1, torch.float16, d=32)
+    with pytest.raises(RuntimeError):
+        AttentionPlan([4], [0], 1, torch.float16, d=64)       # queries without keys
+    with pytest.raises(RuntimeError):
+        AttentionPlan([100], [100], 1, torch.float16, d=64, small_only=True)
+    with pytest.raises(RuntimeError):
+        AttentionPlan([4], [4], 1, torch.float32, d=64)
+    assert AttentionPlan([0, 0], [0, 5], 2, torch.bfloat16, d=128).summary["launches"] == 0
+
+
 def test_schedule_bins_and_work():
     w = workload("molecular")
     p = GemmPlan(w.M, w.N, w.K, w.H, w.dtype, softmax=True)
