@@ -91,29 +91,6 @@ __device__ __forceinline__ bool fa_work(const BlkFlashParams& p, uint32_t w, FaW
     return true;
 }
 
-// tcgen05.ld of 32 columns without the wait (fa_ld_wait() before the registers are read)
-__device__ __forceinline__ void fa_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,"
-        "%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-// D += A B with the first operand in tensor memory (16-bit elements, two per column, row = lane)
-__device__ __forceinline__ void fa_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n .reg .pred q;\n setp.ne.b32 q, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, q;\n}\n"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(db), "r"(idesc), "r"(acc)
-        : "memory");
-}
-__device__ __forceinline__ void fa_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void fa_sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
 template <typename Tag, int D>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap mapQ,
@@ -270,7 +247,7 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
 #pragma unroll
                 for (int k = 0; k < FA_BN / 16; ++k)  // 16 probabilities of a row are 8 columns; 16 value rows are 2048 bytes
                     if (k < ksteps)
-                        fa_mma_f16_ts(d_tmem, a_tmem + 8u * k, db0 + (uint64_t)(128 * k), idesc_pv, (c.j | k) != 0);
+                        tc_mma_f16_ts(d_tmem, a_tmem + 8u * k, db0 + (uint64_t)(128 * k), idesc_pv, (c.j | k) != 0);
                 tc_commit(v_empty(vs));                             // value tile reusable
                 tc_commit(pv_done(buf));                            // O at rest until the next P V
                 if (c.j == c.wk.T - 1) tc_commit(o_ready(ob));     // the item's result is complete
@@ -325,9 +302,9 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 if (!mbar_wait(s_full(buf), (g >> 1) & 1u, abort_flag, p.status, 30)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t scol = lane_addr + (uint32_t)(buf * FA_BN + 64 * h);
-                fa_ld32_nowait(scol, ra);
-                fa_ld32_nowait(scol + 32, rb);
-                fa_ld_wait();
+                tc_ld32_nowait(scol, ra);
+                tc_ld32_nowait(scol + 32, rb);
+                tc_ld_wait();
                 const int ncols = min(wk.it.N - j * FA_BN, FA_BN);
                 const int lim = ncols - 64 * h;  // valid columns of this half
                 if (lim < 64) {
@@ -401,7 +378,7 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                     const int t = (warp - 2) * 32 + lane;
                     if (t < nz) {
                         const int rr = t / (L::NB * 8), rem = t % (L::NB * 8);
-                        fa_sts_v4(sV(vs) + (rem >> 3) * FA_BLOCK_BYTES + (ncols + rr) * 128 + (rem & 7) * 16, 0u, 0u, 0u, 0u);
+                        tc_sts_v4(sV(vs) + (rem >> 3) * FA_BLOCK_BYTES + (ncols + rr) * 128 + (rem & 7) * 16, 0u, 0u, 0u, 0u);
                     }
                     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy writes before the MMA's reads
                 }
