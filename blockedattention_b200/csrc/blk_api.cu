@@ -251,7 +251,7 @@ extern "C" int blk_plan_offsets(const blk_plan_t* p, int64_t* a1, int64_t* a2, i
 }
 
 static int launches_per_run(const blk_plan* p) {
-    if (p->attn == 2) return p->flash_items.empty() ? 0 : 1;
+    if (p->attn) return (p->flash_items.empty() ? 0 : 1) + (p->packs.empty() ? 0 : 1);
     int n = (!p->tile_items.empty()) + (!p->simt_items.empty()) + (!p->umma_items.empty()) + (!p->smx_chunks.empty());
     if (p->small_pipe) return n + 1;
     for (const auto& v : p->small_items) n += !v.empty();
@@ -266,7 +266,7 @@ extern "C" int blk_plan_summary(const blk_plan_t* p, int64_t counts[8]) {
     counts[0] = p->S;
     counts[1] = (int64_t)small_count(p);
     counts[2] = (int64_t)p->tile_items.size();
-    counts[3] = (int64_t)(p->attn == 2 ? p->flash_items.size() : p->umma_items.size());
+    counts[3] = (int64_t)(p->attn ? p->flash_items.size() : p->umma_items.size());
     counts[4] = (int64_t)p->smx_chunks.size();
     counts[5] = p->H > 0 ? launches_per_run(p) : 0;
     counts[6] = (int64_t)p->simt_items.size();
@@ -305,7 +305,7 @@ extern "C" int blk_plan_check(const blk_plan_t* p, void* cuda_stream) {
 
 // Schedule of the tcgen05 attention kernel: one item per 128-row block of the queries of a segment, longest
 // key/value sweeps first (the persistent CTAs take the items round-robin in this order).
-static int build_flash_items(blk_plan* p) {
+static int build_flash_items(blk_plan* p, bool skip_small) {
     const int64_t d = p->head_dim;
     if (p->a1[p->S] / d >= (int64_t)1 << 31 || p->a2[p->S] / d >= (int64_t)1 << 31) {
         blk_set_error("attention plan: more than 2^31 rows");
@@ -314,6 +314,7 @@ static int build_flash_items(blk_plan* p) {
     for (int64_t s = 0; s < p->S; ++s) {
         const int64_t M = p->M[s], N = p->N[s];
         if (M == 0) continue;
+        if (skip_small && M <= BLK_SMALL_MAXM && N <= BLK_SMALL_MAXN) continue;  // in a pack
         for (int64_t tm = 0; tm * BLK_FLASH_BM < M; ++tm)
             p->flash_items.push_back(BlkFlashItem{(int32_t)(p->a1[s] / d + tm * BLK_FLASH_BM), (int32_t)(p->a2[s] / d),
                                                   (int32_t)(M - tm * BLK_FLASH_BM), (int32_t)N});
@@ -383,33 +384,34 @@ static int attention_plan_impl(blk_plan_t** plan, const int64_t* M, const int64_
     size_t nonempty = 0;
     for (int64_t s = 0; s < S; ++s) nonempty += M[s] > 0 && N[s] > 0;
     int rc = BLK_OK;
-    if (small) {
+    // d = 64: the segments of at most 64 x 64 go into packs of the small-segment kernel (the scheduler of the GEMM
+    // bins them; what it schedules for the other segments is of no use here), the rest to the tcgen05 kernel
+    bool packs = false;
+    if (head_dim == 64) {
         rc = blk_build_gemm_schedule(p);
-        const bool packs_only = rc == BLK_OK && (nonempty == 0 || (p->small_pipe && p->tile_items.empty() &&
-                                                                   p->umma_items.empty() && p->simt_items.empty()));
-        if (rc == BLK_OK && !packs_only) {
-            if (any_length) {
-                small = false;  // the pack kernel is switched off: the general kernel takes the batch
-            } else {
-                blk_set_error("blk_attention_plan_create: the pack kernel cannot take this batch (BLK_DISABLE_PIPE or "
-                              "BLK_DISABLE_SMALL set?)");
-                rc = BLK_ERR_UNSUPPORTED;
-            }
+        packs = rc == BLK_OK && p->small_pipe && !p->packs.empty();
+        p->tile_items.clear();
+        p->umma_items.clear();
+        p->simt_items.clear();
+        if (!packs) {
+            p->packs.clear(); p->pack_blocks.clear(); p->small_pipe = 0;
+            for (auto& v : p->small_items) v.clear();
+        }
+        if (rc == BLK_OK && !any_length && nonempty > 0 && !(small && packs)) {
+            blk_set_error("blk_attention_plan_create: the pack kernel cannot take this batch (BLK_DISABLE_PIPE or "
+                          "BLK_DISABLE_SMALL set?)");
+            rc = BLK_ERR_UNSUPPORTED;
         }
     }
-    if (rc == BLK_OK && !small) {
-        // every segment on the tcgen05 attention kernel; none of the GEMM schedules is used
-        p->attn = 2;
-        p->segs.clear(); p->tile_items.clear(); p->umma_items.clear(); p->simt_items.clear();
-        p->packs.clear(); p->pack_blocks.clear(); p->small_pipe = 0;
-        for (auto& v : p->small_items) v.clear();
+    if (rc == BLK_OK && !(small && packs)) {
         p->Dm1 = p->Dout = p->a1[S];
         p->Dm2 = p->a2[S];
-        rc = build_flash_items(p);
+        rc = build_flash_items(p, packs);
         if (rc == BLK_OK && (int64_t)p->flash_items.size() * H >= ((int64_t)1 << 32)) {
             blk_set_error("attention plan: more than 2^32 work items");
             rc = BLK_ERR_UNSUPPORTED;
         }
+        if (!p->flash_items.empty()) p->attn = packs ? 3 : 2;  // 3: packs and tcgen05 items, two launches
     }
     if (rc == BLK_OK) {
         p->flops = p->bytes = 0;
@@ -418,7 +420,7 @@ static int attention_plan_impl(blk_plan_t** plan, const int64_t* M, const int64_
             p->bytes += (double)H * 2.0 * (double)head_dim * (double)(2 * M[s] + 2 * N[s]);
         }
     }
-    if (rc == BLK_OK && p->attn == 1 && !grid_ok((int64_t)p->packs.size(), H, "attention plan")) rc = BLK_ERR_UNSUPPORTED;
+    if (rc == BLK_OK && !p->packs.empty() && !grid_ok((int64_t)p->packs.size(), H, "attention plan")) rc = BLK_ERR_UNSUPPORTED;
     if (rc == BLK_OK) rc = upload_plan(p);
     if (rc != BLK_OK) {
         blk_plan_destroy(p);
@@ -467,7 +469,7 @@ static int attention_run_impl(const blk_plan* p, const void* q, const void* k, c
         blk_set_error("blk_attention_run: the plan was created without a device");
         return BLK_ERR_INVALID;
     }
-    if ((p->attn == 1 ? p->packs.empty() : p->flash_items.empty()) || p->H == 0) return BLK_OK;
+    if ((p->packs.empty() && p->flash_items.empty()) || p->H == 0) return BLK_OK;
     if (!q || !k || !v || !out) {
         blk_set_error("blk_attention_run: null buffer");
         return BLK_ERR_INVALID;
@@ -477,7 +479,7 @@ static int attention_run_impl(const blk_plan* p, const void* q, const void* k, c
         return BLK_ERR_UNALIGNED;
     }
     if (scale == 0.f) scale = 1.17549435e-38f;  // softmax(0 * S) is the uniform distribution
-    if (p->attn == 2) {
+    if (!p->flash_items.empty()) {
         const int64_t d = p->head_dim;
         const bool strips = row_stride == 0;
         BlkFlashParams fp{};
@@ -496,8 +498,8 @@ static int attention_run_impl(const blk_plan* p, const void* q, const void* k, c
         fp.out_head_stride = strips ? p->Dm1 : head_stride;
         cudaError_t e = blk_launch_attn_umma(fp, q, k, v, p->num_sms, reinterpret_cast<cudaStream_t>(cuda_stream));
         if (e != cudaSuccess) return cuda_fail("attention launch", e);
-        return BLK_OK;
     }
+    if (p->packs.empty()) return BLK_OK;
     BlkPackParams pp{};
     pp.A = reinterpret_cast<const uint16_t*>(q);
     pp.B = reinterpret_cast<const uint16_t*>(k);

@@ -254,6 +254,7 @@ int blk_build_gemm_schedule(blk_plan* p) {
             blk_set_error("gemm plan: int64 overflow");
             return BLK_ERR_INVALID;
         }
+        if (p->attn) needC[s] = needA[s];  // an attention plan's output holds result rows, not scores
     }
     int rc;
     if ((rc = validate_offsets("gemm plan: mat1Accum", p->a1, needA, S)) != BLK_OK) return rc;

@@ -149,8 +149,9 @@ BLK_API int blk_gemm_run_strided(const blk_plan_t* plan, const void* mat1, int64
 BLK_API int blk_attention_plan_create(blk_plan_t** plan, const int64_t* M, const int64_t* N, int64_t S, int64_t H,
                               int dtype, int device);
 /* The same operator for any batch: segments of any length (M_s >= 0 queries,
- * N_s >= 1 keys where M_s > 0), head dimension 64 or 128.  A batch the kernel
- * above can take runs on it; every other batch runs on one tcgen05 kernel that
+ * N_s >= 1 keys where M_s > 0), head dimension 64 or 128.  At head dimension
+ * 64 the segments the kernel above can take run on it (a first launch); every
+ * other segment -- every segment at head dimension 128 -- runs on one tcgen05 kernel that
  * sweeps a segment's keys and values in tiles of 128 rows with an online
  * softmax, the scores in tensor memory, the probabilities handed to the second
  * product through shared memory: neither is ever stored.  q (H, sum M_s * d),

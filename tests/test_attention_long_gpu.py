@@ -47,8 +47,9 @@ def test_attention_every_edge_of_the_tiling(cuda_device, dtype, d, scale):
     H = 3
     q, k, v = inputs(M, N, d, H, dtype, 11)
     plan = AttentionPlan(M, N, H, dtype, device=dev, d=d)
-    assert plan.summary["umma_items"] == int(np.ceil(M / 128).sum()) and plan.summary["packs"] == 0
-    assert plan.summary["launches"] == 1
+    big = (M > 64) | (N > 64) if d == 64 else np.ones(len(M), bool)   # at d = 64 the small segments go into packs
+    assert plan.summary["umma_items"] == int(np.ceil(M[big] / 128).sum())
+    assert plan.summary["launches"] == 1 + int(d == 64)
     out = torch.full((H, int(M.sum()) * d), float("nan"), dtype=dtype, device=dev)
     plan.run(q.to(dev), k.to(dev), v.to(dev), out=out, scale=scale)
     plan.check()
@@ -81,6 +82,27 @@ def test_attention_long_tail_batch_and_composition(cuda_device):
     dl = np.full_like(n, d)
     comp = blockGEMM(blockAttnScores(qd, kd, n, n, dl, scale=0.125), vd, None, None, None, n, dl, n, False, True)
     close(got, comp.float().cpu(), BF16, "fused vs composed")
+
+
+def test_attention_mixed_batch_uses_both_kernels(cuda_device):
+    # molecular sizes with a few graphs beyond 64 nodes (d = 64): the small graphs go into packs of the small-segment
+    # kernel, the large ones to the tcgen05 kernel; two launches write disjoint rows of one result
+    dev = cuda_device
+    rs = np.random.RandomState(7)
+    n = np.clip(np.rint(rs.normal(25, 10, 500)), 2, 64).astype(np.int64)
+    n[::50] = rs.randint(65, 400, size=len(n[::50]))
+    M = n.copy(); N = n.copy()
+    N[5] = 100                                       # few queries, many keys: not a small segment either
+    H, d = 4, 64
+    q, k, v = inputs(M, N, d, H, F16, 51)
+    plan = AttentionPlan(M, N, H, F16, device=dev, d=d)
+    s = plan.summary
+    big = (M > 64) | (N > 64)
+    assert s["packs"] > 0 and s["launches"] == 2 and s["umma_items"] == int(np.ceil(M[big] / 128).sum())
+    out = torch.full((H, int(M.sum()) * d), float("nan"), dtype=F16, device=dev)
+    plan.run(q.to(dev), k.to(dev), v.to(dev), out=out, scale=0.125)
+    plan.check()
+    close(out, oracle_attention(q, k, v, M, N, d, 0.125), F16, "attention, mixed batch")
 
 
 def test_attention_values_of_a_neighbour_do_not_leak(cuda_device):

@@ -94,15 +94,29 @@ def test_attention_schedule_picks_the_kernel_by_batch():
     s = p.summary
     assert s["packs"] > 0 and s["umma_items"] == 0 and s["launches"] == 1
     assert p.work[0] == pytest.approx(w.flops()) and p.work[1] == pytest.approx(w.bytes())
-    # any longer segment, or d = 128: one item per 128-row block of queries on the tcgen05 attention kernel
+    # longer segments, or d = 128: one item per 128-row block of queries on the tcgen05 attention kernel (at d = 64
+    # the segments of at most 64 x 64 stay in packs: two launches)
     for name in ("long_tail_attention", "full_forward_attention"):
         w = workload(name)
-        p = AttentionPlan(w.M, w.N, w.H, w.dtype, d=int(w.K[0]))
+        d = int(w.K[0])
+        p = AttentionPlan(w.M, w.N, w.H, w.dtype, d=d)
         s = p.summary
-        assert s["packs"] == 0 and s["tile_items"] == 0 and s["launches"] == 1
-        assert s["umma_items"] == int(np.ceil(w.M / 128).sum())
+        big = (w.M > 64) | (w.N > 64) if d == 64 else np.ones(w.S, bool)
+        assert (s["packs"] > 0) == bool((~big).any()) and s["tile_items"] == 0
+        assert s["launches"] == 1 + int((~big).any())
+        assert s["umma_items"] == int(np.ceil(w.M[big] / 128).sum())
         assert p.work[0] == pytest.approx(w.flops()) and p.work[1] == pytest.approx(w.bytes())
         assert p.extents[0] == int(w.M.sum()) * int(w.K[0]) and p.extents[2] == p.extents[0]
+    # d = 64 with a few long segments: packs for the small ones, tcgen05 items for the rest, two launches
+    w = workload("molecular")
+    M = w.M.copy(); N = w.N.copy()
+    M[::97] = 150; N[::97] = 150
+    N[5] = 100
+    p = AttentionPlan(M, N, w.H, w.dtype, d=64)
+    s = p.summary
+    big = (M > 64) | (N > 64)
+    assert s["packs"] > 0 and s["launches"] == 2
+    assert s["umma_items"] == int(np.ceil(M[big] / 128).sum()) and s["small_items"] == int((~big).sum())
     # what neither kernel takes
     with pytest.raises(RuntimeError):
         AttentionPlan([4], [4], 1, torch.float16, d=32)
