@@ -407,8 +407,8 @@ static int attention_plan_impl(blk_plan_t** plan, const int64_t* M, const int64_
         p->Dm1 = p->Dout = p->a1[S];
         p->Dm2 = p->a2[S];
         rc = build_flash_items(p, packs);
-        if (rc == BLK_OK && (int64_t)p->flash_items.size() * H >= ((int64_t)1 << 32)) {
-            blk_set_error("attention plan: more than 2^32 work items");
+        if (rc == BLK_OK && (int64_t)p->flash_items.size() * H >= ((int64_t)1 << 31)) {
+            blk_set_error("attention plan: more than 2^31 work items");
             rc = BLK_ERR_UNSUPPORTED;
         }
         if (!p->flash_items.empty()) p->attn = packs ? 3 : 2;  // 3: packs and tcgen05 items, two launches
