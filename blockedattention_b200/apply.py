@@ -242,9 +242,11 @@ def blockAttention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, MList, NLi
     if rows_q <= 0 or rows_kv <= 0:
         raise RuntimeError("blockAttention needs at least one query row and one key row")
     if d is None:
-        d = 64 if q.numel() % (rows_q * 64) == 0 and k.numel() == (q.numel() // (rows_q * 64)) * rows_kv * 64 else None
-        if d is None:
-            raise RuntimeError("give the head dimension d (it cannot be told apart from the number of heads)")
+        # a (H, sum m_s * d) tensor tells d by its last extent; a flat one cannot (d and H only appear as a product)
+        if q.dim() >= 2 and q.shape[-1] % rows_q == 0:
+            d = int(q.shape[-1]) // rows_q
+        else:
+            raise RuntimeError("give the head dimension d (a flat tensor cannot tell it apart from the number of heads)")
     if q.numel() % (rows_q * d) or k.numel() != (q.numel() // (rows_q * d)) * rows_kv * d or v.numel() != k.numel():
         raise RuntimeError("q / k / v do not match the packed extents of the lists")
     H = q.numel() // (rows_q * d)

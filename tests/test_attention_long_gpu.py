@@ -114,7 +114,7 @@ def test_attention_values_of_a_neighbour_do_not_leak(cuda_device):
     q, k, v = inputs(M, N, d, H, F16, 41)
     v = v.clone()
     v.view(H, -1, d)[:, 37:, :] = float("inf")
-    got = blockAttention(q.to(dev), k.to(dev), v.to(dev), M, N, scale=0.09, d=d)
+    got = blockAttention(q.to(dev), k.to(dev), v.to(dev), M, N, scale=0.09)   # d = 128 read off the (H, rows * d) shape
     first = got.view(H, -1, d)[:, :50, :].float().cpu()
     want = oracle_attention(q, k, torch.nan_to_num(v, posinf=0.0), M, N, d, 0.09).view(H, -1, d)[:, :50, :]
     assert bool(torch.isfinite(first).all())
