@@ -228,13 +228,44 @@ def blockAttnScores(q: torch.Tensor, k: torch.Tensor, MList, NList, KList, scale
                      scale=scale, out_dtype=out_dtype, softmax=True)
 
 
+class _BlockAttentionFn(torch.autograd.Function):
+    """Fused forward.  The backward recomputes the probabilities with the fused scores operator and runs the softmax
+    backward kernel and four blocked products (the same kernels the two-operator path differentiates with), so the
+    probabilities exist in memory only during the backward pass.  Gradients have the layouts of q, k and v."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, plan, scale):
+        ctx.plan, ctx.scale = plan, scale
+        ctx.save_for_backward(q, k, v)
+        return plan.run(q, k, v, scale=scale)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, k, v = ctx.saved_tensors
+        plan, scale = ctx.plan, ctx.scale
+        m, n = plan.M, plan.N
+        dl = np.full_like(m, plan.d)
+        with torch.no_grad():
+            go = grad_out.contiguous().reshape(q.shape).to(q.dtype)
+            p = blockGEMM(q, k, None, None, None, m, n, dl, False, False, scale=scale, softmax=True)   # (m, n)
+            dv = blockGEMM(p, go, None, None, None, n, dl, m, True, True)           # P^T dO: (n, d)
+            dp = blockGEMM(go, v, None, None, None, m, n, dl, False, False)         # dO V^T: (m, n)
+            key = ("attn_bwd_smx", m.tobytes(), n.tobytes(), plan.H, q.dtype, str(q.device))
+            sp = _cached(key, lambda: SoftmaxPlan(m, n, plan.H, q.dtype, device=q.device))
+            ds = sp.run_backward(p, dp)                                              # d(scale * scores)
+            dq = blockGEMM(ds, k, None, None, None, m, dl, n, False, True, scale=scale)   # dS K: (m, d)
+            dk = blockGEMM(ds, q, None, None, None, n, dl, m, True, True, scale=scale)    # dS^T Q: (n, d)
+        return dq.reshape(q.shape), dk.reshape(k.shape), dv.reshape(v.shape), None, None
+
+
 def blockAttention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, MList, NList, scale: float = 1.0,
                    d: Optional[int] = None) -> torch.Tensor:
     """``softmax_rows(scale * Q_s K_s^T) V_s`` per segment: ``q -> (H, sum m_s*d)``, ``k, v -> (H, sum n_s*d)``, result
     ``(H, sum m_s*d)``, all packed head-major.  With 16-bit inputs and ``d`` 64 or 128 the batch runs as one kernel
     that never stores the probabilities (the pack kernel when every segment has at most 64 rows and columns and
     ``d = 64``, the tcgen05 attention kernel otherwise); any other batch is the composition
-    ``blockGEMM(blockAttnScores(q, k), v, transpose2=True)`` of the two operators.  Forward only."""
+    ``blockGEMM(blockAttnScores(q, k), v, transpose2=True)`` of the two operators.  Carries autograd history: the
+    backward pass recomputes the probabilities with the two-operator path."""
     for name, t in (("q", q), ("k", k), ("v", v)):
         _check_operand(name, t)
     M, N = _host_i64(MList), _host_i64(NList)
@@ -256,6 +287,8 @@ def blockAttention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, MList, NLi
         key = ("attn", M.tobytes(), N.tobytes(), H, d, q.dtype, str(q.device))
         try:
             plan = _cached(key, lambda: AttentionPlan(M, N, H, q.dtype, device=q.device, d=d))
+            if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+                return _BlockAttentionFn.apply(q, k, v, plan, scale)
             return plan.run(q, k, v, scale=scale)
         except L.BlkError as e:
             if e.code != L.BLK_ERR_UNSUPPORTED:

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from helpers import O, packed_inputs
-from blockedattention_b200 import blockAttnScores, blockGEMM, blockSoftmax
+from blockedattention_b200 import blockAttention, blockAttnScores, blockGEMM, blockSoftmax
 from blockedattention_b200.plan import SoftmaxPlan
 
 pytestmark = pytest.mark.gpu
@@ -111,3 +111,40 @@ def test_fused_scores_backward(cuda_device, dtype):
     w1, w2 = O.block_gemm_backward(Q, Kt, ds, n, n, Kl, scale=0.125)
     close(q.grad, w1, dtype, "dq")
     close(k.grad, w2, dtype, "dk")
+
+
+@pytest.mark.parametrize("d,sizes", [(64, [5, 33, 64, 17]),          # packs of the small-segment kernel
+                                     (64, [5, 200, 64, 130]),        # packs and the tcgen05 attention kernel
+                                     (128, [150, 7, 260])])          # the tcgen05 attention kernel
+def test_fused_attention_backward(cuda_device, d, sizes):
+    # forward on the fused kernels; backward recomputes the probabilities with the two-operator path.  Checked against
+    # torch autograd of the per-segment formula in float64.
+    dev = cuda_device
+    n = np.array(sizes, np.int64)
+    m = np.maximum(n - 3, 1)                      # fewer queries than keys
+    H, scale = 2, 0.1
+    g = torch.Generator().manual_seed(5)
+    q0 = torch.randn((H, int(m.sum()) * d), generator=g).to(F16)
+    k0 = torch.randn((H, int(n.sum()) * d), generator=g).to(F16)
+    v0 = torch.randn((H, int(n.sum()) * d), generator=g).to(F16)
+    go = torch.randn((H, int(m.sum()) * d), generator=g).to(F16)
+    q, k, v = (t.to(dev).requires_grad_(True) for t in (q0, k0, v0))
+    out = blockAttention(q, k, v, m, n, scale=scale, d=d)
+    out.backward(go.to(dev))
+    # reference
+    qr, kr, vr = (t.double().requires_grad_(True) for t in (q0, k0, v0))
+    outs = []; oq = okv = 0
+    for ms, ns in zip(m, n):
+        ms, ns = int(ms), int(ns)
+        Q = qr[:, oq * d:(oq + ms) * d].reshape(H, ms, d); K = kr[:, okv * d:(okv + ns) * d].reshape(H, ns, d)
+        V = vr[:, okv * d:(okv + ns) * d].reshape(H, ns, d)
+        outs.append((torch.softmax(scale * Q @ K.transpose(1, 2), dim=-1) @ V).reshape(H, ms * d))
+        oq += ms; okv += ns
+    ref = torch.cat(outs, dim=1)
+    ref.backward(go.double())
+    close(out, ref.detach(), F16, "fused attention forward")
+    for name, got, want in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
+        assert got is not None and got.shape == want.shape
+        s = max(1.0, float(want.abs().max()))
+        err = float((got.float().cpu() - want.float()).abs().max())
+        assert err <= 1e-2 * s, f"{name}: max abs err {err} (scale {s})"
