@@ -134,3 +134,18 @@ def test_token_major_attention_long_segments(cuda_device, d):
     strips = [t.permute(1, 0, 2).reshape(H, T * d).contiguous() for t in (q, k, v)]
     want = blockAttention(*strips, n, n, scale=0.1, d=d).reshape(H, T, d).permute(1, 0, 2)
     assert torch.equal(got, want)
+
+
+def test_attention_very_long_key_sweep_and_single_query(cuda_device):
+    # 40 key tiles per query block, one query row against thousands of keys, one head: the rings, the two score
+    # buffers and the two result buffers wrap many times inside one item
+    dev = cuda_device
+    M = np.array([1, 130, 3]); N = np.array([5000, 4100, 129])
+    H, d = 1, 128
+    q, k, v = inputs(M, N, d, H, BF16, 61)
+    plan = AttentionPlan(M, N, H, BF16, device=dev, d=d)
+    out = torch.full((H, int(M.sum()) * d), float("nan"), dtype=BF16, device=dev)
+    for _ in range(2):                                 # a second run of the same plan: barriers start afresh
+        plan.run(q.to(dev), k.to(dev), v.to(dev), out=out, scale=0.09)
+        plan.check()
+    close(out, oracle_attention(q, k, v, M, N, d, 0.09), BF16, "attention, very long key sweep")
