@@ -58,6 +58,21 @@ def softmax_case(name, rows, cols, H, dtype, seed):
                         acc=O.softmax_offsets(rows, cols))
 
 
+def attention_case(name, M, N, d, H, dtype, seed, scale):
+    # softmax(scale Q K^T) V per segment: the composition of the two operators, all float32 in the oracle
+    M = np.asarray(M, np.int64); N = np.asarray(N, np.int64)
+    dl = np.full_like(M, d)
+    g = torch.Generator().manual_seed(seed)
+    Q = torch.randn((H, int(M.sum()) * d), generator=g).to(dtype)
+    K = torch.randn((H, int(N.sum()) * d), generator=g).to(dtype)
+    V = torch.randn((H, int(N.sum()) * d), generator=g).to(dtype)
+    P = O.block_scores(Q, K, M, N, dl, scale=scale)
+    out = O.block_gemm(P, V, M, dl, N, transpose2=True)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), kind="attention", M=M, N=N, d=d, H=H,
+                        dtype=str(dtype).split(".")[-1], scale=scale, A=_np(Q), B=_np(K), X=_np(V),
+                        out=out.numpy().astype(np.float32))
+
+
 def main():
     rs = np.random.RandomState(0)
     n = rs.randint(4, 33, size=32)
@@ -78,6 +93,11 @@ def main():
     softmax_case("softmax_5x2047_fp16", [5, 5, 5], [2047, 2047, 2047], 2, torch.float16, 6)
     # the script's softmax check, test/pytest.py:54-62 (H reduced)
     softmax_case("softmax_script_fp32", [33, 99, 64], [64, 64, 64], 2, torch.float32, 7)
+    # fused attention: graph sizes of csrc/sparseBlockedAttention.cpp:147-155 at d = 64 (the small-segment kernel),
+    # and segments beyond one 128-row block / 128-key tile at d = 128 (the tcgen05 attention kernel)
+    attention_case("attention_graphs_d64_fp16", [10, 5, 20, 5, 60], [10, 5, 20, 5, 60], 64, 2, torch.float16, 8, 0.125)
+    attention_case("attention_long_d128_bf16", [130, 3, 40], [150, 257, 40], 128, 2, torch.bfloat16, 9,
+                   1 / np.sqrt(128.0))
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -6,7 +6,7 @@ import torch
 
 from helpers import assert_probs_close, assert_scores_close
 from test_oracle import GOLDEN, load_golden
-from blockedattention_b200.plan import GemmPlan, SoftmaxPlan
+from blockedattention_b200.plan import AttentionPlan, GemmPlan, SoftmaxPlan
 
 pytestmark = pytest.mark.gpu
 
@@ -28,6 +28,13 @@ def test_cuda_matches_golden(cuda_device, path):
             assert_scores_close(out, d["out"], path)
             if "arange" in path:   # integer-valued fp32 answers come out exactly
                 assert torch.equal(out.cpu(), d["out"])
+    elif str(d["kind"]) == "attention":
+        plan = AttentionPlan(d["M"], d["N"], int(d["H"]), dt, device=dev, d=int(d["d"]))
+        out = plan.run(d["A"].to(dev), d["B"].to(dev), d["X"].to(dev), scale=float(d["scale"]))
+        plan.check()
+        want = d["out"]
+        tol = (2e-3 if dt == torch.float16 else 1.6e-2) * max(1.0, float(want.abs().max()))
+        assert float((out.float().cpu() - want).abs().max()) <= tol, path
     else:
         plan = SoftmaxPlan(d["rows"], d["cols"], int(d["H"]), dt, device=dev)
         assert (plan.offsets == d["acc"]).all()

@@ -42,6 +42,10 @@ def test_oracle_matches_golden(path):
             out = O.block_softmax(out, d["M"], d["N"])
         a1, a2, ao = O.offsets_from_lists(d["M"], d["N"], d["K"])
         assert (a1 == d["a1"]).all() and (a2 == d["a2"]).all() and (ao == d["ao"]).all()
+    elif str(d["kind"]) == "attention":
+        dl = np.full_like(d["M"], int(d["d"]))
+        out = O.block_gemm(O.block_scores(d["A"], d["B"], d["M"], d["N"], dl, scale=float(d["scale"])), d["X"],
+                           d["M"], dl, d["N"], transpose2=True)
     else:
         out = O.block_softmax(d["X"], d["rows"], d["cols"])
         assert (O.softmax_offsets(d["rows"], d["cols"]) == d["acc"]).all()
