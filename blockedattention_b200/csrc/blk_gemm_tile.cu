@@ -327,9 +327,12 @@ __device__ __forceinline__ void scores_body(const BlkGemmParams& p, const BlkSeg
     store_frag<Tag, NJW>(p.C, p.out_f32, cbase, acc, r0, M, N, n0 + (warp >> 2) * (8 * NJW), t, pair_ok);
 }
 
-// SOFTMAX: the fused two-sweep kernel (four warps); otherwise the scores kernel (eight warps).
+// SOFTMAX: the fused two-sweep kernel (four warps); otherwise the scores kernel (eight warps).  The scores kernel
+// without transposed operands is held to 64 registers (a few spills) for a fourth resident CTA: its tiles are bound
+// by the latency of their load chain, and one more tile in flight measured 8 % faster; the transposed variants
+// measured slower that way.
 template <typename Tag, bool TA, bool TB, bool SOFTMAX>
-__global__ void __launch_bounds__(SOFTMAX ? NT : NT_SC, 3) blk_gemm_tile_kernel(const BlkGemmParams p) {
+__global__ void __launch_bounds__(SOFTMAX ? NT : NT_SC, (SOFTMAX || TA || TB) ? 3 : 4) blk_gemm_tile_kernel(const BlkGemmParams p) {
     __shared__ __align__(16) uint16_t sA[2][A_STAGE];
     __shared__ __align__(16) uint16_t sB[2][B_STAGE];
     const int64_t bid = blockIdx.x;
