@@ -53,6 +53,11 @@ int upload_plan(blk_plan* p) {
     int rc;
     if ((rc = upload(p->segs, &p->d_segs, "upload segments")) != BLK_OK) return rc;
     if ((rc = upload(p->tile_items, &p->d_tile_items, "upload tile items")) != BLK_OK) return rc;
+    if (p->dtype_in != BLK_F32) {
+        std::vector<BlkTileRec> recs(p->tile_items.size());
+        for (size_t i = 0; i < recs.size(); ++i) recs[i] = BlkTileRec{p->segs[p->tile_items[i].seg], p->tile_items[i], 0};
+        if ((rc = upload(recs, &p->d_tile_recs, "upload tile records")) != BLK_OK) return rc;
+    }
     if ((rc = upload(p->simt_items, &p->d_simt_items, "upload simt items")) != BLK_OK) return rc;
     for (int b = 0; b < BLK_SMALL_BUCKETS; ++b)
         if ((rc = upload(p->small_items[b], &p->d_small_items[b], "upload small items")) != BLK_OK) return rc;
@@ -214,6 +219,7 @@ extern "C" void blk_plan_destroy(blk_plan_t* p) {
         DeviceScope scope(p->device);
         cudaFree(p->d_segs);
         cudaFree(p->d_tile_items);
+        cudaFree(p->d_tile_recs);
         cudaFree(p->d_simt_items);
         for (int b = 0; b < BLK_SMALL_BUCKETS; ++b) cudaFree(p->d_small_items[b]);
         cudaFree(p->d_umma_items);
@@ -639,6 +645,7 @@ static int gemm_run_impl(const blk_plan* p, const void* mat1, const void* mat2, 
         gp.C = out;
         gp.segs = p->d_segs;
         gp.items = p->d_tile_items;
+        gp.recs = p->d_tile_recs;
         gp.Dm1 = p->Dm1; gp.Dm2 = p->Dm2; gp.Dout = p->Dout;
         gp.num_items = (int)p->tile_items.size();
         gp.H = (int)p->H;

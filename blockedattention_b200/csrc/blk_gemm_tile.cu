@@ -337,8 +337,9 @@ __global__ void __launch_bounds__(SOFTMAX ? NT : NT_SC, (SOFTMAX || TA || TB) ? 
     __shared__ __align__(16) uint16_t sB[2][B_STAGE];
     const int64_t bid = blockIdx.x;
     const int head = (int)(bid / p.num_items);
-    const BlkTileItem it = p.items[bid % p.num_items];
-    const BlkSeg sd = p.segs[it.seg];
+    const BlkTileRec rec = p.recs[bid % p.num_items];
+    const BlkTileItem it = rec.it;
+    const BlkSeg sd = rec.sd;
     const int64_t baseA = (int64_t)head * p.Dm1 + sd.offA, baseB = (int64_t)head * p.Dm2 + sd.offB;
     const int64_t cbase = (int64_t)head * p.Dout + sd.offC;
     const uint16_t* gA = p.A + baseA;

@@ -31,6 +31,15 @@ struct BlkTileItem {
     int32_t ntn;
 };
 
+// What a CTA of the staged mma.sync kernel reads first: its item and the item's segment in one 64-byte record, so
+// that the operand addresses depend on one global load instead of two in a row.
+struct BlkTileRec {
+    BlkSeg sd;
+    BlkTileItem it;
+    int64_t pad;
+};
+static_assert(sizeof(BlkTileRec) == 64, "BlkTileRec layout");
+
 // One warp of the packed small-segment kernel: a whole (segment, head) score
 // block with N <= 64, K a multiple of 32, everything 16-byte aligned.
 struct BlkSmallItem {
@@ -148,6 +157,7 @@ struct blk_plan {
     // device copies
     BlkSeg* d_segs = nullptr;
     BlkTileItem* d_tile_items = nullptr;
+    BlkTileRec* d_tile_recs = nullptr;
     BlkTileItem* d_simt_items = nullptr;
     BlkSmallItem* d_small_items[BLK_SMALL_BUCKETS] = {nullptr, nullptr};
     int num_sms = 148;

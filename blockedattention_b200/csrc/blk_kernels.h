@@ -20,6 +20,7 @@ struct BlkGemmParams {
     void* C;
     const BlkSeg* segs;
     const BlkTileItem* items;
+    const BlkTileRec* recs;  // items[i] and its segment side by side
     int64_t Dm1, Dm2, Dout;
     int num_items;
     int H;
