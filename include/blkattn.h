@@ -153,8 +153,8 @@ BLK_API int blk_attention_plan_create(blk_plan_t** plan, const int64_t* M, const
  * 64 the segments the kernel above can take run on it (a first launch); every
  * other segment -- every segment at head dimension 128 -- runs on one tcgen05 kernel that
  * sweeps a segment's keys and values in tiles of 128 rows with an online
- * softmax, the scores in tensor memory, the probabilities handed to the second
- * product through shared memory: neither is ever stored.  q (H, sum M_s * d),
+ * softmax, the scores in tensor memory and the probabilities written over them
+ * for the second product: neither is ever stored.  q (H, sum M_s * d),
  * k, v (H, sum N_s * d), out (H, sum M_s * d).  Replaces the upstream chain
  * blockGEMM -> blockSoftmax -> blockGEMM (blockedAttention/apply.py:6-41,
  * test/pytest.py:35-38) where its result feeds the product with V.
