@@ -7,9 +7,10 @@ Differences from upstream, all at the boundary:
 * keyword-only extensions ``scale``, ``out_dtype`` and ``softmax`` (defaults
   reproduce upstream behaviour: no scale, output dtype = input dtype, separate
   softmax call);
-* lists/offsets are read to the host once per distinct (tensor, version) and
-  the resulting plan is cached, where upstream synchronises seven to eleven
-  times per call;
+* lists/offsets are read to the host once per distinct list tensor (kept
+  alive while remembered, so an address cannot come back with other values)
+  and the plan is cached under the list *values*, where upstream synchronises
+  seven to eleven times per call;
 * the shape checks upstream leaves to ``assert`` raise ``RuntimeError``;
 * ``blockSoftmax`` passes its arguments by name, so ``srcAccum`` reaches the
   offsets parameter (upstream ``apply.py:41`` hands it to ``rowList``);
@@ -33,15 +34,30 @@ from .plan import AttentionPlan, GemmPlan, SoftmaxPlan, _host_i64
 
 _CACHE: "OrderedDict[tuple, object]" = OrderedDict()
 _CACHE_MAX = 32
+# List tensors already read to the host: (data_ptr, _version, numel, dtype, device) -> (the tensor, its values as
+# bytes).  The entry keeps the tensor alive, so its storage cannot be freed and handed to a tensor with other
+# values while the entry exists; an in-place write moves _version.  A hit therefore costs no device->host copy,
+# and the plan cache below is keyed on the values themselves, never on addresses.
+_LISTS: "OrderedDict[tuple, tuple]" = OrderedDict()
+_LISTS_MAX = 256
 
 
 def _key_of(x):
+    """Cache key of a list / offset argument: its int64 values."""
     if x is None:
         return None
     if isinstance(x, torch.Tensor):
-        return ("t", x.data_ptr(), x._version, x.numel(), str(x.device))
-    a = np.asarray(x, dtype=np.int64)
-    return ("h", a.tobytes())
+        fast = (x.data_ptr(), x._version, x.numel(), x.dtype, str(x.device))
+        hit = _LISTS.get(fast)
+        if hit is not None:
+            _LISTS.move_to_end(fast)
+            return ("v", hit[1])
+        data = _host_i64(x).tobytes()
+        _LISTS[fast] = (x, data)
+        while len(_LISTS) > _LISTS_MAX:
+            _LISTS.popitem(last=False)
+        return ("v", data)
+    return ("v", np.ascontiguousarray(np.asarray(x, dtype=np.int64)).tobytes())
 
 
 def _cached(key, build):
@@ -49,16 +65,29 @@ def _cached(key, build):
     if plan is None:
         plan = build()
         _CACHE[key] = plan
+        # An evicted plan is only dropped from the table: an autograd context or a queued host-pipe step may
+        # still hold it, and the library handle is released when the last reference goes away.
         while len(_CACHE) > _CACHE_MAX:
-            _CACHE.popitem(last=False)[1].close()
+            _CACHE.popitem(last=False)
     else:
         _CACHE.move_to_end(key)
     return plan
 
 
 def clear_plan_cache() -> None:
-    while _CACHE:
-        _CACHE.popitem()[1].close()
+    """Forgets every cached plan and list (plans still referenced elsewhere stay usable)."""
+    _CACHE.clear()
+    _LISTS.clear()
+
+
+def check_plans() -> None:
+    """Synchronises the current stream of every cached plan's device and raises ``BlkError``
+    (``BLK_ERR_TIMEOUT``) if a kernel of one of them gave up a bounded device-side wait since the last check --
+    the result of that call is then incomplete.  ``BLK_CHECK=1`` in the environment does this after every run."""
+    for plan in list(_CACHE.values()):
+        inner = getattr(plan, "plan", plan)   # a host pipe wraps its plan
+        if getattr(inner, "device", None) is not None:
+            inner.check()
 
 
 def _check_operand(name: str, t: torch.Tensor) -> None:
@@ -346,9 +375,6 @@ class _HostPipe:
                       torch.empty((self.Hg, p.Dm2), dtype=dtype, device=device),
                       torch.empty((self.Hg, p.Dout), dtype=odt, device=device)) for _ in range(2)]
         self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(device=device) for _ in range(3))
-
-    def close(self):
-        self.plan.close()
 
 
 def blockAttnScoresHost(q: torch.Tensor, k: torch.Tensor, MList, NList, KList, scale: float = 1.0,

@@ -448,6 +448,22 @@ int blk_build_softmax_schedule(blk_plan* p) {
     p->flops = 0;
     p->bytes = 0;
     const int64_t window = BLK_SMX_WINDOW_BYTES / es;  // elements
+    // Count the chunks before making them: a batch of very many long rows must be refused, not materialised.
+    {
+        const int64_t cap = p->max_chunks > 0 ? p->max_chunks : (int64_t)0x7fffffff / std::max<int64_t>(p->H, 1);
+        int64_t count = 0;
+        for (int64_t s = 0; s < S && count <= cap; ++s) {
+            const int64_t rows = p->M[s], cols = p->N[s];
+            if (rows == 0 || cols == 0) continue;
+            const int64_t rpc = cols > window ? 1 : window / cols;
+            count += (rows + rpc - 1) / rpc;
+        }
+        if (count > cap) {
+            blk_set_error("softmax plan: this batch needs more than " + std::to_string(cap) +
+                          " chunks of 16 KB (a row longer than 16 KB is one chunk)");
+            return BLK_ERR_UNSUPPORTED;
+        }
+    }
     for (int64_t s = 0; s < S; ++s) {
         const int64_t rows = p->M[s], cols = p->N[s];
         p->bytes += 2.0 * (double)p->H * (double)rows * (double)cols * es;

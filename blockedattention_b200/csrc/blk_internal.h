@@ -141,6 +141,7 @@ struct blk_plan {
     std::vector<BlkUmmaItem> umma_items;    // tcgen05 kernel
     std::vector<BlkSmxChunk> smx_chunks;    // softmax kernel (also second pass of fp32 scores)
     std::vector<BlkSmxWindow> smx_windows;  // pipelined softmax kernels: groups of chunks
+    int64_t max_chunks = 0;                 // > 0: the softmax scheduler refuses batches that need more chunks
     int umma_K = 0;                         // uniform K of the tcgen05 bin
     int small_K = 0;                        // uniform K of the small bin
     int small_pipe = 0;                     // 1: the small segments run as packs on the pipelined kernel

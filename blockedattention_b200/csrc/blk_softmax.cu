@@ -206,11 +206,16 @@ cudaError_t blk_launch_softmax(const BlkSmxParams& p, int dtype, cudaStream_t st
 //
 // Some hosts of this library may not allocate device memory at the point where
 // they need the operator: a runtime that has handed all device memory to its
-// own arena, a plugin called inside someone else's memory pool, a caller on a
-// real-time path where cudaMalloc's implicit synchronisation is not acceptable.
-// For them the chunk table that blk_softmax_plan_create would upload into a
-// cudaMalloc'ed buffer lives instead in the fixed array below, which every GPU
-// that loads the library carries (1 MB) until the process exits.
+// own arena, a plugin called inside someone else's memory pool, a caller that
+// must not disturb other streams (cudaMalloc and cudaFree synchronise the
+// whole device).  For them the chunk table that blk_softmax_plan_create would
+// upload into a cudaMalloc'ed buffer lives instead in the fixed array below,
+// which every GPU that loads the library carries (1 MB) until the process
+// exits.  The table is copied from ordinary host memory, which the runtime
+// stages before the call returns; that copy may make the call wait for earlier
+// work on the same stream, and it is why the call refuses a capturing stream
+// (a captured copy would read the host table again at every replay, after it
+// has been freed).
 // ---------------------------------------------------------------------------
 static __device__ __align__(256) BlkSmxChunk g_noalloc_chunks[BLK_NOALLOC_MAX_CHUNKS];
 
@@ -237,6 +242,7 @@ extern "C" int blk_softmax_noalloc(const void* src, void* out, const int64_t* ro
     plan.H = H;
     plan.dtype_in = plan.dtype_out = dtype;
     plan.device = -1;
+    plan.max_chunks = BLK_NOALLOC_MAX_CHUNKS;  // refused by count, before any chunk is made
     plan.M.assign(rows, rows + S);
     plan.N.assign(cols, cols + S);
     plan.a1.resize(S + 1);
@@ -245,10 +251,8 @@ extern "C" int blk_softmax_noalloc(const void* src, void* out, const int64_t* ro
     if (rc != BLK_OK) return rc;
     const size_t nchunks = plan.smx_chunks.size();
     if (nchunks == 0 || H == 0) return BLK_OK;
-    if (nchunks > (size_t)BLK_NOALLOC_MAX_CHUNKS) {
-        blk_set_error("blk_softmax_noalloc: this batch needs " + std::to_string(nchunks) +
-                      " chunks of 16 KB, the built-in table holds " + std::to_string(BLK_NOALLOC_MAX_CHUNKS) +
-                      "; use blk_softmax_plan_create / blk_softmax_run for larger batches");
+    if (nchunks > (size_t)BLK_NOALLOC_MAX_CHUNKS) {  // the scheduler has already refused by count; kept as a guard
+        blk_set_error("blk_softmax_noalloc: the built-in table holds " + std::to_string(BLK_NOALLOC_MAX_CHUNKS) + " chunks");
         return BLK_ERR_UNSUPPORTED;
     }
     if ((int64_t)nchunks * H > 0x7fffffffLL) {
@@ -281,6 +285,19 @@ extern "C" int blk_softmax_noalloc(const void* src, void* out, const int64_t* ro
     }
     BlkSmxChunk* table = g_noalloc_dev_ptr[dev];
     cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        e = cudaStreamIsCapturing(st, &cap);
+        if (e != cudaSuccess) {
+            blk_set_error(std::string("blk_softmax_noalloc: cannot query the stream: ") + cudaGetErrorString(e));
+            return BLK_ERR_CUDA;
+        }
+        if (cap != cudaStreamCaptureStatusNone) {
+            blk_set_error("blk_softmax_noalloc: the stream is being captured; this entry point uploads its table from "
+                          "temporary host memory and cannot be recorded -- capture blk_softmax_run on a plan instead");
+            return BLK_ERR_UNSUPPORTED;
+        }
+    }
     // every call rewrites the entries it uses; nothing in the table has to start at zero
     e = cudaMemcpyAsync(table, plan.smx_chunks.data(), nchunks * sizeof(BlkSmxChunk), cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) {

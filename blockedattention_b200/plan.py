@@ -10,6 +10,7 @@ on torch's current stream and does not synchronise.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional, Sequence
 
 import numpy as np
@@ -77,6 +78,13 @@ class _Plan:
     def check(self):
         """Synchronises the current stream and raises if a kernel reported a timed-out wait."""
         L.check(L.lib.blk_plan_check(self._h, C.c_void_p(_stream_ptr(self.device))))
+
+    def _ran(self):
+        # A kernel whose bounded wait gives up only sets the plan's status word and returns with its output
+        # incomplete; nothing reads that word unless asked.  BLK_CHECK=1 asks after every run (one stream
+        # synchronisation per call: a debugging switch, not a production setting).
+        if os.environ.get("BLK_CHECK", "0") not in ("", "0"):
+            self.check()
 
 
 class GemmPlan(_Plan):
@@ -150,6 +158,7 @@ class GemmPlan(_Plan):
             L.check(L.lib.blk_gemm_run(self._h, C.c_void_p(mat1.data_ptr()), C.c_void_p(mat2.data_ptr()),
                                        C.c_void_p(out.data_ptr()), C.c_float(scale),
                                        C.c_void_p(_stream_ptr(mat1.device))))
+        self._ran()
         return out
 
 
@@ -178,6 +187,7 @@ class GemmPlan(_Plan):
                                                C.c_void_p(mat2.data_ptr()), self.H * d, d,
                                                C.c_void_p(out.data_ptr()), C.c_float(scale),
                                                C.c_void_p(_stream_ptr(mat1.device))))
+        self._ran()
         return out
 
 
@@ -224,6 +234,7 @@ class AttentionPlan(_Plan):
             L.check(L.lib.blk_attention_run(self._h, C.c_void_p(q.data_ptr()), C.c_void_p(k.data_ptr()),
                                             C.c_void_p(v.data_ptr()), C.c_void_p(out.data_ptr()), C.c_float(scale),
                                             C.c_void_p(_stream_ptr(q.device))))
+        self._ran()
         return out
 
 
@@ -249,6 +260,7 @@ class AttentionPlan(_Plan):
                                                     C.c_void_p(v.data_ptr()), C.c_void_p(out.data_ptr()),
                                                     self.H * self.d, self.d, C.c_float(scale),
                                                     C.c_void_p(_stream_ptr(q.device))))
+        self._ran()
         return out
 
 
@@ -299,6 +311,7 @@ class SoftmaxPlan(_Plan):
         with torch.cuda.device(src.device):
             L.check(L.lib.blk_softmax_run(self._h, C.c_void_p(src.data_ptr()), C.c_void_p(out.data_ptr()),
                                           C.c_float(scale), C.c_void_p(_stream_ptr(src.device))))
+        self._ran()
         return out
 
     def run_backward(self, out: torch.Tensor, grad_out: torch.Tensor, grad_src: Optional[torch.Tensor] = None,
@@ -325,4 +338,5 @@ class SoftmaxPlan(_Plan):
             L.check(L.lib.blk_softmax_backward_run(self._h, C.c_void_p(out.data_ptr()), C.c_void_p(grad_out.data_ptr()),
                                                    C.c_void_p(grad_src.data_ptr()), C.c_float(scale),
                                                    C.c_void_p(_stream_ptr(out.device))))
+        self._ran()
         return grad_src

@@ -197,21 +197,25 @@ BLK_API int blk_softmax_backward_run(const blk_plan_t* plan, const void* out, co
 
 /* The row softmax for callers that cannot allocate device memory when they
  * need it: a host whose runtime owns all device memory through its own arena,
- * a plugin running inside another component's pool, a latency-critical path
- * that must not hit cudaMalloc's implicit synchronisation.  No plan: rows and
- * cols are host lists (packed offsets), and the chunk table a plan would
- * upload into allocated memory goes into a fixed 1 MB array that every GPU
- * loading the library carries until exit.  Limit: the batch may need at most
- * 65536 chunks (a chunk covers up to 16 KB of one head's rows; a row longer
- * than 16 KB is one chunk) -- larger batches get BLK_ERR_UNSUPPORTED and
- * should use the plan entry points.  The call performs no cudaMalloc/cudaFree:
- * it copies the table with cudaMemcpyAsync and launches on cuda_stream.  The
- * first call on each device also resolves the array's device address, so make
- * that first call outside any stream capture, with the device current.  All
- * calls on a device share the one array: calls whose GPU work may overlap
- * (different streams, no dependency between them) race on it; calls on one
- * stream are safe.  src/out as for blk_softmax_run.  This entry point has no
- * counterpart in the upstream project. */
+ * a plugin running inside another component's pool, a caller that must not
+ * stall other streams (cudaMalloc and cudaFree synchronise the device).  No
+ * plan: rows and cols are host lists (packed offsets), and the chunk table a
+ * plan would upload into allocated memory goes into a fixed 1 MB array that
+ * every GPU loading the library carries until exit.  Limit: the batch may need
+ * at most 65536 chunks (a chunk covers up to 16 KB of one head's rows; a row
+ * longer than 16 KB is one chunk) -- larger batches get BLK_ERR_UNSUPPORTED,
+ * decided from the lists before anything is built, and should use the plan
+ * entry points.  The call performs no cudaMalloc/cudaFree: it copies the table
+ * with cudaMemcpyAsync from ordinary host memory (the runtime stages that copy
+ * before the call returns, which may wait for earlier work on the stream) and
+ * launches on cuda_stream.  A stream that is being captured is refused with
+ * BLK_ERR_UNSUPPORTED, nothing issued.  The first call on each device also
+ * resolves the array's device address, so make that first call outside any
+ * stream capture, with the device current.  All calls on a device share the
+ * one array: calls whose GPU work may overlap (different streams, no
+ * dependency between them) race on it; calls on one stream are safe.  src/out
+ * as for blk_softmax_run.  This entry point has no counterpart in the upstream
+ * project. */
 BLK_API int blk_softmax_noalloc(const void* src, void* out, const int64_t* rows, const int64_t* cols,
                         int64_t S, int64_t H, int dtype, float scale, void* cuda_stream);
 

@@ -7,7 +7,8 @@ plus ``oracle/ref_shim.cpp`` (a pybind binding of the launchers declared at
 repository; objects and the shared library go to ``oracle/_ref/`` only, which
 is git-ignored.  The upstream build system (setup.py / CMake) is not run.
 
-Usage: ``python oracle/build_ref.py [--ref /path/to/upstream/checkout]``.
+Usage: ``python oracle/build_ref.py --ref /path/to/upstream/checkout`` (or the
+environment variable ``BLK_REFERENCE_DIR``); without either nothing is built.
 The result needs a GPU to do anything; it is used by the ``-m gpu`` parity
 tests as a second checker beside the CPU oracle.
 """
@@ -24,12 +25,12 @@ OUT = os.path.join(HERE, "_ref")
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("BLK_REFERENCE_DIR", "/root/reference"))
+    ap.add_argument("--ref", default=os.environ.get("BLK_REFERENCE_DIR", ""))
     ap.add_argument("--force", action="store_true")
     args = ap.parse_args(argv)
     ref = args.ref
-    if not os.path.isdir(os.path.join(ref, "csrc", "cuda")):
-        print(f"upstream checkout not found at {ref}; nothing built")
+    if not ref or not os.path.isdir(os.path.join(ref, "csrc", "cuda")):
+        print(f"no upstream checkout given (--ref or BLK_REFERENCE_DIR; got {ref!r}); nothing built")
         return 0
     import torch
     from torch.utils import cpp_extension as ce

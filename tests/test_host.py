@@ -228,3 +228,49 @@ def test_partition_edge_cases():
         P.partition_contiguous([1.0, -1.0], 2)
     with pytest.raises(L.BlkError):
         P.partition_contiguous([1.0], 0)
+
+
+def test_plan_cache_is_keyed_on_list_values_not_addresses():
+    # a freed list tensor's address comes back with other values: the key must follow the values
+    from blockedattention_b200 import apply as A
+    A.clear_plan_cache()
+    keys, ptrs = set(), set()
+    for i in range(40):
+        t = torch.tensor([10 + i, 50 - i])
+        ptrs.add(t.data_ptr())
+        keys.add(A._key_of(t))
+        A._LISTS.clear()          # the memo would keep t alive; without it the allocator reuses the block
+        del t
+    assert len(keys) == 40, "two lists with different values shared a key"
+    # a remembered tensor is not read again, and an in-place write is seen
+    t = torch.tensor([3, 4, 5])
+    k1 = A._key_of(t)
+    assert A._key_of(t) == k1 and len(A._LISTS) == 1
+    t[1] = 9
+    assert A._key_of(t) != k1
+    # host sequences, arrays and tensors with equal values share one key
+    assert A._key_of([3, 9, 5]) == A._key_of(np.array([3, 9, 5])) == A._key_of(t)
+    A.clear_plan_cache()
+
+
+def test_evicted_plans_stay_usable_for_their_holders():
+    # the cache drops an evicted plan without closing it: whoever still holds it (an autograd context between
+    # forward and backward, a queued host-pipe step) keeps a live handle
+    from blockedattention_b200 import apply as A
+    A.clear_plan_cache()
+    first = A._cached(("t", 0), lambda: SoftmaxPlan([3], [4], 1, torch.float16))
+    for i in range(1, A._CACHE_MAX + 5):
+        A._cached(("t", i), lambda: SoftmaxPlan([3], [4 + i], 1, torch.float16))
+    assert ("t", 0) not in A._CACHE and len(A._CACHE) == A._CACHE_MAX
+    assert first._h and first.extents[0] == 12
+    A.clear_plan_cache()
+    assert first._h and first.extents[0] == 12
+
+
+def test_softmax_schedule_refuses_by_count_before_building():
+    # 2^30 rows of more than a window each would be 2^30 chunks (tens of GB of host memory): refused from the lists alone, quickly
+    import time
+    t0 = time.perf_counter()
+    with pytest.raises(L.BlkError) as e:
+        SoftmaxPlan([2 ** 29, 2 ** 29], [9000, 9000], 4, torch.float16)
+    assert e.value.code == L.BLK_ERR_UNSUPPORTED and time.perf_counter() - t0 < 1.0
