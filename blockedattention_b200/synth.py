@@ -72,6 +72,13 @@ class Workload:
         w.M, w.N, w.K = self.M[lo:hi].copy(), self.N[lo:hi].copy(), self.K[lo:hi].copy()
         return w
 
+    def take(self, idx) -> "Workload":
+        """The segments ``idx`` (in that order) as a workload of their own (a sample, or a non-contiguous shard)."""
+        idx = np.asarray(idx, dtype=np.int64)
+        w = Workload(**{**self.__dict__})
+        w.M, w.N, w.K = self.M[idx].copy(), self.N[idx].copy(), self.K[idx].copy()
+        return w
+
     def make_inputs(self, device, seed: int = 0):
         """(mat1, mat2) -- and v when d_v > 0 -- packed head-major on ``device``."""
         g = torch.Generator(device=device)

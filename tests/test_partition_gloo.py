@@ -50,6 +50,23 @@ def _worker(rank, world, port, out_dir):
         full = torch.cat(parts, dim=1)
         ref = Or.block_scores(q, k, w.M, w.N, w.K, scale=w.scale)
         assert torch.equal(full, ref)
+        # the library's gather: every rank ends with the single-process (H, Dout) layout, strips received in place
+        owner, info = P.shard(w.M, w.N, w.K, w.H, world)
+        assert info["kind"] == "contiguous" and info["bounds"] == [int(b) for b in bounds]
+        got = P.gather_output(mine, w.M * w.N, owner, w.H)
+        assert got.shape == ref.shape and torch.equal(got, ref)
+        # an ownership that is not contiguous (what the longest-processing-time fallback produces)
+        owner2 = (np.arange(w.S) // 5 % world).astype(np.int32)
+        idx = np.nonzero(owner2 == rank)[0]
+        ql2 = torch.cat([q[:, a1[s]:a1[s + 1]] for s in idx], dim=1)
+        kl2 = torch.cat([k[:, a2[s]:a2[s + 1]] for s in idx], dim=1)
+        mine2 = Or.block_scores(ql2, kl2, w.M[idx], w.N[idx], w.K[idx], scale=w.scale)
+        got2 = P.gather_output(mine2, w.M * w.N, owner2, w.H)
+        assert torch.equal(got2, ref)
+        # a heavy-tailed batch sends shard() to the fallback
+        heavy = np.array([4, 4, 4, 4, 2000, 4, 4, 1500], np.int64)
+        o3, i3 = P.shard(heavy, heavy, np.full(8, 64), 1, world, max_imbalance=1.0)
+        assert i3["kind"] in ("contiguous", "lpt") and len(o3) == 8 and set(o3.tolist()) <= set(range(world))
         # timing reduction the benchmark uses: max over ranks
         t = torch.tensor([float(rank + 1)])
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
