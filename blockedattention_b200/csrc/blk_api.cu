@@ -18,17 +18,6 @@ int cuda_fail(const char* what, cudaError_t e) {
     return BLK_ERR_CUDA;
 }
 
-template <typename T>
-int upload(const std::vector<T>& v, T** dptr, const char* what) {
-    *dptr = nullptr;
-    if (v.empty()) return BLK_OK;
-    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(dptr), v.size() * sizeof(T));
-    if (e != cudaSuccess) return cuda_fail(what, e);
-    e = cudaMemcpy(*dptr, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice);
-    if (e != cudaSuccess) return cuda_fail(what, e);
-    return BLK_OK;
-}
-
 struct DeviceScope {
     int prev = -1;
     bool ok = true;
@@ -43,6 +32,9 @@ struct DeviceScope {
     int target = -1;
 };
 
+// All device tables of a plan live in one allocation, filled by one copy: the tables are laid out in a host
+// staging block (kept per thread and reused, so a new plan touches no fresh pages) at 256-byte aligned offsets,
+// followed by the status / counter words, and the block goes up with a single cudaMemcpy.
 int upload_plan(blk_plan* p) {
     if (p->device < 0) return BLK_OK;
     DeviceScope scope(p->device);
@@ -50,32 +42,56 @@ int upload_plan(blk_plan* p) {
         blk_set_error("cannot select CUDA device " + std::to_string(p->device));
         return BLK_ERR_CUDA;
     }
-    int rc;
-    if ((rc = upload(p->segs, &p->d_segs, "upload segments")) != BLK_OK) return rc;
-    if ((rc = upload(p->tile_items, &p->d_tile_items, "upload tile items")) != BLK_OK) return rc;
-    if (p->dtype_in != BLK_F32) {
-        std::vector<BlkTileRec> recs(p->tile_items.size());
-        for (size_t i = 0; i < recs.size(); ++i) recs[i] = BlkTileRec{p->segs[p->tile_items[i].seg], p->tile_items[i], 0};
-        if ((rc = upload(recs, &p->d_tile_recs, "upload tile records")) != BLK_OK) return rc;
-    }
-    if ((rc = upload(p->simt_items, &p->d_simt_items, "upload simt items")) != BLK_OK) return rc;
-    for (int b = 0; b < BLK_SMALL_BUCKETS; ++b)
-        if ((rc = upload(p->small_items[b], &p->d_small_items[b], "upload small items")) != BLK_OK) return rc;
     {
         int sms = 0;
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device) == cudaSuccess && sms > 0)
             p->num_sms = sms;
     }
-    if ((rc = upload(p->umma_items, &p->d_umma_items, "upload umma items")) != BLK_OK) return rc;
-    if ((rc = upload(p->flash_items, &p->d_flash_items, "upload attention items")) != BLK_OK) return rc;
-    if ((rc = upload(p->packs, &p->d_packs, "upload packs")) != BLK_OK) return rc;
-    if ((rc = upload(p->pack_blocks, &p->d_pack_blocks, "upload pack blocks")) != BLK_OK) return rc;
-    if ((rc = upload(p->smx_chunks, &p->d_smx_chunks, "upload softmax chunks")) != BLK_OK) return rc;
-    if ((rc = upload(p->smx_windows, &p->d_smx_windows, "upload softmax windows")) != BLK_OK) return rc;
-    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&p->d_status), 2 * sizeof(int));
-    if (e != cudaSuccess) return cuda_fail("allocate status word", e);
-    e = cudaMemset(p->d_status, 0, 2 * sizeof(int));
-    if (e != cudaSuccess) return cuda_fail("clear status word", e);
+    struct Piece { const void* src; size_t bytes; void** dst; size_t off; };
+    std::vector<Piece> pieces;
+    size_t total = 0;
+    auto add = [&](const void* src, size_t bytes, void** dst) {
+        *dst = nullptr;
+        if (bytes == 0) return;
+        pieces.push_back(Piece{src, bytes, dst, total});
+        total += (bytes + 255) & ~(size_t)255;
+    };
+    auto add_vec = [&](const auto& v, auto** dst) {
+        add(v.data(), v.size() * sizeof(v[0]), reinterpret_cast<void**>(dst));
+    };
+    add_vec(p->segs, &p->d_segs);
+    add_vec(p->tile_items, &p->d_tile_items);
+    // the staged kernel reads an item and its segment as one record: built straight into the staging block
+    const size_t nrecs = p->dtype_in != BLK_F32 ? p->tile_items.size() : 0;
+    add(nullptr, nrecs * sizeof(BlkTileRec), reinterpret_cast<void**>(&p->d_tile_recs));
+    add_vec(p->simt_items, &p->d_simt_items);
+    for (int b = 0; b < BLK_SMALL_BUCKETS; ++b) add_vec(p->small_items[b], &p->d_small_items[b]);
+    add_vec(p->umma_items, &p->d_umma_items);
+    add_vec(p->flash_items, &p->d_flash_items);
+    add_vec(p->packs, &p->d_packs);
+    add_vec(p->pack_blocks, &p->d_pack_blocks);
+    add_vec(p->smx_chunks, &p->d_smx_chunks);
+    add_vec(p->smx_windows, &p->d_smx_windows);
+    const size_t status_off = total;
+    total += 256;
+    static thread_local std::vector<unsigned char> stage;
+    if (stage.size() < total) stage.resize(total);
+    for (const Piece& pc : pieces) {
+        if (pc.src) {
+            std::memcpy(stage.data() + pc.off, pc.src, pc.bytes);
+        } else {
+            BlkTileRec* recs = reinterpret_cast<BlkTileRec*>(stage.data() + pc.off);
+            for (size_t i = 0; i < nrecs; ++i) recs[i] = BlkTileRec{p->segs[p->tile_items[i].seg], p->tile_items[i], 0};
+        }
+    }
+    std::memset(stage.data() + status_off, 0, 256);
+    cudaError_t e = cudaMalloc(&p->d_pool, total);
+    if (e != cudaSuccess) return cuda_fail("allocate plan tables", e);
+    e = cudaMemcpy(p->d_pool, stage.data(), total, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return cuda_fail("upload plan tables", e);
+    unsigned char* base = reinterpret_cast<unsigned char*>(p->d_pool);
+    for (const Piece& pc : pieces) *pc.dst = base + pc.off;
+    p->d_status = reinterpret_cast<int*>(base + status_off);
     p->d_counter = p->d_status + 1;
     return BLK_OK;
 }
@@ -217,18 +233,7 @@ extern "C" void blk_plan_destroy(blk_plan_t* p) {
     if (!p) return;
     if (p->device >= 0) {
         DeviceScope scope(p->device);
-        cudaFree(p->d_segs);
-        cudaFree(p->d_tile_items);
-        cudaFree(p->d_tile_recs);
-        cudaFree(p->d_simt_items);
-        for (int b = 0; b < BLK_SMALL_BUCKETS; ++b) cudaFree(p->d_small_items[b]);
-        cudaFree(p->d_umma_items);
-        cudaFree(p->d_flash_items);
-        cudaFree(p->d_packs);
-        cudaFree(p->d_pack_blocks);
-        cudaFree(p->d_smx_chunks);
-        cudaFree(p->d_smx_windows);
-        cudaFree(p->d_status);
+        cudaFree(p->d_pool);  // every table and the status words are pieces of this one allocation
     }
     delete p;
 }
@@ -634,6 +639,10 @@ static int gemm_run_impl(const blk_plan* p, const void* mat1, const void* mat2, 
         up.epi = p->epi;
         up.scale = scale;
         up.status = p->d_status;
+        if (blk_env_flag("BLK_TEST_STALL_PRODUCER")) {  // test hook: see BlkUmmaParams::stall
+            up.stall = 1;
+            up.spin_limit = 4096;
+        }
         if ((e = blk_launch_gemm_umma(up, mat1, mat2, layout(layA, p->Dm1, p->umma_K), layout(layB, p->Dm2, p->umma_K),
                                       p->num_sms, st)) != cudaSuccess)
             return cuda_fail("tcgen05 GEMM launch", e);

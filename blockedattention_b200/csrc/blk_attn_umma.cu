@@ -447,7 +447,7 @@ template <typename Tag, int D>
 cudaError_t launch(const BlkFlashParams& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, int sms,
                    cudaStream_t st) {
     auto kern = blk_attn_umma_kernel<Tag, D>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FL<D>::SMEM_BYTES);
+    cudaError_t e = blk_func_smem(reinterpret_cast<const void*>(kern), FL<D>::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     const int64_t total = (int64_t)p.num_items * p.H;
     const dim3 grid((unsigned)(total < sms ? total : sms)), block(FA_THREADS);

@@ -40,6 +40,8 @@
 // kernels (csrc/cuda/spBlkSoftmax.cu:88-269).
 #include <cuda.h>
 
+#include <mutex>
+
 #include "blk_device.cuh"
 #include "blk_kernels.h"
 #include "blk_umma_ptx.cuh"
@@ -218,10 +220,11 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int nkb = p.K / UM_BK;
+    const uint32_t lim = p.spin_limit ? p.spin_limit : BLK_UMMA_SPIN_LIMIT;
 
     if (warp == 0) {
         // ---------------- producer ----------------
-        if (lane == 0) {
+        if (lane == 0 && !p.stall) {
             int stage = 0;
             uint32_t phase = 0;
             Work wk;
@@ -230,7 +233,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 for (int sw = 0; ok && sw < wk.sweeps; ++sw)
                     for (int ch = 0; ok && ch < wk.nchunks; ++ch)
                         for (int kb = 0; kb < nkb; ++kb) {
-                            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+                            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, lim)) { ok = false; break; }
                             const uint32_t sA = smem_u32 + stage * UM_STAGE_BYTES, sB = sA + UM_A_BYTES;
                             mbar_expect_tx(full_bar(stage), UM_STAGE_BYTES);
                             // coordinates (k, row, head), or (k, head, row) for a token-major operand
@@ -254,13 +257,13 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 for (int sw = 0; ok && sw < wk.sweeps; ++sw)
                     for (int ch = 0; ok && ch < wk.nchunks; ++ch) {
                         const int buf = slot & 1;
-                        if (!mbar_wait(tempty_bar(buf), ((slot >> 1) & 1u) ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+                        if (!mbar_wait(tempty_bar(buf), ((slot >> 1) & 1u) ^ 1u, abort_flag, p.status, 2, lim)) { ok = false; break; }
                         tc_fence_after();
                         const int ncols = min(wk.it.N - ch * UM_BN, UM_BN);
                         const uint32_t idesc = instr_desc(p.bf16, (ncols + 15) & ~15, p.epi == BLK_EPI_SOFTMAX && p.scale < 0.f);
                         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * UM_BN);
                         for (int kb = 0; kb < nkb; ++kb) {
-                            if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3)) { ok = false; break; }
+                            if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, lim)) { ok = false; break; }
                             tc_fence_after();
                             const uint32_t sA = smem_u32 + stage * UM_STAGE_BYTES, sB = sA + UM_A_BYTES;
 #pragma unroll
@@ -338,7 +341,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
             if (!softmax) {
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
                     const int buf = slot & 1;
-                    if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 4)) { ok = false; break; }
+                    if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 4, lim)) { ok = false; break; }
                     tc_fence_after();
                     const int ncols = min(N - ch * UM_BN, UM_BN);
                     const int lo = h * CB, hi = min(lo + CB, ncols);
@@ -353,7 +356,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
             } else if (wk.sweeps == 1) {
                 // whole row resident: chunk k of the row sits in accumulator (slot + k) & 1
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch)
-                    if (!mbar_wait(tfull_bar((slot + ch) & 1), ((slot + ch) >> 1) & 1u, abort_flag, p.status, 5)) ok = false;
+                    if (!mbar_wait(tfull_bar((slot + ch) & 1), ((slot + ch) >> 1) & 1u, abort_flag, p.status, 5, lim)) ok = false;
                 if (!ok) break;
                 tc_fence_after();
                 auto tcol = [&](int c) {  // tensor-memory column of row column c
@@ -420,7 +423,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 uint32_t r[32];
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
                     const int buf = slot & 1;
-                    if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 6)) { ok = false; break; }
+                    if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 6, lim)) { ok = false; break; }
                     tc_fence_after();
                     const int ncols = min(N - ch * UM_BN, UM_BN);
                     const int lo = h * CB, hi = min(lo + CB, ncols);
@@ -466,7 +469,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 const float off = -mx * sl - __log2f(sum);  // exp2(x * sl + off) = exp2((x - max) * sl) / sum: no multiply after the exponential
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
                     const int buf = slot & 1;
-                    if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 7)) { ok = false; break; }
+                    if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 7, lim)) { ok = false; break; }
                     tc_fence_after();
                     const int ncols = min(N - ch * UM_BN, UM_BN);
                     const int lo = h * CB, hi = min(lo + CB, ncols);
@@ -517,7 +520,7 @@ EncodeTiledFn encode_fn() {
 template <typename Tag, bool OUT32>
 cudaError_t launch(const BlkUmmaParams& p, const CUtensorMap& a, const CUtensorMap& b, int sms, cudaStream_t st) {
     auto kern = blk_gemm_umma_kernel<Tag, OUT32>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_SMEM_BYTES);
+    cudaError_t e = blk_func_smem(reinterpret_cast<const void*>(kern), UM_SMEM_BYTES);
     if (e != cudaSuccess) return e;
     const int64_t total = (int64_t)p.num_items * p.H;
     const dim3 grid((unsigned)(total < sms ? total : sms)), block(UM_THREADS);
@@ -527,11 +530,39 @@ cudaError_t launch(const BlkUmmaParams& p, const CUtensorMap& a, const CUtensorM
 
 }  // namespace
 
+// Encoded maps are remembered: a map depends only on the arguments below (never on the memory it describes), and a
+// plan is run many times on the same buffers, so the driver's encoder is called once per distinct view.
+namespace {
+struct MapKey {
+    const void* base; int64_t K, H, rows, row_stride, head_stride; int bf16, box_k, box_rows;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && K == o.K && H == o.H && rows == o.rows && row_stride == o.row_stride &&
+               head_stride == o.head_stride && bf16 == o.bf16 && box_k == o.box_k && box_rows == o.box_rows;
+    }
+};
+struct MapSlot { MapKey key; CUtensorMap map; int head_first; uint64_t stamp; bool used; };
+constexpr int MAP_SLOTS = 64;
+MapSlot g_map_slots[MAP_SLOTS];
+uint64_t g_map_clock = 0;
+std::mutex g_map_mu;
+}  // namespace
+
 bool blk_make_row_map(CUtensorMap_st* map, const void* base, int bf16, int64_t K, int64_t H, const BlkOperandLayout& lay,
                       int box_k, int box_rows, int* head_first) {
     EncodeTiledFn fn = encode_fn();
     if (!fn || lay.rows <= 0 || H <= 0) return false;
     if (lay.row_stride % 8 || lay.head_stride % 8 || lay.row_stride < K) return false;  // 16-byte strides
+    const MapKey key{base, K, H, lay.rows, lay.row_stride, lay.head_stride, bf16, box_k, box_rows};
+    {
+        std::lock_guard<std::mutex> g(g_map_mu);
+        for (MapSlot& sl : g_map_slots)
+            if (sl.used && sl.key == key) {
+                sl.stamp = ++g_map_clock;
+                *map = sl.map;
+                *head_first = sl.head_first;
+                return true;
+            }
+    }
     const bool hf = lay.head_stride < lay.row_stride;  // token-major: heads are the closer dimension
     *head_first = hf ? 1 : 0;
     const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)(hf ? H : lay.rows), (cuuint64_t)(hf ? lay.rows : H)};
@@ -539,10 +570,44 @@ bool blk_make_row_map(CUtensorMap_st* map, const void* base, int bf16, int64_t K
                                    (cuuint64_t)(hf ? lay.row_stride : lay.head_stride) * 2};
     const cuuint32_t box[3] = {(cuuint32_t)box_k, (cuuint32_t)(hf ? 1 : box_rows), (cuuint32_t)(hf ? box_rows : 1)};
     const cuuint32_t estr[3] = {1, 1, 1};
-    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+           const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    std::lock_guard<std::mutex> g(g_map_mu);
+    MapSlot* victim = &g_map_slots[0];
+    for (MapSlot& sl : g_map_slots) {
+        if (!sl.used) { victim = &sl; break; }
+        if (sl.stamp < victim->stamp) victim = &sl;
+    }
+    victim->key = key;
+    victim->map = *map;
+    victim->head_first = *head_first;
+    victim->stamp = ++g_map_clock;
+    victim->used = true;
+    return true;
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel and device instead of before every launch.
+cudaError_t blk_func_smem(const void* kern, int bytes) {
+    constexpr int SLOTS = 256;
+    static struct { const void* kern; int dev; } done[SLOTS];
+    static int ndone = 0;
+    static std::mutex mu;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    {
+        std::lock_guard<std::mutex> g(mu);
+        for (int i = 0; i < ndone; ++i)
+            if (done[i].kern == kern && done[i].dev == dev) return cudaSuccess;
+    }
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> g(mu);
+    if (ndone < SLOTS) { done[ndone].kern = kern; done[ndone].dev = dev; ++ndone; }
+    return cudaSuccess;
 }
 
 cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p_in, const void* A, const void* B, const BlkOperandLayout& layA,

@@ -216,8 +216,9 @@ static int elem_bytes(int dtype) { return dtype == BLK_F32 ? 4 : 2; }
 // a (H, D) buffer of es-byte elements: 2 -> 16 bytes, 1 -> 4 bytes (a pair of
 // 16-bit elements; one fp32 element), 0 -> one element.
 static int access_class(int64_t H, int64_t D, int64_t off, int64_t pitch, int es) {
-    const int64_t v16 = 16 / es, v4 = es == 2 ? 2 : 1;
-    auto ok = [&](int64_t v) { return (H <= 1 || D % v == 0) && off % v == 0 && pitch % v == 0; };
+    const int64_t v16 = 16 / es, v4 = es == 2 ? 2 : 1;  // powers of two: masks instead of divisions
+    const int64_t bits = (H <= 1 ? 0 : D) | off | pitch;
+    auto ok = [&](int64_t v) { return (bits & (v - 1)) == 0; };
     if (ok(v16)) return 2;
     if (ok(v4)) return 1;
     return 0;
@@ -366,50 +367,66 @@ int blk_build_gemm_schedule(blk_plan* p) {
     if (p->small_K == 64 && p->dtype_out != BLK_F32 && rows_ok && !blk_env_flag("BLK_DISABLE_PIPE") && !small_segs.empty()) {
         p->small_pipe = 1;
         const int pack_rows = p->attn ? BLK_PACK_ROWS_ATTN : BLK_PACK_ROWS;
-        struct Tmp { BlkPack pk; std::vector<BlkPackBlock> blocks; double cost; };
-        std::vector<Tmp> tmp;
+        // packs in batch order with their blocks in one flat array, then emitted heaviest first
+        std::vector<BlkPack> pk;
+        std::vector<double> cost;
+        std::vector<BlkPackBlock> flat;
+        pk.reserve(small_segs.size() / 4 + 1);
+        cost.reserve(small_segs.size() / 4 + 1);
+        flat.reserve(small_segs.size() * 2);
         for (size_t q = 0; q < small_segs.size(); ++q) {
             const BlkSeg& sd = p->segs[small_segs[q]];
             const int32_t mblocks = (sd.M + 15) / 16;  // one block per 16 first-operand rows of the segment
             bool extend = false;
-            if (!tmp.empty()) {
-                const Tmp& t = tmp.back();
-                extend = t.pk.offA + (int64_t)t.pk.rowsA * 64 == sd.offA && t.pk.offB + (int64_t)t.pk.rowsB * 64 == sd.offB &&
-                         t.pk.rowsA + sd.M <= pack_rows && t.pk.rowsB + sd.N <= pack_rows &&
-                         t.pk.nblocks + mblocks <= BLK_PACK_BLOCKS;
+            if (!pk.empty()) {
+                const BlkPack& t = pk.back();
+                extend = t.offA + (int64_t)t.rowsA * 64 == sd.offA && t.offB + (int64_t)t.rowsB * 64 == sd.offB &&
+                         t.rowsA + sd.M <= pack_rows && t.rowsB + sd.N <= pack_rows &&
+                         t.nblocks + mblocks <= BLK_PACK_BLOCKS;
             }
             if (!extend) {
-                Tmp t;
-                t.pk = BlkPack{sd.offA, sd.offB, 0, 0, 0, 0};
-                t.cost = 0;
-                tmp.push_back(t);
+                pk.push_back(BlkPack{sd.offA, sd.offB, 0, 0, (int32_t)flat.size(), 0});
+                cost.push_back(0.0);
             }
-            Tmp& t = tmp.back();
+            BlkPack& t = pk.back();
             for (int32_t mb = 0; mb < mblocks; ++mb)
                 // output of the block: M x N scores, or for an attention plan M x 64 result rows
-                t.blocks.push_back(BlkPackBlock{sd.offC + (int64_t)mb * 16 * (p->attn ? 64 : sd.N), t.pk.rowsA + 16 * mb, t.pk.rowsB,
-                                                std::min<int32_t>(16, sd.M - 16 * mb), sd.N, 0, 0});
-            t.pk.rowsA += sd.M;
-            t.pk.rowsB += sd.N;
-            t.pk.nblocks += mblocks;
-            t.cost += (double)sd.M * sd.N + (double)(sd.M + sd.N) * 64;
+                flat.push_back(BlkPackBlock{sd.offC + (int64_t)mb * 16 * (p->attn ? 64 : sd.N), t.rowsA + 16 * mb, t.rowsB,
+                                            std::min<int32_t>(16, sd.M - 16 * mb), sd.N, 0, 0});
+            t.rowsA += sd.M;
+            t.rowsB += sd.N;
+            t.nblocks += mblocks;
+            cost.back() += (double)sd.M * sd.N + (double)(sd.M + sd.N) * 64;
         }
         // heaviest packs first: persistent CTAs take packs with a fixed stride
-        std::stable_sort(tmp.begin(), tmp.end(), [](const Tmp& a, const Tmp& b) { return a.cost > b.cost; });
-        for (Tmp& t : tmp) {
-            t.pk.first_block = (int32_t)p->pack_blocks.size();
-            // consumers claim blocks in table order: widest first
-            std::stable_sort(t.blocks.begin(), t.blocks.end(), [](const BlkPackBlock& a, const BlkPackBlock& b) { return a.N > b.N; });
-            for (BlkPackBlock& bl : t.blocks) {
-                bl.nblocks = t.pk.nblocks;
-                p->pack_blocks.push_back(bl);
+        std::vector<int32_t> order(pk.size());
+        std::iota(order.begin(), order.end(), 0);
+        std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return cost[a] > cost[b]; });
+        p->packs.reserve(pk.size());
+        p->pack_blocks.reserve(flat.size() + BLK_PACK_BLOCKS);
+        for (int32_t i : order) {
+            BlkPack t = pk[i];
+            BlkPackBlock* first = flat.data() + t.first_block;
+            // consumers claim blocks in table order: widest first (at most 16 blocks: insertion sort, stable)
+            for (int32_t a = 1; a < t.nblocks; ++a) {
+                const BlkPackBlock key = first[a];
+                int32_t b = a - 1;
+                while (b >= 0 && first[b].N < key.N) { first[b + 1] = first[b]; --b; }
+                first[b + 1] = key;
             }
-            p->packs.push_back(t.pk);
+            t.first_block = (int32_t)p->pack_blocks.size();
+            for (int32_t a = 0; a < t.nblocks; ++a) {
+                first[a].nblocks = t.nblocks;
+                p->pack_blocks.push_back(first[a]);
+            }
+            p->packs.push_back(t);
         }
         // the block table is read in 16-record pieces: keep 16 records of slack behind the last pack
         for (int q = 0; q < BLK_PACK_BLOCKS; ++q) p->pack_blocks.push_back(BlkPackBlock{0, 0, 0, 0, 0, 0, 0});
     }
-    // Persistent warps take small items in list order with a fixed stride: heaviest first evens the tails.
+    // Persistent warps take small items in list order with a fixed stride: heaviest first evens the tails
+    // (the pack kernel does not read these lists).
+    if (!p->small_pipe)
     for (auto& v : p->small_items)
         std::stable_sort(v.begin(), v.end(), [](const BlkSmallItem& a, const BlkSmallItem& b) {
             return (int64_t)a.M * a.N + (int64_t)(a.M + a.N) * 64 > (int64_t)b.M * b.N + (int64_t)(b.M + b.N) * 64;

@@ -155,7 +155,8 @@ struct blk_plan {
     BlkPack* d_packs = nullptr;
     BlkPackBlock* d_pack_blocks = nullptr;
 
-    // device copies
+    // device copies: pieces of the one allocation d_pool
+    void* d_pool = nullptr;
     BlkSeg* d_segs = nullptr;
     BlkTileItem* d_tile_items = nullptr;
     BlkTileRec* d_tile_recs = nullptr;

@@ -68,6 +68,11 @@ struct BlkUmmaParams {
     float scale;
     int* status;
     int head_firstA, head_firstB;  // coordinate order of the operands' tensor maps
+    // Test hook for the bounded waits: stall != 0 makes the producer role issue no copies at all (nothing is ever
+    // in flight), so the first wait for operands runs out after spin_limit polls (0: the normal limit), the kernel
+    // records BLK_ERR_TIMEOUT's status code and returns.
+    int stall;
+    uint32_t spin_limit;
 };
 
 struct BlkPackParams {
@@ -121,6 +126,9 @@ struct BlkSmxParams {
 struct CUtensorMap_st;
 bool blk_make_row_map(CUtensorMap_st* map, const void* base, int bf16, int64_t K, int64_t H, const BlkOperandLayout& lay,
                       int box_k, int box_rows, int* head_first);
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel and device.  Defined in blk_gemm_umma.cu.
+cudaError_t blk_func_smem(const void* kern, int bytes);
 
 cudaError_t blk_launch_gemm_tile(const BlkGemmParams& p, int dtype_in, int ta, int tb, cudaStream_t st);
 // Pipelined softmax kernels (blk_softmax_pipe.cu).  Forward: in0 = src, in1 unused; backward: in0 = forward

@@ -547,7 +547,7 @@ cudaError_t launch_pipe(const BlkPackParams& p_in, int sms, cudaStream_t st) {
     }
     const dim3 grid((unsigned)(total < sms ? total : sms)), block(P_THREADS);
     auto go = [&](auto kern, int smem) -> cudaError_t {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = blk_func_smem(reinterpret_cast<const void*>(kern), smem);
         if (e != cudaSuccess) return e;
         kern<<<grid, block, smem, st>>>(p, mA, mB, mV);
         return cudaGetLastError();

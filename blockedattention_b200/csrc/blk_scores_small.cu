@@ -227,7 +227,7 @@ cudaError_t launch_variant(const BlkSmallParams& p, int sms, cudaStream_t st) {
     const size_t smem = (size_t)SW * (MAXM * NTMAX * 8 * (o32 ? 4 : 2) + 32);
     auto go = [&](auto kern) -> cudaError_t {
         if (smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaError_t e = blk_func_smem(reinterpret_cast<const void*>(kern), (int)smem);
             if (e != cudaSuccess) return e;
         }
         kern<<<grid, block, smem, st>>>(p);

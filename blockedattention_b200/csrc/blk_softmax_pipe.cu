@@ -481,7 +481,7 @@ cudaError_t blk_launch_softmax_pipe(const BlkSmxPipeParams& p, int dtype, int ba
     if (total == 0) return cudaSuccess;
     auto go = [&](auto kern, int nin) -> cudaError_t {
         const int smem = 2 * nin * SP_BUF;
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = blk_func_smem(reinterpret_cast<const void*>(kern), smem);
         if (e != cudaSuccess) return e;
         const int64_t resident = (int64_t)sms * (nin == 1 ? 6 : 3);
         const dim3 grid((unsigned)(total < resident ? total : resident)), block(SP_THREADS);

@@ -31,8 +31,8 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false when another role has already given up or when the bound is hit
 // (then the status word and the CTA's abort flag are set).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code) {
-    for (uint32_t i = 0; i < BLK_UMMA_SPIN_LIMIT; ++i) {
+                                          int code, uint32_t limit = BLK_UMMA_SPIN_LIMIT) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_test(bar, parity)) return true;
         if (i > 128) __nanosleep(64);
         if ((i & 255u) == 255u && *abort_flag) return false;
