@@ -84,6 +84,26 @@ __device__ __forceinline__ float blk_exp2(float x) {
     return y;
 }
 
+// max(a, b, c) in one instruction (three-input maximum of sm_100).
+__device__ __forceinline__ float blk_max3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
+// exp2 of two values at once on packed 16-bit arguments: the pair is rounded to the Tag's 16-bit format, one
+// special-function instruction evaluates both, and the result is the packed pair in that format.
+template <typename Tag> __device__ __forceinline__ uint32_t blk_exp2_pair(float a, float b);
+template <> __device__ __forceinline__ uint32_t blk_exp2_pair<BlkHalfTag>(float a, float b) {
+    uint32_t x = BlkCvt<BlkHalfTag>::pack2(a, b), y;
+    asm("ex2.approx.f16x2 %0, %1;\n" : "=r"(y) : "r"(x));
+    return y;
+}
+template <> __device__ __forceinline__ uint32_t blk_exp2_pair<BlkBf16Tag>(float a, float b) {
+    uint32_t x = BlkCvt<BlkBf16Tag>::pack2(a, b), y;
+    asm("ex2.approx.ftz.bf16x2 %0, %1;\n" : "=r"(y) : "r"(x));
+    return y;
+}
+
 // 16-byte global load that does not allocate in L1 (data touched once).  Not a
 // read-only (.nc) load: the softmax may run in place.
 __device__ __forceinline__ uint4 blk_ldg_stream16(const void* p) {

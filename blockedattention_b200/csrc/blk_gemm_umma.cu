@@ -14,9 +14,15 @@
 //            quarter; the four warps of a quarter each take 64 of every 256
 //            columns of the row and exchange partial row statistics through
 //            shared memory.  A thread reads its row 32 columns at a time
-//            (tcgen05.ld), applies the epilogue and the warp writes the piece
-//            out through a padded shared-memory strip so that lanes store
-//            consecutive addresses with the widest store the row allows.
+//            (tcgen05.ld), applies the epilogue and writes the packed words into
+//            the quarter's strip (32 rows x 256 columns) at the position the row
+//            has in global memory modulo one 32-bit word; after a rendezvous of
+//            the quarter's warps each warp writes eight whole rows of the strip,
+//            a row being 512 contiguous bytes stored as four fully coalesced
+//            128-byte word stores (an odd first or last element goes out as a
+//            16-bit store).  Wide contiguous row pieces are what the memory
+//            system needs here: the same data written as 128-byte pieces with
+//            element-wise ragged edges runs at little more than half the rate.
 //
 // Epilogues.  Scores: scale and round.  Softmax with N <= 512: both
 // accumulators hold the whole row; pass 1 takes the row maximum, pass 2 writes
@@ -60,11 +66,13 @@ constexpr int UM_EPI_WARPS = 4 * UM_SPLIT;
 constexpr int UM_THREADS = 64 + 32 * UM_EPI_WARPS;
 constexpr int UM_CB = UM_BN / UM_SPLIT;               // columns of a chunk owned by one of them
 constexpr int UM_PIECE = 32;                          // columns per tcgen05.ld
-constexpr int UM_ROWPIECE_BYTES = 128;                // bytes of an output row staged per flush (64 x 16-bit, 32 x fp32)
-constexpr int UM_STRIP_PITCH = UM_ROWPIECE_BYTES + 20;  // bytes per strip row: 37 words, odd, so lanes on one column hit 32 banks
-constexpr int UM_STRIP_BYTES = 32 * UM_STRIP_PITCH;   // per epilogue warp
+constexpr int UM_PW = 128;                            // 32-bit words of an output row staged per flush (256 x 16-bit, 128 x fp32)
+// Strip row pitch in words: odd, so that the 32 row-owning lanes of a store (same word, consecutive rows) hit 32
+// different banks; a row holds UM_PW words plus the half word an odd first element pushes past the end.
+constexpr int UM_STRIP_PITCHW = UM_PW + 5;
+constexpr int UM_STRIP_BYTES = 32 * UM_STRIP_PITCHW * 4;  // per quarter (four epilogue warps share it)
 constexpr int UM_XCH_BYTES = 2 * 2 * UM_SPLIT * 128 * 4;  // row statistics exchanged between the two halves, double-buffered
-constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + UM_EPI_WARPS * UM_STRIP_BYTES + UM_XCH_BYTES + 256;
+constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + 4 * UM_STRIP_BYTES + UM_XCH_BYTES + 512;
 static_assert(UM_SMEM_BYTES <= 227 * 1024, "shared memory budget");
 static_assert(UM_STAGES <= 4, "barrier slots");
 
@@ -86,90 +94,20 @@ __device__ __forceinline__ bool next_work(const BlkUmmaParams& p, uint32_t w, Wo
     return true;
 }
 
-// Stage 32 consecutive columns of this thread's row (strip row = lane) at column offset `sub` * 32 of the
-// current row piece.  The strip pitch is an odd number of words (37), so the 32 lanes of a store hit 32
-// different banks.
-template <typename Tag, bool OUT32>
-__device__ __forceinline__ void emit32(const float (&v)[32], unsigned char* strip, int sub, int lane) {
-    const uint32_t base = blk_smem_u32(strip) + lane * UM_STRIP_PITCH + sub * (UM_PIECE * (OUT32 ? 4 : 2));
-    if (OUT32) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) blk_sts_f32(base + 4 * i, v[i]);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) blk_sts_b32(base + 4 * i, BlkCvt<Tag>::pack2(v[2 * i], v[2 * i + 1]));
-    }
-}
-
 // Predicated global stores as single instructions (no branch around them).
-__device__ __forceinline__ void stg_v4_if(void* p, const uint4& v, bool ok) {
-    asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %5, 0;\n @q st.global.v4.b32 [%0], {%1, %2, %3, %4};\n}\n" ::"l"(p),
-                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"((int)ok)
-                 : "memory");
-}
-__device__ __forceinline__ void stg_b16_if(void* p, uint16_t v, bool ok) {
-    asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %2, 0;\n @q st.global.b16 [%0], %1;\n}\n" ::"l"(p), "h"(v), "r"((int)ok)
-                 : "memory");
-}
 __device__ __forceinline__ void stg_b32_if(void* p, uint32_t v, bool ok) {
     asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %2, 0;\n @q st.global.b32 [%0], %1;\n}\n" ::"l"(p), "r"(v), "r"((int)ok)
                  : "memory");
 }
-
-// Strip -> global for the warp's 32 rows x `ncols` columns starting at column col0.  Four rows per pass,
-// eight lanes per row; lane hl owns the 16-byte vector hl of the row piece *as aligned in global memory*.
-// A row piece starts at an arbitrary 2-byte (4-byte for fp32) offset sh inside its first vector, so the
-// lane gathers its 16 bytes from the strip as five words and funnel-shifts them into place; only the
-// ragged first and last vector of a row piece go out as single elements, one per lane.  Branch-free.
-template <bool OUT32>
-__device__ __forceinline__ void flush_piece(const BlkUmmaParams& p, unsigned char* strip, int64_t cbase, int row0,
-                                            int M, int N, int col0, int ncols, int lane) {
-    constexpr int ES = OUT32 ? 4 : 2;
-    constexpr int LPR = UM_ROWPIECE_BYTES / 16;  // lanes (vectors) per row
-    constexpr int RPP = 32 / LPR;                // rows per pass
-    __syncwarp();
-    const int hl = lane % LPR, rsel = lane / LPR;
-    const int nbytes = ncols * ES;
-    const int eoff = ES * hl;  // byte of this lane's edge elements inside the first / last vector
-    int64_t b0 = (cbase + (int64_t)(row0 + rsel) * N + col0) * ES;  // byte offset of this lane's row piece
-    const int64_t bstep = (int64_t)RPP * N * ES;
-    const unsigned char* src = strip + rsel * UM_STRIP_PITCH;  // byte 0 of src <-> byte b0 of the output
-    unsigned char* C = reinterpret_cast<unsigned char*>(p.C);
-#pragma unroll 4
-    for (int r = rsel; r < 32; r += RPP, b0 += bstep, src += RPP * UM_STRIP_PITCH) {
-        const bool row_ok = row0 + r < M;
-        const int sh = (int)(b0 & 15);
-        unsigned char* dst = C + (b0 - sh);  // 16-byte aligned
-        const int end = sh + nbytes;         // the row piece is bytes [sh, end) counted from dst
-        // vector [16 hl, 16 hl + 16) if it lies inside [sh, end): strip bytes [x, x + 16), x = 16 hl - sh
-        const int lo = 16 * hl, x = lo - sh;
-        const int xw = x > 0 ? (x & ~3) : 0;
-        const int sb = (x & 2) * 8;
-        const uint32_t* wp = reinterpret_cast<const uint32_t*>(src + xw);
-        const uint32_t w0 = wp[0], w1 = wp[1], w2 = wp[2], w3 = wp[3], w4 = wp[4];
-        uint4 vec;
-        vec.x = __funnelshift_r(w0, w1, sb);
-        vec.y = __funnelshift_r(w1, w2, sb);
-        vec.z = __funnelshift_r(w2, w3, sb);
-        vec.w = __funnelshift_r(w3, w4, sb);
-        stg_v4_if(dst + lo, vec, row_ok && lo >= sh && lo + 16 <= end);
-        // ragged first and last vector: lane hl takes element hl of each
-        const int tail = end & ~15;
-        const bool in_vec = eoff < 16;
-        const bool first_full = sh == 0 && end >= 16;
-        const bool ok_h = row_ok && in_vec && !first_full && eoff >= sh && eoff < end;
-        const int bt = tail + eoff;
-        const bool ok_t = row_ok && in_vec && tail != 0 && bt < end;
-        const int sh_h = ok_h ? eoff - sh : 0, sh_t = ok_t ? bt - sh : 0;  // strip bytes of the two elements
-        if (OUT32) {
-            stg_b32_if(dst + eoff, *reinterpret_cast<const uint32_t*>(src + sh_h), ok_h);
-            stg_b32_if(dst + bt, *reinterpret_cast<const uint32_t*>(src + sh_t), ok_t);
-        } else {
-            stg_b16_if(dst + eoff, *reinterpret_cast<const uint16_t*>(src + sh_h), ok_h);
-            stg_b16_if(dst + bt, *reinterpret_cast<const uint16_t*>(src + sh_t), ok_t);
-        }
-    }
-    __syncwarp();
+__device__ __forceinline__ void stg_b16_if(void* p, uint32_t v, bool ok) {
+    asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %2, 0;\n @q st.global.b16 [%0], %1;\n}\n" ::"l"(p), "h"((uint16_t)v),
+                 "r"((int)ok)
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t lds_b32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
 }
 
 template <typename Tag, bool OUT32>
@@ -183,9 +121,10 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
         return;
     }
     unsigned char* strips = smem + UM_STAGES * UM_STAGE_BYTES;
-    float* xch = reinterpret_cast<float*>(strips + UM_EPI_WARPS * UM_STRIP_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(strips + UM_EPI_WARPS * UM_STRIP_BYTES + UM_XCH_BYTES);
-    // bars[0..3] full (UM_STAGES used), [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty
+    float* xch = reinterpret_cast<float*>(strips + 4 * UM_STRIP_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(strips + 4 * UM_STRIP_BYTES + UM_XCH_BYTES);
+    // bars[0..3] full (UM_STAGES used), [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty; per quarter q:
+    // [16+q] rendezvous for the row statistics, [20+q] strip written, [24+q] strip read
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
 
@@ -207,7 +146,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
             mbar_init(tempty_bar(b), UM_EPI_WARPS);
         }
         *abort_flag = 0;
-        for (int i = 0; i < 4; ++i) reinterpret_cast<volatile uint32_t*>(bars + 14)[i] = 0;
+        for (int i = 0; i < 12; ++i) mbar_init(bar0 + 8u * (16 + i), UM_SPLIT);  // one arrival per warp of the quarter
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
@@ -282,9 +221,9 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
     } else {
         // ---------------- epilogue: warps 2..17 ----------------
         // lane quarter q = warp % 4 (the 32 accumulator lanes a warp may read); the UM_SPLIT warps of a quarter
-        // split the row's 128-column blocks by parity (half h) and exchange their partial row statistics.
+        // split the columns (share h) and exchange their partial row statistics.
         const int q = warp & 3, h = (warp - 2) >> 2;  // h in [0, UM_SPLIT)
-        unsigned char* strip = strips + (warp - 2) * UM_STRIP_BYTES;
+        const uint32_t qstrip = blk_smem_u32(strips + q * UM_STRIP_BYTES);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         const int myrow = q * 32 + lane;
         uint32_t slot = 0, seq = 0;
@@ -293,50 +232,161 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
         const bool softmax = p.epi == BLK_EPI_SOFTMAX;
         const float sl = softmax ? fabsf(p.scale) * BLK_LOG2E : p.scale;  // a negative softmax scale is applied by
                                                                           // the MMA (negated A), see instr_desc
-        constexpr int RP = UM_ROWPIECE_BYTES / (OUT32 ? 4 : 2);  // columns per staged row piece
-        constexpr int CB = UM_CB;                                // columns of a chunk owned by this warp
-        // Rendezvous of the warps of a quarter (after each has published its row statistics): a shared
-        // counter and a bounded spin, so that a warp whose partner gave up cannot wait for ever.
-        volatile uint32_t* pair_cnt = reinterpret_cast<volatile uint32_t*>(bars + 14) + q;
-        uint32_t pair_target = 0;
-        auto pair_sync = [&]() -> bool {
-            pair_target += UM_SPLIT;
-            __threadfence_block();
+        constexpr int ES = OUT32 ? 4 : 2;
+        constexpr int PC = UM_PW * 4 / ES;   // columns of a staged row piece: 256 x 16-bit or 128 x fp32
+        constexpr int CB = UM_CB;            // columns of a chunk owned by this warp in the statistics passes
+        constexpr int SH = PC / UM_SPLIT;    // columns of a staged piece this warp converts (32 words)
+        // Rendezvous of the warps of a quarter: an mbarrier that one lane of each warp arrives on, waited for like
+        // every other barrier (suspended, bounded), so that a warp whose partner gave up cannot wait for ever.
+        auto quarter_sync = [&](uint32_t bar, uint32_t& phase) -> bool {
             __syncwarp();
-            if (lane == 0) atomicAdd(const_cast<uint32_t*>(pair_cnt), 1u);
-            bool good = false;
-            for (uint32_t i = 0; i < BLK_UMMA_SPIN_LIMIT; ++i) {
-                if ((int32_t)(*pair_cnt - pair_target) >= 0) { good = true; break; }
-                if (i > 64) __nanosleep(32);
-                if ((i & 255u) == 255u && *abort_flag) break;
-            }
-            if (!good) {
-                *abort_flag = 1;
-                atomicCAS(p.status, 0, 8);
-            }
+            if (lane == 0) mbar_arrive(bar);
+            const bool good = mbar_wait(bar, phase, abort_flag, p.status, 8, lim);
+            phase ^= 1u;
             __syncwarp();
-            __threadfence_block();
             return good;
         };
-        // scale, round and store columns [c_lo, c_hi) of the row; tcol(c) gives the tensor-memory column
-        auto store_cols = [&](int c_lo, int c_hi, auto tcol, auto xform, int64_t cbase, int M, int N) {
+        const uint32_t stat_bar = bar0 + 8u * (16 + q), written_bar = bar0 + 8u * (20 + q), read_bar = bar0 + 8u * (24 + q);
+        uint32_t stat_phase = 0, written_phase = 0;
+        uint32_t pieces = 0;  // pieces staged so far: piece n may be staged once all four warps have read piece n - 1
+        auto pair_sync = [&]() -> bool { return quarter_sync(stat_bar, stat_phase); };
+
+        // Store the piece of up to PC columns starting at column c0 of the 32 rows of this quarter.  tcol(c) gives the
+        // tensor-memory column of row column c; pack(r, w) turns 32 raw accumulator words into output words (32 fp32
+        // words, or 16 words of 16-bit pairs); loaded() runs right after this warp's last tensor-memory load of the
+        // piece, where the caller hands the accumulator back to the MMA role.
+        //   1. This warp converts columns [c0 + h SH, c0 + (h + 1) SH) of its lane's row and writes the words into the
+        //      row of the quarter's strip, at the word the element has in global memory: strip word j of a row holds the
+        //      output's 32-bit word (first word of the piece) + j.  A 16-bit piece that starts on an odd element is
+        //      shifted by half a word with a funnel shift through the previous pair; its first and last half words are
+        //      written as 16-bit stores, since the other half of those words belongs to the neighbouring warp.
+        //   2. Rendezvous; then this warp writes rows 8h .. 8h+7 of the strip: lane l carries words l, l + 32, l + 64,
+        //      l + 96 of the row, i.e. four stores of 128 contiguous bytes per row, and the half words at the two ends of
+        //      the eight rows go out in one 16-bit store by sixteen lanes.
+        auto store_piece = [&](int c0, int pcols, auto tcol, auto pack, int64_t cbase, int M, int N, bool anyodd,
+                               auto loaded) -> bool {
             uint32_t r[32];
-            float v[32];
-            for (int c0 = c_lo; c0 < c_hi; c0 += RP) {
-                const int pc = min(RP, c_hi - c0);
-                for (int c = 0; c < pc; c += UM_PIECE) {
-                    tc_ld32(lane_addr + tcol(c0 + c), r);
+            const int64_t g = cbase + (int64_t)myrow * N + c0;       // element index of this lane's piece in the output
+            const uint32_t par = OUT32 ? 0u : (uint32_t)(g & 1);
+            [[maybe_unused]] const uint32_t par16 = par * 16u;
+            const uint32_t srow = qstrip + (uint32_t)lane * (UM_STRIP_PITCHW * 4) + (uint32_t)h * (SH * ES);  // word 32 h of my row
+            const int mycols = min(SH, pcols - h * SH);              // columns of the piece this warp converts (<= 0: none)
+            if (pieces != 0 && !mbar_wait(read_bar, (pieces - 1) & 1u, abort_flag, p.status, 8, lim)) return false;
+            if (mycols <= 0) {
+                loaded();
+            } else if constexpr (OUT32) {
+                uint32_t w[32];
+                tc_ld32(lane_addr + tcol(c0 + h * SH), r);
+                loaded();
+                pack(r, w);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = xform(__uint_as_float(r[i]));
-                    emit32<Tag, OUT32>(v, strip, c / UM_PIECE, lane);
+                for (int i = 0; i < 32; ++i) blk_sts_b32(srow + 4 * i, w[i]);
+            } else {
+                uint32_t w[16];
+                uint32_t prev = 0;
+                const int nu = (mycols + UM_PIECE - 1) / UM_PIECE;
+                for (int u = 0; u < nu; ++u) {
+                    tc_ld32(lane_addr + tcol(c0 + h * SH + u * UM_PIECE), r);
+                    if (u == nu - 1) loaded();
+                    pack(r, w);
+                    const uint32_t a = srow + 64 * u;
+                    if (!anyodd) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) blk_sts_b32(a + 4 * i, w[i]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const uint32_t v = __funnelshift_l(prev, w[i], par16);
+                            if (u == 0 && i == 0) {
+                                // the low half of my first word is the neighbouring warp's last element when the piece is odd
+                                if (par) blk_sts_b16(a + 2, v >> 16);
+                                else blk_sts_b32(a, v);
+                            } else {
+                                blk_sts_b32(a + 4 * i, v);
+                            }
+                            prev = w[i];
+                        }
+                    }
                 }
-                flush_piece<OUT32>(p, strip, cbase, q * 32, M, N, c0, pc, lane);
+                if (anyodd && par) blk_sts_b16(srow + 64 * nu, prev >> 16);  // my last element: low half of the next word
             }
+            if (!quarter_sync(written_bar, written_phase)) return false;
+            // ---- rows 8h .. 8h+7 of the strip -> global memory
+            unsigned char* C = reinterpret_cast<unsigned char*>(p.C);
+            const int64_t g0 = cbase + (int64_t)(q * 32 + 8 * h) * N + c0;   // element index of row 8h's piece
+            const uint32_t rbase = qstrip + (uint32_t)(8 * h) * (UM_STRIP_PITCHW * 4) + 4u * lane;
+#pragma unroll
+            for (int kb = 0; kb < 8; kb += 2) {
+                uint32_t v[2][4];
+#pragma unroll
+                for (int k = 0; k < 2; ++k)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) v[k][i] = lds_b32(rbase + (uint32_t)(kb + k) * (UM_STRIP_PITCHW * 4) + 128u * i);
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const int64_t gr = g0 + (int64_t)(kb + k) * N;
+                    const int pr = OUT32 ? 0 : (int)(gr & 1);
+                    const bool row_ok = q * 32 + 8 * h + kb + k < M;
+                    // whole words of the piece: [pr, (pr + pcols) / 2) for 16-bit elements, [0, pcols) for fp32
+                    const int wl = OUT32 ? pcols : ((pr + pcols) >> 1);
+                    uint32_t* wp = reinterpret_cast<uint32_t*>(C + (gr - pr) * ES);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int wi = lane + 32 * i;
+                        stg_b32_if(wp + wi, v[k][i], row_ok && wi >= pr && wi < wl);
+                    }
+                }
+            }
+            if (!OUT32 && (anyodd || (pcols & 1))) {
+                // half words at the ends: lane k (< 8) the odd first element of row k, lane 8 + k the last element of
+                // row k when the piece ends on half a word
+                const int k = lane & 7;
+                const bool tail = (lane & 8) != 0;
+                const int64_t gr = g0 + (int64_t)k * N;
+                const int pr = (int)(gr & 1);
+                const int endh = pr + pcols;                 // half words [pr, endh) of the row's words are the piece
+                const bool row_ok = q * 32 + 8 * h + k < M;
+                const int wi = tail ? (endh >> 1) : 0;       // word that is only half inside the piece
+                const bool need = lane < 16 && row_ok && (tail ? (endh & 1) != 0 : pr != 0);
+                const uint32_t word = lds_b32(qstrip + (uint32_t)(8 * h + k) * (UM_STRIP_PITCHW * 4) + 4u * (need ? wi : 0));
+                unsigned char* dst = C + (gr - pr) * 2 + 4 * (int64_t)wi + (tail ? 0 : 2);
+                stg_b16_if(dst, tail ? (word & 0xffffu) : (word >> 16), need);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(read_bar);  // my reads of the strip are done
+            ++pieces;
+            return true;
+        };
+        // the pieces of columns [c_lo, c_hi) of a chunk
+        auto store_cols = [&](int c_lo, int c_hi, auto tcol, auto pack, int64_t cbase, int M, int N, bool anyodd,
+                              auto loaded) -> bool {
+            for (int c0 = c_lo; c0 < c_hi; c0 += PC) {
+                const bool last = c0 + PC >= c_hi;
+                if (!store_piece(c0, min(PC, c_hi - c0), tcol, pack, cbase, M, N, anyodd, [&]() { if (last) loaded(); }))
+                    return false;
+            }
+            return true;
+        };
+        // pack(r, w) for an elementwise map of the accumulator values
+        auto pack_with = [](auto xform) {
+            return [xform](const uint32_t (&r)[32], auto& w) {
+                if constexpr (OUT32) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(xform(__uint_as_float(r[i])));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        w[i] = BlkCvt<Tag>::pack2(xform(__uint_as_float(r[2 * i])), xform(__uint_as_float(r[2 * i + 1])));
+                }
+            };
         };
         for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x, ++seq) {
             const int M = wk.it.M - wk.it.tm * UM_BM;  // rows of the segment from this block on
             const int N = wk.it.N;
             const int64_t cbase = (int64_t)wk.head * p.Dout + wk.it.offC + (int64_t)wk.it.tm * UM_BM * N;
+            // 16-bit rows that start on an odd element need the half-word shift while staging (chunks and pieces start
+            // on even columns, so a row's parity is the same for all of them); the quarter's warps hold the same rows
+            const bool anyodd = !OUT32 && __any_sync(0xffffffffu, (int)((cbase + (int64_t)myrow * N) & 1));
             volatile float* xm = xch + (seq & 1) * (2 * UM_SPLIT * 128);  // [part][row] maxima, then [UM_SPLIT + part][row] sums
             if (!softmax) {
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
@@ -344,14 +394,14 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                     if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 4, lim)) { ok = false; break; }
                     tc_fence_after();
                     const int ncols = min(N - ch * UM_BN, UM_BN);
-                    const int lo = h * CB, hi = min(lo + CB, ncols);
-                    if (lo < hi)
-                        store_cols(ch * UM_BN + lo, ch * UM_BN + hi,
-                                   [&](int c) { return (uint32_t)(buf * UM_BN + (c - ch * UM_BN)); },
-                                   [&](float x) { return x * sl; }, cbase, M, N);
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                    auto release = [&]() {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty_bar(buf));
+                    };
+                    ok = store_cols(ch * UM_BN, ch * UM_BN + ncols,
+                                    [&](int c) { return (uint32_t)(buf * UM_BN + (c - ch * UM_BN)); },
+                                    pack_with([sl](float x) { return x * sl; }), cbase, M, N, anyodd, release);
                 }
             } else if (wk.sweeps == 1) {
                 // whole row resident: chunk k of the row sits in accumulator (slot + k) & 1
@@ -363,7 +413,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                     return (uint32_t)((((slot + (c >> 8)) & 1) * UM_BN) + (c & (UM_BN - 1)));
                 };
                 uint32_t r[32];
-                // pass 1: maximum over this half's blocks
+                // pass 1: maximum over this warp's blocks
                 float mx = -INFINITY;
                 for (int b0 = h * CB; b0 < N; b0 += UM_BN) {
                     const int bend = min(b0 + CB, N);
@@ -371,8 +421,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                         tc_ld32(lane_addr + tcol(c), r);
                         if (c + 32 <= bend) {
 #pragma unroll
-                            for (int i = 0; i < 32; i += 2)
-                                mx = fmaxf(mx, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+                            for (int i = 0; i < 32; i += 2) mx = blk_max3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
                         } else {
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
@@ -404,21 +453,27 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 tc_wait_st();
                 float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
                 xm[(UM_SPLIT + h) * 128 + myrow] = sum;
+                tc_fence_before();   // the exponentials written above are read below by the other warps of the quarter
                 if (!pair_sync()) { ok = false; break; }
+                tc_fence_after();
                 sum = 0.f;
 #pragma unroll
                 for (int o = 0; o < UM_SPLIT; ++o) sum += xm[(UM_SPLIT + o) * 128 + myrow];
                 const float inv = __frcp_rn(sum);
-                // pass 3: normalise and store
-                for (int b0 = h * CB; b0 < N; b0 += UM_BN)
-                    store_cols(b0, min(b0 + CB, N), tcol, [&](float x) { return x * inv; }, cbase, M, N);
-                tc_fence_before();
-                __syncwarp();
-                for (int ch = 0; ch < wk.nchunks; ++ch)
-                    if (lane == 0) mbar_arrive(tempty_bar((slot + ch) & 1));
+                // pass 3: normalise and store; an accumulator goes back to the MMA role as soon as this warp has read its
+                // share of it, so the next item's products overlap the rest of this item's stores
+                for (int ch = 0; ok && ch < wk.nchunks; ++ch) {
+                    auto release = [&]() {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty_bar((slot + ch) & 1));
+                    };
+                    ok = store_cols(ch * UM_BN, min((ch + 1) * UM_BN, N), tcol, pack_with([inv](float x) { return x * inv; }),
+                                    cbase, M, N, anyodd, release);
+                }
                 slot += wk.nchunks;
             } else {
-                // two sweeps: running (max, sum) over this half's blocks, then recompute and store
+                // two sweeps: running (max, sum) over this warp's blocks, then recompute and store
                 float mx = -INFINITY, sum = 0.f;
                 uint32_t r[32];
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
@@ -437,8 +492,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                         }
                         float pm = -INFINITY;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2)
-                            pm = fmaxf(pm, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+                        for (int i = 0; i < 32; i += 2) pm = blk_max3(pm, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
                         const float mnew = fmaxf(mx, pm);  // finite: column c of the piece is inside the row
                         const float nm = -mnew * sl;
                         float s4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -454,7 +508,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 if (!ok) break;
                 xm[h * 128 + myrow] = mx;
                 xm[(UM_SPLIT + h) * 128 + myrow] = sum;
-                if (!pair_sync()) break;
+                if (!pair_sync()) { ok = false; break; }
                 {
                     float m = -INFINITY;
 #pragma unroll
@@ -472,14 +526,15 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                     if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 7, lim)) { ok = false; break; }
                     tc_fence_after();
                     const int ncols = min(N - ch * UM_BN, UM_BN);
-                    const int lo = h * CB, hi = min(lo + CB, ncols);
-                    if (lo < hi)
-                        store_cols(ch * UM_BN + lo, ch * UM_BN + hi,
-                                   [&](int c) { return (uint32_t)(buf * UM_BN + (c - ch * UM_BN)); },
-                                   [&](float x) { return blk_exp2(fmaf(x, sl, off)); }, cbase, M, N);
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                    auto release = [&]() {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty_bar(buf));
+                    };
+                    ok = store_cols(ch * UM_BN, ch * UM_BN + ncols,
+                                    [&](int c) { return (uint32_t)(buf * UM_BN + (c - ch * UM_BN)); },
+                                    pack_with([sl, off](float x) { return blk_exp2(fmaf(x, sl, off)); }), cbase, M, N, anyodd,
+                                    release);
                 }
             }
         }

@@ -7,7 +7,7 @@
 
 namespace {
 
-constexpr uint32_t BLK_UMMA_SPIN_LIMIT = 6u << 20;
+constexpr uint32_t BLK_UMMA_SPIN_LIMIT = 1u << 20;  // suspended waits of about 2 us each: a couple of seconds
 
 // ---- PTX wrappers -------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -28,14 +28,25 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// One suspended wait: the thread sleeps in hardware until the phase completes or about two microseconds pass,
+// whichever comes first, so a waiting role costs no issue slots.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred q;\n mbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2, %3;\n selp.u32 %0, 1, 0, q;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(2000u)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false when another role has already given up or when the bound is hit
 // (then the status word and the CTA's abort flag are set).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int code, uint32_t limit = BLK_UMMA_SPIN_LIMIT) {
+    if (mbar_test(bar, parity)) return true;
     for (uint32_t i = 0; i < limit; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if (i > 128) __nanosleep(64);
-        if ((i & 255u) == 255u && *abort_flag) return false;
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 7u) == 7u && *abort_flag) return false;
     }
     *abort_flag = 1;
     atomicCAS(status, 0, code);
