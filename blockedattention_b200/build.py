@@ -23,7 +23,7 @@ LIBDIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIBDIR, "libblkattn.so")
 
 SOURCES = ["blk_host.cpp", "blk_api.cu", "blk_gemm_tile.cu", "blk_gemm_simt.cu", "blk_scores_small.cu",
-           "blk_softmax.cu", "blk_softmax_pipe.cu", "blk_gemm_umma.cu", "blk_scores_pipe.cu", "blk_attn_umma.cu"]
+           "blk_softmax.cu", "blk_softmax_pipe.cu", "blk_gemm_umma.cu", "blk_scores_pipe.cu", "blk_attn_umma.cu", "blk_pv_umma.cu"]
 GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -67,6 +67,7 @@ int upload_plan(blk_plan* p) {
     add_vec(p->simt_items, &p->d_simt_items);
     for (int b = 0; b < BLK_SMALL_BUCKETS; ++b) add_vec(p->small_items[b], &p->d_small_items[b]);
     add_vec(p->umma_items, &p->d_umma_items);
+    add_vec(p->pv_items, &p->d_pv_items);
     add_vec(p->flash_items, &p->d_flash_items);
     add_vec(p->packs, &p->d_packs);
     add_vec(p->pack_blocks, &p->d_pack_blocks);
@@ -174,6 +175,7 @@ extern "C" int blk_gemm_plan_create(blk_plan_t** plan, const int64_t* M, const i
                           grid_ok((int64_t)p->smx_chunks.size(), H, "gemm plan") &&
                           grid_ok((int64_t)small_count(p), H, "gemm plan") &&
                           grid_ok((int64_t)p->umma_items.size(), H, "gemm plan") &&
+                          grid_ok((int64_t)p->pv_items.size(), H, "gemm plan") &&
                           grid_ok((int64_t)p->packs.size(), H, "gemm plan")))
         rc = BLK_ERR_UNSUPPORTED;
     if (rc == BLK_OK) rc = upload_plan(p);
@@ -263,7 +265,8 @@ extern "C" int blk_plan_offsets(const blk_plan_t* p, int64_t* a1, int64_t* a2, i
 
 static int launches_per_run(const blk_plan* p) {
     if (p->attn) return (p->flash_items.empty() ? 0 : 1) + (p->packs.empty() ? 0 : 1);
-    int n = (!p->tile_items.empty()) + (!p->simt_items.empty()) + (!p->umma_items.empty()) + (!p->smx_chunks.empty());
+    int n = (!p->tile_items.empty()) + (!p->simt_items.empty()) + (!p->umma_items.empty()) + (!p->smx_chunks.empty()) +
+            (!p->pv_items.empty());
     if (p->small_pipe) return n + 1;
     for (const auto& v : p->small_items) n += !v.empty();
     return n;
@@ -277,7 +280,7 @@ extern "C" int blk_plan_summary(const blk_plan_t* p, int64_t counts[8]) {
     counts[0] = p->S;
     counts[1] = (int64_t)small_count(p);
     counts[2] = (int64_t)p->tile_items.size();
-    counts[3] = (int64_t)(p->attn ? p->flash_items.size() : p->umma_items.size());
+    counts[3] = (int64_t)(p->attn ? p->flash_items.size() : p->umma_items.size() + p->pv_items.size());
     counts[4] = (int64_t)p->smx_chunks.size();
     counts[5] = p->H > 0 ? launches_per_run(p) : 0;
     counts[6] = (int64_t)p->simt_items.size();
@@ -647,6 +650,20 @@ static int gemm_run_impl(const blk_plan* p, const void* mat1, const void* mat2, 
                                       p->num_sms, st)) != cudaSuccess)
             return cuda_fail("tcgen05 GEMM launch", e);
     }
+    if (!p->pv_items.empty()) {
+        BlkPvParams vp{};
+        vp.A = mat1;
+        vp.C = out;
+        vp.items = p->d_pv_items;
+        vp.Dm1 = p->Dm1; vp.Dm2 = p->Dm2; vp.Dout = p->Dout;
+        vp.num_items = (int)p->pv_items.size();
+        vp.H = (int)p->H;
+        vp.D = p->pv_D;
+        vp.bf16 = p->dtype_in == BLK_BF16;
+        vp.scale = scale;
+        vp.status = p->d_status;
+        if ((e = blk_launch_pv_umma(vp, mat2, p->num_sms, st)) != cudaSuccess) return cuda_fail("tcgen05 P V launch", e);
+    }
     if (!p->tile_items.empty()) {
         BlkGemmParams gp{};
         gp.A = reinterpret_cast<const uint16_t*>(mat1);
@@ -687,7 +704,7 @@ extern "C" int blk_gemm_run_strided(const blk_plan_t* p, const void* mat1, int64
     // Only the kernels that fetch operands through tensor maps take strides: every segment must be on the
     // pack kernel or the tcgen05 kernel, which also means one contraction length for the whole batch.
     const bool small_ok = p->small_pipe || small_count(p) == 0;
-    if (!small_ok || !p->tile_items.empty() || !p->simt_items.empty()) {
+    if (!small_ok || !p->tile_items.empty() || !p->simt_items.empty() || !p->pv_items.empty()) {
         blk_set_error("blk_gemm_run_strided: this batch needs a kernel that reads packed operands only "
                       "(16-bit inputs, not transposed, packed offsets, one K that is a multiple of 64 are required)");
         return BLK_ERR_UNSUPPORTED;

@@ -296,6 +296,28 @@ int blk_build_gemm_schedule(blk_plan* p) {
         for (int64_t s = 0; s < S; ++s) all += (double)p->M[s] * (double)p->N[s] * (double)p->K[s];
         if (best < 0.1 * all && !blk_env_flag("BLK_FORCE_UMMA")) p->umma_K = 0;
     }
+    // The tcgen05 kernel for a second operand stored (K, D) -- the product of a probability block with the values --
+    // takes 16-bit segments whose second operand has D = 64 or 128 columns (one D per plan: the one carrying the
+    // most work), whose value rows are rows of the (rows, D) view of the strip and whose result rows are 16-byte
+    // aligned.  The first operand may have any row length and alignment.
+    const bool allow_pv = !blk_env_flag("BLK_DISABLE_UMMA") && p->dtype_in != BLK_F32 && p->dtype_out == p->dtype_in &&
+                          !p->ta && p->tb && p->epi == BLK_EPI_SCORES && p->Dm2 % 8 == 0 && p->Dout % 8 == 0 && !p->attn;
+    auto pv_candidate = [&](int64_t s, int64_t D) {
+        return allow_pv && p->N[s] == D && p->M[s] > 0 && p->K[s] > 0 && p->a2[s] % D == 0 && p->ao[s] % 8 == 0 &&
+               p->Dm2 / D < INT32_MAX;
+    };
+    p->pv_D = 0;
+    if (allow_pv) {
+        double w64 = 0, w128 = 0, all = 0;
+        for (int64_t s = 0; s < S; ++s) {
+            const double wk = (double)p->M[s] * (double)p->N[s] * (double)p->K[s];
+            all += wk;
+            if (pv_candidate(s, 64)) w64 += wk;
+            if (pv_candidate(s, 128)) w128 += wk;
+        }
+        const double best = std::max(w64, w128);
+        if (best > 0 && (best >= 0.1 * all || blk_env_flag("BLK_FORCE_UMMA"))) p->pv_D = w128 >= w64 ? 128 : 64;
+    }
     p->segs.resize(S);
     p->flops = p->bytes = 0;
     std::vector<int64_t> small_segs;  // segments of the small bin, in batch order
@@ -335,6 +357,12 @@ int blk_build_gemm_schedule(blk_plan* p) {
                 BlkSmallItem{sd.offA, sd.offB, sd.offC, (int32_t)m, (int32_t)n});
             continue;
         }
+        if (p->pv_D != 0 && pv_candidate(s, p->pv_D)) {
+            for (int64_t tm = 0; tm * BLK_UMMA_BM < m; ++tm)
+                p->pv_items.push_back(BlkPvItem{sd.offA + tm * BLK_UMMA_BM * k, sd.offC + tm * BLK_UMMA_BM * n,
+                                                (int32_t)(sd.offB / n), (int32_t)(m - tm * BLK_UMMA_BM), (int32_t)k, 0});
+            continue;
+        }
         if (p->umma_K != 0 && k == p->umma_K && umma_candidate(s)) {
             const int32_t tms = (int32_t)((m + BLK_UMMA_BM - 1) / BLK_UMMA_BM);
             for (int32_t tm = 0; tm < tms; ++tm)
@@ -356,6 +384,8 @@ int blk_build_gemm_schedule(blk_plan* p) {
     std::stable_sort(p->umma_items.begin(), p->umma_items.end(), [](const BlkUmmaItem& a, const BlkUmmaItem& b) {
         return (int64_t)std::min(a.M - a.tm * BLK_UMMA_BM, BLK_UMMA_BM) * a.N > (int64_t)std::min(b.M - b.tm * BLK_UMMA_BM, BLK_UMMA_BM) * b.N;
     });
+    // longest contractions first for the same reason
+    std::stable_sort(p->pv_items.begin(), p->pv_items.end(), [](const BlkPvItem& a, const BlkPvItem& b) { return a.K > b.K; });
     // K = 64 with 16-bit output: the small segments run on the pipelined kernel, grouped into packs of
     // consecutive segments whose operands are contiguous in memory (one bulk copy per operand per pack).
     p->small_pipe = 0;

@@ -98,6 +98,18 @@ struct BlkUmmaItem {
 };
 static_assert(sizeof(BlkUmmaItem) == 32, "BlkUmmaItem layout");
 
+// One work item of the tcgen05 kernel for the product with a (K, D) second operand (P V): a 128-row block of the
+// first operand of one segment.
+struct BlkPvItem {
+    int64_t offA;   // element offset of the block's first row inside a head strip of the first operand
+    int64_t offC;   // element offset of the block's first result row inside a head strip of the output
+    int32_t rowB;   // first row of the segment in the (rows, D) view of the second operand
+    int32_t M;      // rows of the segment from this block on (the block holds min(M, 128))
+    int32_t K;      // contraction length = row pitch of the first operand
+    int32_t pad;
+};
+static_assert(sizeof(BlkPvItem) == 32, "BlkPvItem layout");
+
 // One work item of the fused attention kernel for long segments: a 128-row block of the queries of a segment.
 struct BlkFlashItem {
     int32_t rowQ;   // first query row of the block in the (rows, d) view of q (and of the result)
@@ -139,6 +151,8 @@ struct blk_plan {
     std::vector<BlkTileItem> simt_items;    // fp32 SIMT kernel
     std::vector<BlkSmallItem> small_items[BLK_SMALL_BUCKETS];  // packed small-segment kernel, by column count
     std::vector<BlkUmmaItem> umma_items;    // tcgen05 kernel
+    std::vector<BlkPvItem> pv_items;        // tcgen05 kernel for transposed second operands of 64 or 128 columns
+    int pv_D = 0;                           // columns of that second operand
     std::vector<BlkSmxChunk> smx_chunks;    // softmax kernel (also second pass of fp32 scores)
     std::vector<BlkSmxWindow> smx_windows;  // pipelined softmax kernels: groups of chunks
     int64_t max_chunks = 0;                 // > 0: the softmax scheduler refuses batches that need more chunks
@@ -164,6 +178,7 @@ struct blk_plan {
     BlkSmallItem* d_small_items[BLK_SMALL_BUCKETS] = {nullptr, nullptr};
     int num_sms = 148;
     BlkUmmaItem* d_umma_items = nullptr;
+    BlkPvItem* d_pv_items = nullptr;
     BlkSmxChunk* d_smx_chunks = nullptr;
     BlkSmxWindow* d_smx_windows = nullptr;
     int* d_status = nullptr;

@@ -75,6 +75,19 @@ struct BlkUmmaParams {
     uint32_t spin_limit;
 };
 
+struct BlkPvParams {
+    const void* A;  // first operand: rows of K elements at arbitrary 2-byte offsets
+    void* C;
+    const BlkPvItem* items;
+    int64_t Dm1, Dm2, Dout;
+    int num_items;
+    int H;
+    int D;  // columns of the second operand and of the result: 64 or 128
+    int bf16;
+    float scale;
+    int* status;
+};
+
 struct BlkPackParams {
     const uint16_t* A;
     const uint16_t* B;
@@ -152,6 +165,7 @@ cudaError_t blk_launch_scores_small(const BlkSmallParams& p, int dtype_in, int K
 cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p, const void* A, const void* B, const BlkOperandLayout& layA,
                                  const BlkOperandLayout& layB,
                                  int sms, cudaStream_t st);
+cudaError_t blk_launch_pv_umma(const BlkPvParams& p, const void* V, int sms, cudaStream_t st);
 cudaError_t blk_launch_attn_umma(const BlkFlashParams& p, const void* q, const void* k, const void* v, int sms,
                                  cudaStream_t st);
 cudaError_t blk_launch_scores_pipe(const BlkPackParams& p, int dtype_in, int sms, cudaStream_t st);
