@@ -10,19 +10,27 @@
 //            tcgen05.mma (M = 128, N up to 256, K = 16 per instruction) into
 //            one of two 256-column accumulators; tcgen05.commit hands shared
 //            memory stages back to the producer and accumulators to the epilogue;
-//   warps 2-17 epilogue: a warp may read the 32 accumulator lanes (= rows) of its
-//            quarter; the four warps of a quarter each take 64 of every 256
+//   warps 2-9 epilogue arithmetic: a warp may read the 32 accumulator lanes (= rows)
+//            of its quarter; the two warps of a quarter each take 64 of every 128
 //            columns of the row and exchange partial row statistics through
 //            shared memory.  A thread reads its row 32 columns at a time
 //            (tcgen05.ld), applies the epilogue and writes the packed words into
-//            the quarter's strip (32 rows x 256 columns) at the position the row
-//            has in global memory modulo one 32-bit word; after a rendezvous of
-//            the quarter's warps each warp writes eight whole rows of the strip,
-//            a row being 512 contiguous bytes stored as four fully coalesced
-//            128-byte word stores (an odd first or last element goes out as a
-//            16-bit store).  Wide contiguous row pieces are what the memory
-//            system needs here: the same data written as 128-byte pieces with
-//            element-wise ragged edges runs at little more than half the rate.
+//            one of the quarter's two strips (32 rows x 128 columns each, used
+//            alternately), at the position the row has in global memory modulo
+//            one 32-bit word;
+//   warps 10-17 stores: one warp per quarter and strip.  It waits for the strip to
+//            be filled, writes its 32 rows to global memory -- a row piece is 256
+//            contiguous bytes stored as two fully coalesced 128-byte word stores;
+//            an odd first or last element goes out as a 16-bit store -- and hands
+//            the strip back.  Keeping the stores in warps of their own matters:
+//            a warp that alternates between exponentials and stores leaves the
+//            special-function unit idle whenever the memory system pushes back
+//            on its stores, and all warps of a CTA reach that point together;
+//            with separate warps the exponentials of one piece run while the
+//            previous piece drains (both alone and together they take the same
+//            time on this machine).  Wide contiguous row pieces matter as well:
+//            the same data written as 128-byte pieces with element-wise ragged
+//            edges runs at little more than half the rate.
 //
 // Epilogues.  Scores: scale and round.  Softmax with N <= 512: both
 // accumulators hold the whole row; pass 1 takes the row maximum, pass 2 writes
@@ -61,18 +69,29 @@ constexpr int UM_STAGES = 3;
 constexpr int UM_A_BYTES = UM_BM * UM_BK * 2;  // 16 KB
 constexpr int UM_B_BYTES = UM_BN * UM_BK * 2;  // 32 KB
 constexpr int UM_STAGE_BYTES = UM_A_BYTES + UM_B_BYTES;
-constexpr int UM_SPLIT = 4;                           // epilogue warps per accumulator-lane quarter
-constexpr int UM_EPI_WARPS = 4 * UM_SPLIT;
-constexpr int UM_THREADS = 64 + 32 * UM_EPI_WARPS;
-constexpr int UM_CB = UM_BN / UM_SPLIT;               // columns of a chunk owned by one of them
+constexpr int UM_SPLIT = 2;                           // arithmetic warps per accumulator-lane quarter
+constexpr int UM_EPI_WARPS = 4 * UM_SPLIT;            // arithmetic warps
+constexpr int UM_STORE_WARPS = 8;                     // one per quarter and strip
+constexpr int UM_THREADS = 64 + 32 * (UM_EPI_WARPS + UM_STORE_WARPS);
 constexpr int UM_PIECE = 32;                          // columns per tcgen05.ld
-constexpr int UM_PW = 128;                            // 32-bit words of an output row staged per flush (256 x 16-bit, 128 x fp32)
+constexpr int UM_PW = 64;                             // 32-bit words of a staged row piece (128 x 16-bit, 64 x fp32)
 // Strip row pitch in words: odd, so that the 32 row-owning lanes of a store (same word, consecutive rows) hit 32
 // different banks; a row holds UM_PW words plus the half word an odd first element pushes past the end.
 constexpr int UM_STRIP_PITCHW = UM_PW + 5;
-constexpr int UM_STRIP_BYTES = 32 * UM_STRIP_PITCHW * 4;  // per quarter (four epilogue warps share it)
+constexpr int UM_STRIP_BYTES = 32 * UM_STRIP_PITCHW * 4;  // one strip; a quarter has two
+// What the arithmetic warps tell the store warp about the piece in a strip.
+struct UmPiece {
+    int64_t g0;   // element index in the output of the piece's first element in the quarter's first row
+    int32_t N;    // row pitch of the output block
+    int32_t pcols;  // columns of the piece
+    int32_t rows;   // rows of the quarter inside the block (0..32)
+    int32_t halves; // a row may start or end on half a word
+    int32_t stop;   // no more pieces: the store warp leaves
+    int32_t pad;
+};
+static_assert(sizeof(UmPiece) == 32, "UmPiece layout");
 constexpr int UM_XCH_BYTES = 2 * 2 * UM_SPLIT * 128 * 4;  // row statistics exchanged between the two halves, double-buffered
-constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + 4 * UM_STRIP_BYTES + UM_XCH_BYTES + 512;
+constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + 8 * UM_STRIP_BYTES + UM_XCH_BYTES + 8 * 32 + 512;
 static_assert(UM_SMEM_BYTES <= 227 * 1024, "shared memory budget");
 static_assert(UM_STAGES <= 4, "barrier slots");
 
@@ -121,10 +140,11 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
         return;
     }
     unsigned char* strips = smem + UM_STAGES * UM_STAGE_BYTES;
-    float* xch = reinterpret_cast<float*>(strips + 4 * UM_STRIP_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(strips + 4 * UM_STRIP_BYTES + UM_XCH_BYTES);
+    float* xch = reinterpret_cast<float*>(strips + 8 * UM_STRIP_BYTES);
+    UmPiece* pieces_desc = reinterpret_cast<UmPiece*>(strips + 8 * UM_STRIP_BYTES + UM_XCH_BYTES);  // [quarter][strip]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(strips + 8 * UM_STRIP_BYTES + UM_XCH_BYTES + 8 * 32);
     // bars[0..3] full (UM_STAGES used), [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty; per quarter q:
-    // [16+q] rendezvous for the row statistics, [20+q] strip written, [24+q] strip read
+    // [16+q] rendezvous for the row statistics; per quarter and strip: [20 + 2q + b] strip filled, [28 + 2q + b] strip drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
 
@@ -146,7 +166,9 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
             mbar_init(tempty_bar(b), UM_EPI_WARPS);
         }
         *abort_flag = 0;
-        for (int i = 0; i < 12; ++i) mbar_init(bar0 + 8u * (16 + i), UM_SPLIT);  // one arrival per warp of the quarter
+        for (int i = 0; i < 4; ++i) mbar_init(bar0 + 8u * (16 + i), UM_SPLIT);   // one arrival per arithmetic warp of the quarter
+        for (int i = 0; i < 8; ++i) mbar_init(bar0 + 8u * (20 + i), UM_SPLIT);   // strip filled: its two arithmetic warps
+        for (int i = 0; i < 8; ++i) mbar_init(bar0 + 8u * (28 + i), 1);          // strip drained: its store warp
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
@@ -218,12 +240,70 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                     }
             }
         }
+    } else if (warp >= 2 + UM_EPI_WARPS) {
+        // ---------------- stores: warps 10..17, one per quarter and strip ----------------
+        const int sq = warp & 3, sb = (warp - 2 - UM_EPI_WARPS) >> 2;
+        const uint32_t strip = blk_smem_u32(strips + (sq * 2 + sb) * UM_STRIP_BYTES);
+        const uint32_t filled_bar = bar0 + 8u * (20 + sq * 2 + sb), drained_bar = bar0 + 8u * (28 + sq * 2 + sb);
+        const volatile UmPiece* desc = pieces_desc + sq * 2 + sb;
+        unsigned char* const C = reinterpret_cast<unsigned char*>(p.C);
+        constexpr int ES = OUT32 ? 4 : 2;
+        for (uint32_t n = 0;; ++n) {
+            if (!mbar_wait(filled_bar, n & 1u, abort_flag, p.status, 10, lim)) break;
+            if (desc->stop) break;
+            const int64_t g0 = desc->g0;
+            const int N = desc->N, pcols = desc->pcols, rows = desc->rows;
+            const bool halves = desc->halves != 0;
+            // lane l carries words l and l + 32 of a row: two stores of 128 contiguous bytes per row, four rows a batch
+            const uint32_t rbase = strip + 4u * lane;
+#pragma unroll 2
+            for (int kb = 0; kb < 32; kb += 4) {
+                if (kb >= rows) break;
+                uint32_t v[4][2];
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) v[k][i] = lds_b32(rbase + (uint32_t)(kb + k) * (UM_STRIP_PITCHW * 4) + 128u * i);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int64_t gr = g0 + (int64_t)(kb + k) * N;
+                    const int pr = OUT32 ? 0 : (int)(gr & 1);
+                    const bool row_ok = kb + k < rows;
+                    // whole words of the piece: [pr, (pr + pcols) / 2) for 16-bit elements, [0, pcols) for fp32
+                    const int wl = OUT32 ? pcols : ((pr + pcols) >> 1);
+                    uint32_t* wp = reinterpret_cast<uint32_t*>(C + (gr - pr) * ES);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int wi = lane + 32 * i;
+                        stg_b32_if(wp + wi, v[k][i], row_ok && wi >= pr && wi < wl);
+                    }
+                }
+            }
+            if (!OUT32 && halves) {
+                // half words at the ends: lane k the odd first element of row k, then the last element of row k when the
+                // piece ends on half a word
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    const bool tail = t != 0;
+                    const int64_t gr = g0 + (int64_t)lane * N;
+                    const int pr = (int)(gr & 1);
+                    const int endh = pr + pcols;                 // half words [pr, endh) of the row's words are the piece
+                    const int wi = tail ? (endh >> 1) : 0;       // word that is only half inside the piece
+                    const bool need = lane < rows && (tail ? (endh & 1) != 0 : pr != 0);
+                    const uint32_t word = lds_b32(strip + (uint32_t)lane * (UM_STRIP_PITCHW * 4) + 4u * (need ? wi : 0));
+                    unsigned char* dst = C + (gr - pr) * 2 + 4 * (int64_t)wi + (tail ? 0 : 2);
+                    stg_b16_if(dst, tail ? (word & 0xffffu) : (word >> 16), need);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(drained_bar);
+        }
     } else {
-        // ---------------- epilogue: warps 2..17 ----------------
-        // lane quarter q = warp % 4 (the 32 accumulator lanes a warp may read); the UM_SPLIT warps of a quarter
-        // split the columns (share h) and exchange their partial row statistics.
+        // ---------------- epilogue arithmetic: warps 2..9 ----------------
+        // lane quarter q = warp % 4 (the 32 accumulator lanes a warp may read); the two warps of a quarter split the
+        // columns (share h: the columns c of a chunk with (c mod PC) / SH == h) and exchange their partial row
+        // statistics.
         const int q = warp & 3, h = (warp - 2) >> 2;  // h in [0, UM_SPLIT)
-        const uint32_t qstrip = blk_smem_u32(strips + q * UM_STRIP_BYTES);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         const int myrow = q * 32 + lane;
         uint32_t slot = 0, seq = 0;
@@ -233,45 +313,44 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
         const float sl = softmax ? fabsf(p.scale) * BLK_LOG2E : p.scale;  // a negative softmax scale is applied by
                                                                           // the MMA (negated A), see instr_desc
         constexpr int ES = OUT32 ? 4 : 2;
-        constexpr int PC = UM_PW * 4 / ES;   // columns of a staged row piece: 256 x 16-bit or 128 x fp32
-        constexpr int CB = UM_CB;            // columns of a chunk owned by this warp in the statistics passes
-        constexpr int SH = PC / UM_SPLIT;    // columns of a staged piece this warp converts (32 words)
-        // Rendezvous of the warps of a quarter: an mbarrier that one lane of each warp arrives on, waited for like
+        constexpr int PC = UM_PW * 4 / ES;   // columns of a staged row piece: 128 x 16-bit or 64 x fp32
+        constexpr int SH = PC / UM_SPLIT;    // columns of a piece this warp converts (32 words)
+        // Rendezvous of the two warps of a quarter: an mbarrier that one lane of each warp arrives on, waited for like
         // every other barrier (suspended, bounded), so that a warp whose partner gave up cannot wait for ever.
-        auto quarter_sync = [&](uint32_t bar, uint32_t& phase) -> bool {
+        const uint32_t stat_bar = bar0 + 8u * (16 + q);
+        uint32_t stat_phase = 0;
+        auto pair_sync = [&]() -> bool {
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar);
-            const bool good = mbar_wait(bar, phase, abort_flag, p.status, 8, lim);
-            phase ^= 1u;
+            if (lane == 0) mbar_arrive(stat_bar);
+            const bool good = mbar_wait(stat_bar, stat_phase, abort_flag, p.status, 8, lim);
+            stat_phase ^= 1u;
             __syncwarp();
             return good;
         };
-        const uint32_t stat_bar = bar0 + 8u * (16 + q), written_bar = bar0 + 8u * (20 + q), read_bar = bar0 + 8u * (24 + q);
-        uint32_t stat_phase = 0, written_phase = 0;
-        uint32_t pieces = 0;  // pieces staged so far: piece n may be staged once all four warps have read piece n - 1
-        auto pair_sync = [&]() -> bool { return quarter_sync(stat_bar, stat_phase); };
+        uint32_t pieces = 0;  // pieces staged so far by this quarter: piece n goes into strip n & 1
 
-        // Store the piece of up to PC columns starting at column c0 of the 32 rows of this quarter.  tcol(c) gives the
-        // tensor-memory column of row column c; pack(r, w) turns 32 raw accumulator words into output words (32 fp32
-        // words, or 16 words of 16-bit pairs); loaded() runs right after this warp's last tensor-memory load of the
-        // piece, where the caller hands the accumulator back to the MMA role.
-        //   1. This warp converts columns [c0 + h SH, c0 + (h + 1) SH) of its lane's row and writes the words into the
-        //      row of the quarter's strip, at the word the element has in global memory: strip word j of a row holds the
-        //      output's 32-bit word (first word of the piece) + j.  A 16-bit piece that starts on an odd element is
-        //      shifted by half a word with a funnel shift through the previous pair; its first and last half words are
-        //      written as 16-bit stores, since the other half of those words belongs to the neighbouring warp.
-        //   2. Rendezvous; then this warp writes rows 8h .. 8h+7 of the strip: lane l carries words l, l + 32, l + 64,
-        //      l + 96 of the row, i.e. four stores of 128 contiguous bytes per row, and the half words at the two ends of
-        //      the eight rows go out in one 16-bit store by sixteen lanes.
+        // Stage the piece of up to PC columns starting at column c0 of the 32 rows of this quarter for its store warp.
+        // tcol(c) gives the tensor-memory column of row column c; pack(r, w) turns 32 raw accumulator words into
+        // output words (32 fp32 words, or 16 words of 16-bit pairs); loaded() runs right after this warp's last
+        // tensor-memory load of the piece, where the caller hands the accumulator back to the MMA role.  This warp
+        // converts columns [c0 + h SH, c0 + (h + 1) SH) of its lane's row and writes the words into the row of the
+        // strip, at the word the element has in global memory: strip word j of a row holds the output's 32-bit word
+        // (first word of the piece) + j.  A 16-bit piece that starts on an odd element is shifted by half a word with
+        // a funnel shift through the previous pair; its first and last half words are written as 16-bit stores, since
+        // the other half of those words belongs to the other warp.
         auto store_piece = [&](int c0, int pcols, auto tcol, auto pack, int64_t cbase, int M, int N, bool anyodd,
                                auto loaded) -> bool {
             uint32_t r[32];
+            const int sb = (int)(pieces & 1u);
+            const uint32_t strip = blk_smem_u32(strips + (q * 2 + sb) * UM_STRIP_BYTES);
+            const uint32_t filled_bar = bar0 + 8u * (20 + q * 2 + sb), drained_bar = bar0 + 8u * (28 + q * 2 + sb);
             const int64_t g = cbase + (int64_t)myrow * N + c0;       // element index of this lane's piece in the output
             const uint32_t par = OUT32 ? 0u : (uint32_t)(g & 1);
             [[maybe_unused]] const uint32_t par16 = par * 16u;
-            const uint32_t srow = qstrip + (uint32_t)lane * (UM_STRIP_PITCHW * 4) + (uint32_t)h * (SH * ES);  // word 32 h of my row
+            const uint32_t srow = strip + (uint32_t)lane * (UM_STRIP_PITCHW * 4) + (uint32_t)h * (SH * ES);  // word 32 h of my row
             const int mycols = min(SH, pcols - h * SH);              // columns of the piece this warp converts (<= 0: none)
-            if (pieces != 0 && !mbar_wait(read_bar, (pieces - 1) & 1u, abort_flag, p.status, 8, lim)) return false;
+            // the strip's previous piece (two pieces ago) has been written out
+            if (!mbar_wait(drained_bar, ((pieces >> 1) & 1u) ^ 1u, abort_flag, p.status, 8, lim)) return false;
             if (mycols <= 0) {
                 loaded();
             } else if constexpr (OUT32) {
@@ -298,7 +377,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                         for (int i = 0; i < 16; ++i) {
                             const uint32_t v = __funnelshift_l(prev, w[i], par16);
                             if (u == 0 && i == 0) {
-                                // the low half of my first word is the neighbouring warp's last element when the piece is odd
+                                // the low half of my first word is the other warp's last element when the piece is odd
                                 if (par) blk_sts_b16(a + 2, v >> 16);
                                 else blk_sts_b32(a, v);
                             } else {
@@ -310,50 +389,17 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 }
                 if (anyodd && par) blk_sts_b16(srow + 64 * nu, prev >> 16);  // my last element: low half of the next word
             }
-            if (!quarter_sync(written_bar, written_phase)) return false;
-            // ---- rows 8h .. 8h+7 of the strip -> global memory
-            unsigned char* C = reinterpret_cast<unsigned char*>(p.C);
-            const int64_t g0 = cbase + (int64_t)(q * 32 + 8 * h) * N + c0;   // element index of row 8h's piece
-            const uint32_t rbase = qstrip + (uint32_t)(8 * h) * (UM_STRIP_PITCHW * 4) + 4u * lane;
-#pragma unroll
-            for (int kb = 0; kb < 8; kb += 2) {
-                uint32_t v[2][4];
-#pragma unroll
-                for (int k = 0; k < 2; ++k)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) v[k][i] = lds_b32(rbase + (uint32_t)(kb + k) * (UM_STRIP_PITCHW * 4) + 128u * i);
-#pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    const int64_t gr = g0 + (int64_t)(kb + k) * N;
-                    const int pr = OUT32 ? 0 : (int)(gr & 1);
-                    const bool row_ok = q * 32 + 8 * h + kb + k < M;
-                    // whole words of the piece: [pr, (pr + pcols) / 2) for 16-bit elements, [0, pcols) for fp32
-                    const int wl = OUT32 ? pcols : ((pr + pcols) >> 1);
-                    uint32_t* wp = reinterpret_cast<uint32_t*>(C + (gr - pr) * ES);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int wi = lane + 32 * i;
-                        stg_b32_if(wp + wi, v[k][i], row_ok && wi >= pr && wi < wl);
-                    }
-                }
-            }
-            if (!OUT32 && (anyodd || (pcols & 1))) {
-                // half words at the ends: lane k (< 8) the odd first element of row k, lane 8 + k the last element of
-                // row k when the piece ends on half a word
-                const int k = lane & 7;
-                const bool tail = (lane & 8) != 0;
-                const int64_t gr = g0 + (int64_t)k * N;
-                const int pr = (int)(gr & 1);
-                const int endh = pr + pcols;                 // half words [pr, endh) of the row's words are the piece
-                const bool row_ok = q * 32 + 8 * h + k < M;
-                const int wi = tail ? (endh >> 1) : 0;       // word that is only half inside the piece
-                const bool need = lane < 16 && row_ok && (tail ? (endh & 1) != 0 : pr != 0);
-                const uint32_t word = lds_b32(qstrip + (uint32_t)(8 * h + k) * (UM_STRIP_PITCHW * 4) + 4u * (need ? wi : 0));
-                unsigned char* dst = C + (gr - pr) * 2 + 4 * (int64_t)wi + (tail ? 0 : 2);
-                stg_b16_if(dst, tail ? (word & 0xffffu) : (word >> 16), need);
+            if (h == 0 && lane == 0) {
+                volatile UmPiece* d = pieces_desc + q * 2 + sb;
+                d->g0 = cbase + (int64_t)(q * 32) * N + c0;
+                d->N = N;
+                d->pcols = pcols;
+                d->rows = max(0, min(M - q * 32, 32));
+                d->halves = (anyodd || (pcols & 1)) ? 1 : 0;
+                d->stop = 0;
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(read_bar);  // my reads of the strip are done
+            if (lane == 0) mbar_arrive(filled_bar);
             ++pieces;
             return true;
         };
@@ -415,8 +461,8 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 uint32_t r[32];
                 // pass 1: maximum over this warp's blocks
                 float mx = -INFINITY;
-                for (int b0 = h * CB; b0 < N; b0 += UM_BN) {
-                    const int bend = min(b0 + CB, N);
+                for (int b0 = h * SH; b0 < N; b0 += PC) {
+                    const int bend = min(b0 + SH, N);
                     for (int c = b0; c < bend; c += UM_PIECE) {
                         tc_ld32(lane_addr + tcol(c), r);
                         if (c + 32 <= bend) {
@@ -436,8 +482,8 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 const float nm = -mx * sl;
                 // pass 2: exponentials back into tensor memory, partial sum
                 float s4[4] = {0.f, 0.f, 0.f, 0.f};
-                for (int b0 = h * CB; b0 < N; b0 += UM_BN) {
-                    const int bend = min(b0 + CB, N);
+                for (int b0 = h * SH; b0 < N; b0 += PC) {
+                    const int bend = min(b0 + SH, N);
                     for (int c = b0; c < bend; c += UM_PIECE) {
                         tc_ld32(lane_addr + tcol(c), r);
 #pragma unroll
@@ -453,15 +499,14 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 tc_wait_st();
                 float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
                 xm[(UM_SPLIT + h) * 128 + myrow] = sum;
-                tc_fence_before();   // the exponentials written above are read below by the other warps of the quarter
                 if (!pair_sync()) { ok = false; break; }
-                tc_fence_after();
                 sum = 0.f;
 #pragma unroll
                 for (int o = 0; o < UM_SPLIT; ++o) sum += xm[(UM_SPLIT + o) * 128 + myrow];
                 const float inv = __frcp_rn(sum);
-                // pass 3: normalise and store; an accumulator goes back to the MMA role as soon as this warp has read its
-                // share of it, so the next item's products overlap the rest of this item's stores
+                // pass 3: normalise and stage (this warp reads back the columns it wrote in pass 2); an accumulator goes
+                // back to the MMA role as soon as this warp has read its share of it, so the next item's products overlap
+                // the rest of this item's epilogue
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch) {
                     auto release = [&]() {
                         tc_fence_before();
@@ -473,7 +518,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 }
                 slot += wk.nchunks;
             } else {
-                // two sweeps: running (max, sum) over this warp's blocks, then recompute and store
+                // two sweeps: running (max, sum) over this warp's blocks, then recompute and stage
                 float mx = -INFINITY, sum = 0.f;
                 uint32_t r[32];
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
@@ -481,25 +526,27 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                     if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 6, lim)) { ok = false; break; }
                     tc_fence_after();
                     const int ncols = min(N - ch * UM_BN, UM_BN);
-                    const int lo = h * CB, hi = min(lo + CB, ncols);
-                    for (int c = lo; c < hi; c += UM_PIECE) {
-                        tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c), r);
-                        const bool part = c + 32 > hi;
-                        if (part) {
+                    for (int b0 = h * SH; b0 < ncols; b0 += PC) {
+                        const int hi = min(b0 + SH, ncols);
+                        for (int c = b0; c < hi; c += UM_PIECE) {
+                            tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c), r);
+                            const bool part = c + 32 > hi;
+                            if (part) {
 #pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (c + i >= hi) r[i] = 0xff800000u;  // -inf
+                                for (int i = 0; i < 32; ++i)
+                                    if (c + i >= hi) r[i] = 0xff800000u;  // -inf
+                            }
+                            float pm = -INFINITY;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) pm = blk_max3(pm, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                            const float mnew = fmaxf(mx, pm);  // finite: column c of the piece is inside the row
+                            const float nm = -mnew * sl;
+                            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) s4[i & 3] += blk_exp2(fmaf(__uint_as_float(r[i]), sl, nm));
+                            sum = sum * blk_exp2((mx - mnew) * sl) + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+                            mx = mnew;
                         }
-                        float pm = -INFINITY;
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) pm = blk_max3(pm, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-                        const float mnew = fmaxf(mx, pm);  // finite: column c of the piece is inside the row
-                        const float nm = -mnew * sl;
-                        float s4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) s4[i & 3] += blk_exp2(fmaf(__uint_as_float(r[i]), sl, nm));
-                        sum = sum * blk_exp2((mx - mnew) * sl) + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
-                        mx = mnew;
                     }
                     tc_fence_before();
                     __syncwarp();
@@ -510,13 +557,17 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                 xm[(UM_SPLIT + h) * 128 + myrow] = sum;
                 if (!pair_sync()) { ok = false; break; }
                 {
+                    // a warp whose share held no column of the row (a last chunk of at most 64 columns) has maximum -inf
+                    // and sum 0: its term is skipped
                     float m = -INFINITY;
 #pragma unroll
                     for (int o = 0; o < UM_SPLIT; ++o) m = fmaxf(m, xm[o * 128 + myrow]);
                     float l = 0.f;
 #pragma unroll
-                    for (int o = 0; o < UM_SPLIT; ++o)
-                        l += xm[(UM_SPLIT + o) * 128 + myrow] * blk_exp2((xm[o * 128 + myrow] - m) * sl);
+                    for (int o = 0; o < UM_SPLIT; ++o) {
+                        const float mo = xm[o * 128 + myrow];
+                        if (mo != -INFINITY) l += xm[(UM_SPLIT + o) * 128 + myrow] * blk_exp2((mo - m) * sl);
+                    }
                     mx = m;
                     sum = l;
                 }
@@ -537,6 +588,16 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                                     release);
                 }
             }
+        }
+        // tell the quarter's two store warps that nothing follows: one more "piece" per strip that only says stop
+        for (int t = 0; t < 2; ++t) {
+            const int sb = (int)(pieces & 1u);
+            const uint32_t filled_bar = bar0 + 8u * (20 + q * 2 + sb), drained_bar = bar0 + 8u * (28 + q * 2 + sb);
+            if (ok && !mbar_wait(drained_bar, ((pieces >> 1) & 1u) ^ 1u, abort_flag, p.status, 8, lim)) ok = false;
+            if (h == 0 && lane == 0) (pieces_desc + q * 2 + sb)->stop = 1;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(filled_bar);
+            ++pieces;
         }
     }
 
