@@ -47,7 +47,7 @@ sys.path.insert(0, ROOT)
 
 DEFAULT_WORKLOAD = "long_tail"
 SUB_WORKLOADS = ("molecular", "general_gemm", "full_forward", "large_k", "long_tail_attention",
-                 "full_forward_attention")
+                 "full_forward_attention", "long_tail_softmax")
 MIN_TIMED_MS = 200.0          # every device-timed region lasts at least this long, whatever --steps says
 CPU_SAMPLE_FLOPS = 2e10       # algorithmic flops of the segment sample one CPU pass works through
 
@@ -287,7 +287,21 @@ class Runner:
         from blockedattention_b200.plan import AttentionPlan, GemmPlan
         self.w, self.dev = w, dev
         self.fused_attn = bool(w.extra.get("fused_attention"))
+        self.softmax_only = bool(w.extra.get("softmax_only"))
         t0 = time.perf_counter()
+        if self.softmax_only:
+            from blockedattention_b200.plan import SoftmaxPlan
+            self.plan = SoftmaxPlan(w.M, w.N, w.H, w.dtype, device=dev)
+            self.plan_pv = None
+            g = torch.Generator(device=dev)
+            g.manual_seed(seed)
+            self.sets = []
+            for i in range(max(1, nbuf)):
+                src = (torch.randn((w.H, self.plan.D), generator=g, device=dev, dtype=torch.float32) * w.std).to(w.dtype)
+                self.sets.append(((src,), torch.empty_like(src), None))
+            self.plan_ms_first = (time.perf_counter() - t0) * 1e3
+            self.launches_per_step = self.plan.summary["launches"] or 1
+            return
         if self.fused_attn:
             self.plan = AttentionPlan(w.M, w.N, w.H, w.dtype, device=dev, d=int(w.K[0]) if w.S else 64)
         else:
@@ -308,6 +322,9 @@ class Runner:
     def step(self, i):
         w = self.w
         ins, out, o2 = self.sets[i % len(self.sets)]
+        if self.softmax_only:
+            self.plan.run(ins[0], out=out, scale=w.scale)
+            return
         if self.fused_attn:
             self.plan.run(ins[0], ins[1], ins[2], out=o2, scale=w.scale)
             return
@@ -317,6 +334,8 @@ class Runner:
 
     def kernel_name(self):
         s = self.plan.summary
+        if self.softmax_only:
+            return "blk_softmax_pipe_kernel"
         if self.fused_attn:
             return "blk_attn_umma_kernel" if s["umma_items"] else "blk_scores_pipe_kernel"
         small = "blk_scores_pipe_kernel" if s["packs"] else "blk_scores_small_kernel"
@@ -490,6 +509,8 @@ def main():
     w = base.take(mine) if world > 1 else base
 
     run = Runner(w, dev, args.nbuf, seed=args.seed + 1000 * rank)
+    if run.softmax_only:   # a device-side line only: this workload has no operands to bring from the host
+        args.no_e2e = args.no_cpu = True
     sampler = ClockSampler(local)
     sampler.start()
     t_wall0 = time.perf_counter()
@@ -506,7 +527,7 @@ def main():
 
     # ---- cost of a new list set: cold plan creation (host schedule + allocation + upload) ------------
     plan_ms = None
-    if not run.fused_attn:
+    if not run.fused_attn and not run.softmax_only:
         ts = []
         for _ in range(5):
             torch.cuda.synchronize()
@@ -605,7 +626,7 @@ def main():
     sampler.stop()
 
     gather = None
-    if args.gather and world > 1 and not run.fused_attn and not w.d_v:
+    if args.gather and world > 1 and not run.fused_attn and not run.softmax_only and not w.d_v:
         outs = run.sets[0][1]
         full = torch.empty((base.H, base.Dout), dtype=outs.dtype, device=dev)
         partition.gather_output(outs, base.M * base.N, owner, base.H, out=full)   # warm-up (connections)

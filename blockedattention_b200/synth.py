@@ -51,6 +51,8 @@ class Workload:
         return int((self.M * self.N).sum())
 
     def flops(self) -> float:
+        if self.extra.get("softmax_only"):
+            return 0.0
         f = 2.0 * self.H * float((self.M * self.N * self.K).sum())
         if self.d_v:
             f += 2.0 * self.H * float((self.M * self.N).sum()) * self.d_v
@@ -59,6 +61,8 @@ class Workload:
     def bytes(self) -> float:
         ei = torch.empty((), dtype=self.dtype).element_size()
         eo = torch.empty((), dtype=self.out_dtype).element_size()
+        if self.extra.get("softmax_only"):     # the score buffer read once and written once
+            return 2.0 * self.H * float((self.M * self.N).sum()) * eo
         if self.extra.get("fused_attention"):  # q, k, v read, O written; P never exists
             return self.H * ei * (float(((self.M + self.N) * self.K).sum()) + float((self.N + self.M).sum()) * self.d_v)
         b = self.H * (float(((self.M + self.N) * self.K).sum()) * ei + float((self.M * self.N).sum()) * eo)
@@ -145,6 +149,11 @@ def workload(name: str, seed: int = 0, segments: Optional[int] = None) -> Worklo
         return Workload(name, b.M, b.N, b.K, b.H, b.dtype, b.dtype, b.scale, True, "normal", std=b.std, d_v=dv,
                         note=b.note.replace(", P then P@V", "") + ", fused softmax(QK^T)V without materialising P",
                         extra={"fused_attention": True})
+    if name.endswith("_softmax"):
+        # the standalone row softmax over the score buffer of a batch (the second of upstream's two operators)
+        b = workload(name[:-len("_softmax")], seed, segments)
+        return Workload(name, b.M, b.N, b.K, b.H, b.out_dtype, b.out_dtype, 1.0, True, "normal", std=2.0,
+                        note=b.note + ", standalone row softmax of its score buffer", extra={"softmax_only": True})
     if name == "large_k":
         S = segments or 64
         n = _i64(rs.randint(1024, 2049, size=S))
@@ -155,4 +164,5 @@ def workload(name: str, seed: int = 0, segments: Optional[int] = None) -> Worklo
 
 
 WORKLOADS = ("cpu_plumbing", "molecular", "molecular_attention", "general_gemm", "long_tail", "full_forward", "large_k",
-             "long_tail_attention", "full_forward_attention")
+             "long_tail_attention", "full_forward_attention", "long_tail_softmax", "full_forward_softmax",
+             "molecular_softmax")
