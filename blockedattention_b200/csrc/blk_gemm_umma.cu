@@ -71,7 +71,10 @@ constexpr int UM_B_BYTES = UM_BN * UM_BK * 2;  // 32 KB
 constexpr int UM_STAGE_BYTES = UM_A_BYTES + UM_B_BYTES;
 constexpr int UM_SPLIT = 2;                           // arithmetic warps per accumulator-lane quarter
 constexpr int UM_EPI_WARPS = 4 * UM_SPLIT;            // arithmetic warps
-constexpr int UM_STORE_WARPS = 8;                     // one per quarter and strip
+#ifndef UM_STORE_WARPS_N
+#define UM_STORE_WARPS_N 4
+#endif
+constexpr int UM_STORE_WARPS = UM_STORE_WARPS_N;      // 4: one per quarter; 8: one per quarter and strip
 constexpr int UM_THREADS = 64 + 32 * (UM_EPI_WARPS + UM_STORE_WARPS);
 constexpr int UM_PIECE = 32;                          // columns per tcgen05.ld
 constexpr int UM_PW = 64;                             // 32-bit words of a staged row piece (128 x 16-bit, 64 x fp32)
@@ -90,6 +93,7 @@ struct UmPiece {
     int32_t pad;
 };
 static_assert(sizeof(UmPiece) == 32, "UmPiece layout");
+constexpr int PCOLS16 = UM_PW * 2;                    // columns of a whole 16-bit piece
 constexpr int UM_XCH_BYTES = 2 * 2 * UM_SPLIT * 128 * 4;  // row statistics exchanged between the two halves, double-buffered
 constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + 8 * UM_STRIP_BYTES + UM_XCH_BYTES + 8 * 32 + 512;
 static_assert(UM_SMEM_BYTES <= 227 * 1024, "shared memory budget");
@@ -102,8 +106,13 @@ struct Work {
     int sweeps;
 };
 
+// Work w of a CTA's walk (w = blockIdx.x + k gridDim.x in round k).  Odd rounds run through the CTAs backwards, so
+// that with the items sorted by cost no CTA always gets the heaviest of a round.  Only the last round can point past
+// the end, so a CTA that gets nothing there has nothing left either.
 __device__ __forceinline__ bool next_work(const BlkUmmaParams& p, uint32_t w, Work& wk) {
     const uint32_t total = (uint32_t)p.num_items * (uint32_t)p.H;
+    const uint32_t round = w / gridDim.x;
+    if (round & 1u) w = round * gridDim.x + (gridDim.x - 1u - (w - round * gridDim.x));
     if (w >= total) return false;
     const uint32_t item = w / (uint32_t)p.H;
     wk.head = (int)(w - item * (uint32_t)p.H);
@@ -242,20 +251,49 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
         }
     } else if (warp >= 2 + UM_EPI_WARPS) {
         // ---------------- stores: warps 10..17, one per quarter and strip ----------------
-        const int sq = warp & 3, sb = (warp - 2 - UM_EPI_WARPS) >> 2;
-        const uint32_t strip = blk_smem_u32(strips + (sq * 2 + sb) * UM_STRIP_BYTES);
-        const uint32_t filled_bar = bar0 + 8u * (20 + sq * 2 + sb), drained_bar = bar0 + 8u * (28 + sq * 2 + sb);
-        const volatile UmPiece* desc = pieces_desc + sq * 2 + sb;
+        const int sq = warp & 3;
         unsigned char* const C = reinterpret_cast<unsigned char*>(p.C);
         constexpr int ES = OUT32 ? 4 : 2;
         for (uint32_t n = 0;; ++n) {
-            if (!mbar_wait(filled_bar, n & 1u, abort_flag, p.status, 10, lim)) break;
+            // with one store warp per quarter it takes the quarter's pieces in order, piece m from strip m & 1; with
+            // two, each warp owns a strip
+            const int sb = UM_STORE_WARPS == 4 ? (int)(n & 1u) : ((warp - 2 - UM_EPI_WARPS) >> 2);
+            const uint32_t use = UM_STORE_WARPS == 4 ? (n >> 1) : n;   // how often the strip has been used before
+            const uint32_t strip = blk_smem_u32(strips + (sq * 2 + sb) * UM_STRIP_BYTES);
+            const uint32_t filled_bar = bar0 + 8u * (20 + sq * 2 + sb), drained_bar = bar0 + 8u * (28 + sq * 2 + sb);
+            const volatile UmPiece* desc = pieces_desc + sq * 2 + sb;
+            if (!mbar_wait(filled_bar, use & 1u, abort_flag, p.status, 10, lim)) break;
             if (desc->stop) break;
             const int64_t g0 = desc->g0;
             const int N = desc->N, pcols = desc->pcols, rows = desc->rows;
             const bool halves = desc->halves != 0;
             // lane l carries words l and l + 32 of a row: two stores of 128 contiguous bytes per row, four rows a batch
             const uint32_t rbase = strip + 4u * lane;
+            if (!OUT32 && pcols == PCOLS16 && rows == 32) {
+                // A whole piece (the common case), with as few instructions per row as it takes: the store warps share
+                // their scheduler's issue slots with the arithmetic warps, and a row costing twenty instructions here
+                // made the second sweep issue bound.  Row k starts at element g0 + k N: at word (t >> 1) past the word
+                // of g0 with t = (g0 & 1) + k N, on its odd half when t is odd.  Words 1..63 of the row are whole; word 0
+                // is whole when the row starts on an even element (its upper half goes out below otherwise), and so does
+                // the lower half of word 64.
+                uint32_t* const w0 = reinterpret_cast<uint32_t*>(C) + (g0 >> 1) + lane;
+                uint32_t t = (uint32_t)(g0 & 1);
+#pragma unroll 2
+                for (int kb = 0; kb < 32; kb += 4) {
+                    uint32_t v[4][2];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) v[k][i] = lds_b32(rbase + (uint32_t)(kb + k) * (UM_STRIP_PITCHW * 4) + 128u * i);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint32_t* wp = w0 + (t >> 1);
+                        stg_b32_if(wp, v[k][0], lane >= (int)(t & 1u));
+                        asm volatile("st.global.b32 [%0], %1;\n" ::"l"(wp + 32), "r"(v[k][1]) : "memory");
+                        t += (uint32_t)N;
+                    }
+                }
+            } else
 #pragma unroll 2
             for (int kb = 0; kb < 32; kb += 4) {
                 if (kb >= rows) break;
