@@ -348,8 +348,9 @@ def blockAttnScoresTokenMajor(q: torch.Tensor, k: torch.Tensor, nList, scale: fl
     """``blockAttnScores`` for the layout attention inputs usually arrive in: ``q, k -> (sum n_s, H, d)``, the tokens
     of all segments in batch order.  The operands are read in place through strided tensor maps -- no permuted copy
     into head-major strips is made -- and the result is the packed head-major ``(H, sum n_s^2)`` buffer of
-    ``blockAttnScores``.  Needs 16-bit inputs and ``d`` a multiple of 64 (``d = 64`` when the batch has segments of
-    at most 64 tokens).  Forward only."""
+    ``blockAttnScores``.  Needs 16-bit inputs and ``d`` a multiple of 8 (16-byte rows for the tensor maps); with ``d = 32`` a batch
+    with hundreds of segments of at most 64 tokens is refused (those run on a kernel that reads packed strips only).
+    Forward only."""
     _check_operand("q", q)
     _check_operand("k", k)
     if q.dim() != 3 or q.shape != k.shape:

@@ -636,7 +636,6 @@ static int gemm_run_impl(const blk_plan* p, const void* mat1, const void* mat2, 
         up.Dout = p->Dout;
         up.num_items = (int)p->umma_items.size();
         up.H = (int)p->H;
-        up.K = p->umma_K;
         up.bf16 = p->dtype_in == BLK_BF16;
         up.out_f32 = p->dtype_out == BLK_F32;
         up.epi = p->epi;
@@ -646,8 +645,9 @@ static int gemm_run_impl(const blk_plan* p, const void* mat1, const void* mat2, 
             up.stall = 1;
             up.spin_limit = 4096;
         }
-        if ((e = blk_launch_gemm_umma(up, mat1, mat2, layout(layA, p->Dm1, p->umma_K), layout(layB, p->Dm2, p->umma_K),
-                                      p->num_sms, st)) != cudaSuccess)
+        const BlkUmmaOperand opA{mat1, p->Dm1, p->umma_viewsA.data(), (int)p->umma_viewsA.size(), layA};
+        const BlkUmmaOperand opB{mat2, p->Dm2, p->umma_viewsB.data(), (int)p->umma_viewsB.size(), layB};
+        if ((e = blk_launch_gemm_umma(up, opA, opB, p->num_sms, st)) != cudaSuccess)
             return cuda_fail("tcgen05 GEMM launch", e);
     }
     if (!p->pv_items.empty()) {
@@ -706,11 +706,11 @@ extern "C" int blk_gemm_run_strided(const blk_plan_t* p, const void* mat1, int64
     const bool small_ok = p->small_pipe || small_count(p) == 0;
     if (!small_ok || !p->tile_items.empty() || !p->simt_items.empty() || !p->pv_items.empty()) {
         blk_set_error("blk_gemm_run_strided: this batch needs a kernel that reads packed operands only "
-                      "(16-bit inputs, not transposed, packed offsets, one K that is a multiple of 64 are required)");
+                      "(16-bit inputs, not transposed, packed offsets, one K that is a multiple of 8 are required)");
         return BLK_ERR_UNSUPPORTED;
     }
     const int64_t K = p->small_pipe ? 64 : p->umma_K;
-    if (K <= 0 || (p->small_pipe && p->umma_K > 0 && p->umma_K != 64)) {
+    if (K <= 0 || (p->small_pipe && p->umma_K != 0 && p->umma_K != 64)) {
         blk_set_error("blk_gemm_run_strided: the batch does not have one contraction length");
         return BLK_ERR_UNSUPPORTED;
     }

@@ -104,6 +104,13 @@ struct Work {
     int head;
     int nchunks;
     int sweeps;
+    int nkb;     // k-blocks of UM_BK; the last may be short (the tensor map fills what lies past K with zeros)
+};
+
+// The tensor maps of the operands' views (BlkUmmaView), passed as one kernel parameter.
+struct UmMaps {
+    CUtensorMap a[BLK_UMMA_VIEWS];
+    CUtensorMap b[BLK_UMMA_VIEWS];
 };
 
 // Work w of a CTA's walk (w = blockIdx.x + k gridDim.x in round k).  Odd rounds run through the CTAs backwards, so
@@ -118,6 +125,7 @@ __device__ __forceinline__ bool next_work(const BlkUmmaParams& p, uint32_t w, Wo
     wk.head = (int)(w - item * (uint32_t)p.H);
     wk.it = p.items[item];
     wk.nchunks = (wk.it.N + UM_BN - 1) / UM_BN;
+    wk.nkb = (wk.it.K + UM_BK - 1) / UM_BK;
     wk.sweeps = (p.epi == BLK_EPI_SOFTMAX && wk.nchunks > 2) ? 2 : 1;
     return true;
 }
@@ -140,8 +148,7 @@ __device__ __forceinline__ uint32_t lds_b32(uint32_t addr) {
 
 template <typename Tag, bool OUT32>
 __global__ void __launch_bounds__(UM_THREADS, 1)
-blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap mapA,
-                     const __grid_constant__ CUtensorMap mapB) {
+blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps) {
     extern __shared__ __align__(1024) unsigned char um_smem_raw[];  // the swizzled tiles need a 1024-byte aligned base
     unsigned char* smem = um_smem_raw;
     if (blk_smem_u32(smem) & 1023u) {  // cannot happen with the alignment above; checked because the swizzle relies on it
@@ -189,7 +196,6 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const int nkb = p.K / UM_BK;
     const uint32_t lim = p.spin_limit ? p.spin_limit : BLK_UMMA_SPIN_LIMIT;
 
     if (warp == 0) {
@@ -202,15 +208,15 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
             for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x) {
                 for (int sw = 0; ok && sw < wk.sweeps; ++sw)
                     for (int ch = 0; ok && ch < wk.nchunks; ++ch)
-                        for (int kb = 0; kb < nkb; ++kb) {
+                        for (int kb = 0; kb < wk.nkb; ++kb) {
                             if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, lim)) { ok = false; break; }
                             const uint32_t sA = smem_u32 + stage * UM_STAGE_BYTES, sB = sA + UM_A_BYTES;
                             mbar_expect_tx(full_bar(stage), UM_STAGE_BYTES);
                             // coordinates (k, row, head), or (k, head, row) for a token-major operand
                             const int rA = wk.it.rowA, rB = wk.it.rowB + ch * UM_BN;
-                            tma_load_3d(sA, &mapA, full_bar(stage), kb * UM_BK, p.head_firstA ? wk.head : rA,
+                            tma_load_3d(sA, &maps.a[wk.it.views & 255], full_bar(stage), kb * UM_BK, p.head_firstA ? wk.head : rA,
                                         p.head_firstA ? rA : wk.head);
-                            tma_load_3d(sB, &mapB, full_bar(stage), kb * UM_BK, p.head_firstB ? wk.head : rB,
+                            tma_load_3d(sB, &maps.b[wk.it.views >> 8], full_bar(stage), kb * UM_BK, p.head_firstB ? wk.head : rB,
                                         p.head_firstB ? rB : wk.head);
                             if (++stage == UM_STAGES) { stage = 0; phase ^= 1u; }
                         }
@@ -232,14 +238,17 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ CUtensorMap 
                         const int ncols = min(wk.it.N - ch * UM_BN, UM_BN);
                         const uint32_t idesc = instr_desc(p.bf16, (ncols + 15) & ~15, p.epi == BLK_EPI_SOFTMAX && p.scale < 0.f);
                         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * UM_BN);
-                        for (int kb = 0; kb < nkb; ++kb) {
+                        for (int kb = 0; kb < wk.nkb; ++kb) {
                             if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, lim)) { ok = false; break; }
                             tc_fence_after();
                             const uint32_t sA = smem_u32 + stage * UM_STAGE_BYTES, sB = sA + UM_A_BYTES;
+                            // steps of 16 along k in this block: all four, or as many as reach the end of a short last block
+                            const int ksteps = min(UM_BK / 16, (wk.it.K - kb * UM_BK + 15) / 16);
 #pragma unroll
                             for (int k = 0; k < UM_BK / 16; ++k)
-                                tc_mma_f16(d_tmem, smem_desc_sw128(sA + 32 * k), smem_desc_sw128(sB + 32 * k), idesc,
-                                           (kb | k) != 0);
+                                if (k < ksteps)
+                                    tc_mma_f16(d_tmem, smem_desc_sw128(sA + 32 * k), smem_desc_sw128(sB + 32 * k), idesc,
+                                               (kb | k) != 0);
                             tc_commit(empty_bar(stage));  // stage reusable once these products have read it
                             if (++stage == UM_STAGES) { stage = 0; phase ^= 1u; }
                         }
@@ -672,13 +681,13 @@ EncodeTiledFn encode_fn() {
 }
 
 template <typename Tag, bool OUT32>
-cudaError_t launch(const BlkUmmaParams& p, const CUtensorMap& a, const CUtensorMap& b, int sms, cudaStream_t st) {
+cudaError_t launch(const BlkUmmaParams& p, const UmMaps& maps, int sms, cudaStream_t st) {
     auto kern = blk_gemm_umma_kernel<Tag, OUT32>;
     cudaError_t e = blk_func_smem(reinterpret_cast<const void*>(kern), UM_SMEM_BYTES);
     if (e != cudaSuccess) return e;
     const int64_t total = (int64_t)p.num_items * p.H;
     const dim3 grid((unsigned)(total < sms ? total : sms)), block(UM_THREADS);
-    kern<<<grid, block, UM_SMEM_BYTES, st>>>(p, a, b);
+    kern<<<grid, block, UM_SMEM_BYTES, st>>>(p, maps);
     return cudaGetLastError();
 }
 
@@ -764,14 +773,94 @@ cudaError_t blk_func_smem(const void* kern, int bytes) {
     return cudaSuccess;
 }
 
-cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p_in, const void* A, const void* B, const BlkOperandLayout& layA,
-                                 const BlkOperandLayout& layB, int sms, cudaStream_t st) {
+// The maps of a launch are remembered as a set under everything they depend on (buffers, strip lengths, views,
+// layouts): a plan is run many times on a few sets of buffers, and encoding up to 48 maps costs more than the launch.
+namespace {
+struct LaunchKey {
+    const void *a, *b;
+    int64_t Da, Db, H;
+    int na, nb, bf16, ga, gb;
+    BlkOperandLayout layA, layB;
+    BlkUmmaView va[BLK_UMMA_VIEWS], vb[BLK_UMMA_VIEWS];
+};
+struct LaunchSlot { LaunchKey key; UmMaps maps; int hfA, hfB; uint64_t stamp; bool used; };
+constexpr int LAUNCH_SLOTS = 8;
+LaunchSlot g_launch_slots[LAUNCH_SLOTS];
+uint64_t g_launch_clock = 0;
+std::mutex g_launch_mu;
+bool same_key(const LaunchKey& x, const LaunchKey& y) {
+    if (x.a != y.a || x.b != y.b || x.Da != y.Da || x.Db != y.Db || x.H != y.H || x.na != y.na || x.nb != y.nb ||
+        x.bf16 != y.bf16 || x.ga != y.ga || x.gb != y.gb)
+        return false;
+    auto lay_eq = [](const BlkOperandLayout& p, const BlkOperandLayout& q) {
+        return p.rows == q.rows && p.row_stride == q.row_stride && p.head_stride == q.head_stride;
+    };
+    if ((x.ga && !lay_eq(x.layA, y.layA)) || (x.gb && !lay_eq(x.layB, y.layB))) return false;
+    for (int i = 0; i < x.na; ++i)
+        if (x.va[i].K != y.va[i].K || x.va[i].residue != y.va[i].residue) return false;
+    for (int i = 0; i < x.nb; ++i)
+        if (x.vb[i].K != y.vb[i].K || x.vb[i].residue != y.vb[i].residue) return false;
+    return true;
+}
+}  // namespace
+
+cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p_in, const BlkUmmaOperand& A, const BlkUmmaOperand& B, int sms,
+                                 cudaStream_t st) {
     if ((int64_t)p_in.num_items * p_in.H == 0) return cudaSuccess;
+    if (A.num_views < 1 || B.num_views < 1 || A.num_views > BLK_UMMA_VIEWS || B.num_views > BLK_UMMA_VIEWS) return cudaErrorInvalidValue;
     BlkUmmaParams p = p_in;
-    CUtensorMap mapA, mapB;
-    if (!blk_make_row_map(&mapA, A, p.bf16, p.K, p.H, layA, UM_BK, UM_BM, &p.head_firstA) ||
-        !blk_make_row_map(&mapB, B, p.bf16, p.K, p.H, layB, UM_BK, UM_BN, &p.head_firstB))
-        return cudaErrorInvalidValue;
-    if (p.bf16) return p.out_f32 ? launch<BlkBf16Tag, true>(p, mapA, mapB, sms, st) : launch<BlkBf16Tag, false>(p, mapA, mapB, sms, st);
-    return p.out_f32 ? launch<BlkHalfTag, true>(p, mapA, mapB, sms, st) : launch<BlkHalfTag, false>(p, mapA, mapB, sms, st);
+    static thread_local LaunchKey key;   // these are kilobytes: not on the stack of a caller's thread
+    static thread_local UmMaps maps;
+    key.a = A.base; key.b = B.base; key.Da = A.D; key.Db = B.D; key.H = p.H;
+    key.na = A.num_views; key.nb = B.num_views; key.bf16 = p.bf16;
+    key.ga = A.given != nullptr; key.gb = B.given != nullptr;
+    if (A.given) key.layA = *A.given;
+    if (B.given) key.layB = *B.given;
+    for (int i = 0; i < A.num_views; ++i) key.va[i] = A.views[i];
+    for (int i = 0; i < B.num_views; ++i) key.vb[i] = B.views[i];
+    bool hit = false;
+    {
+        std::lock_guard<std::mutex> g(g_launch_mu);
+        for (LaunchSlot& sl : g_launch_slots)
+            if (sl.used && same_key(sl.key, key)) {
+                sl.stamp = ++g_launch_clock;
+                maps = sl.maps;
+                p.head_firstA = sl.hfA;
+                p.head_firstB = sl.hfB;
+                hit = true;
+                break;
+            }
+    }
+    if (!hit) {
+        // every view of an operand has the same order of its strides, so the same order of coordinates
+        auto encode = [&](const BlkUmmaOperand& op, CUtensorMap* out, int box_rows, int* head_first) {
+            if (op.given && (op.num_views != 1 || op.views[0].residue != 0)) return false;
+            for (int v = 0; v < op.num_views; ++v) {
+                const BlkUmmaView& vw = op.views[v];
+                const BlkOperandLayout lay = op.given ? *op.given : BlkOperandLayout{(op.D - vw.residue) / vw.K, vw.K, op.D};
+                int hf = 0;
+                if (!blk_make_row_map(&out[v], static_cast<const unsigned char*>(op.base) + 2 * vw.residue, p.bf16, vw.K, p.H, lay,
+                                      UM_BK, box_rows, &hf))
+                    return false;
+                if (v > 0 && hf != *head_first) return false;
+                *head_first = hf;
+            }
+            return true;
+        };
+        if (!encode(A, maps.a, UM_BM, &p.head_firstA) || !encode(B, maps.b, UM_BN, &p.head_firstB)) return cudaErrorInvalidValue;
+        std::lock_guard<std::mutex> g(g_launch_mu);
+        LaunchSlot* victim = &g_launch_slots[0];
+        for (LaunchSlot& sl : g_launch_slots) {
+            if (!sl.used) { victim = &sl; break; }
+            if (sl.stamp < victim->stamp) victim = &sl;
+        }
+        victim->key = key;
+        victim->maps = maps;
+        victim->hfA = p.head_firstA;
+        victim->hfB = p.head_firstB;
+        victim->stamp = ++g_launch_clock;
+        victim->used = true;
+    }
+    if (p.bf16) return p.out_f32 ? launch<BlkBf16Tag, true>(p, maps, sms, st) : launch<BlkBf16Tag, false>(p, maps, sms, st);
+    return p.out_f32 ? launch<BlkHalfTag, true>(p, maps, sms, st) : launch<BlkHalfTag, false>(p, maps, sms, st);
 }

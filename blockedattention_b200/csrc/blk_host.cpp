@@ -5,6 +5,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <numeric>
 #include <queue>
 #include <string>
@@ -265,36 +266,90 @@ int blk_build_gemm_schedule(blk_plan* p) {
     p->Dm2 = p->a2[S];
     p->Dout = p->ao[S];
 
-    const bool allow_small = !blk_env_flag("BLK_DISABLE_SMALL");
+    bool allow_small = !blk_env_flag("BLK_DISABLE_SMALL");
     const bool allow_umma = !blk_env_flag("BLK_DISABLE_UMMA") && p->dtype_in != BLK_F32 && !p->ta && !p->tb &&
                             p->Dm1 % 8 == 0 && p->Dm2 % 8 == 0;
-    // The tcgen05 kernel views each operand as one (rows, K) matrix per head, so it takes the segments of
-    // one K only: the K (a multiple of 64) that carries the most work among the segments too big for the
-    // packed small-segment kernel and whose offsets are whole rows of that view.
+    // The tcgen05 kernel reads each operand through (K, rows, heads) views (BlkUmmaView): a segment needs the view of
+    // its K that starts at its offset modulo K.  It takes the 16-bit segments that are not for the small-segment
+    // kernels (too big, or a K other than theirs) whose K and offsets are multiples of 8 elements (16-byte rows for the tensor maps) and whose views are
+    // among the BLK_UMMA_VIEWS per operand that carry the most work.
     auto umma_candidate = [&](int64_t s) {
         const int64_t m = p->M[s], n = p->N[s], k = p->K[s];
-        return allow_umma && m > 0 && n > 0 && k >= 64 && k % 64 == 0 && (m > BLK_SMALL_MAXM || n > BLK_SMALL_MAXN || !allow_small) &&
-               p->a1[s] % k == 0 && p->a2[s] % k == 0 && p->Dm1 / k < INT32_MAX && p->Dm2 / k < INT32_MAX;
+        return allow_umma && m > 0 && n > 0 && k >= 16 && k % 8 == 0 &&
+               (m > BLK_SMALL_MAXM || n > BLK_SMALL_MAXN || (k != 32 && k != 64) || !allow_small) &&
+               p->a1[s] % 8 == 0 && p->a2[s] % 8 == 0 && p->Dm1 / k < INT32_MAX && p->Dm2 / k < INT32_MAX;
     };
+    std::vector<int32_t> umma_views(allow_umma ? (size_t)S : 0, -1);  // per segment: view of A | view of B << 8, or -1
+    auto select_views = [&]() {
     p->umma_K = 0;
+    p->umma_viewsA.clear();
+    p->umma_viewsB.clear();
+    std::fill(umma_views.begin(), umma_views.end(), -1);
     if (allow_umma) {
-        std::vector<std::pair<int64_t, double>> work;  // (K, work)
+        typedef std::pair<int64_t, int64_t> Key;  // (K, residue)
+        std::map<Key, double> workA, workB;
+        double all = 0;
+        for (int64_t s = 0; s < S; ++s) {
+            const double wk = (double)p->M[s] * (double)p->N[s] * (double)p->K[s];
+            all += wk;
+            if (!umma_candidate(s)) continue;
+            workA[Key(p->K[s], p->a1[s] % p->K[s])] += wk;
+            workB[Key(p->K[s], p->a2[s] % p->K[s])] += wk;
+        }
+        auto pick = [](const std::map<Key, double>& work, std::vector<BlkUmmaView>* out) {
+            std::vector<std::pair<double, Key>> v;
+            for (const auto& kv : work) v.push_back(std::make_pair(kv.second, kv.first));
+            std::stable_sort(v.begin(), v.end(), [](const std::pair<double, Key>& x, const std::pair<double, Key>& y) { return x.first > y.first; });
+            for (size_t i = 0; i < v.size() && i < (size_t)BLK_UMMA_VIEWS; ++i) out->push_back(BlkUmmaView{v[i].second.first, v[i].second.second});
+        };
+        pick(workA, &p->umma_viewsA);
+        pick(workB, &p->umma_viewsB);
+        auto find = [](const std::vector<BlkUmmaView>& views, int64_t k, int64_t r) {
+            for (size_t i = 0; i < views.size(); ++i)
+                if (views[i].K == k && views[i].residue == r) return (int)i;
+            return -1;
+        };
+        double taken = 0;
         for (int64_t s = 0; s < S; ++s) {
             if (!umma_candidate(s)) continue;
-            const double wk = (double)p->M[s] * (double)p->N[s] * (double)p->K[s];
-            bool found = false;
-            for (auto& kv : work)
-                if (kv.first == p->K[s]) { kv.second += wk; found = true; }
-            if (!found) work.push_back(std::make_pair(p->K[s], wk));
+            const int va = find(p->umma_viewsA, p->K[s], p->a1[s] % p->K[s]), vb = find(p->umma_viewsB, p->K[s], p->a2[s] % p->K[s]);
+            if (va < 0 || vb < 0) continue;
+            umma_views[s] = va | (vb << 8);
+            taken += (double)p->M[s] * (double)p->N[s] * (double)p->K[s];
         }
-        double best = 0;
-        for (auto& kv : work)
-            if (kv.second > best) { best = kv.second; p->umma_K = (int)kv.first; }
         // A separate launch pays only if it takes a real share of the batch: when the segments it could take
         // carry under a tenth of all multiply-adds, they stay with the staged kernel.
-        double all = 0;
-        for (int64_t s = 0; s < S; ++s) all += (double)p->M[s] * (double)p->N[s] * (double)p->K[s];
-        if (best < 0.1 * all && !blk_env_flag("BLK_FORCE_UMMA")) p->umma_K = 0;
+        if (taken == 0 || (taken < 0.1 * all && !blk_env_flag("BLK_FORCE_UMMA"))) {
+            std::fill(umma_views.begin(), umma_views.end(), -1);
+            p->umma_viewsA.clear();
+            p->umma_viewsB.clear();
+        } else if (p->umma_viewsA.size() == 1 && p->umma_viewsB.size() == 1 && p->umma_viewsA[0].residue == 0 &&
+                   p->umma_viewsB[0].residue == 0) {
+            p->umma_K = (int)p->umma_viewsA[0].K;
+        } else {
+            p->umma_K = -1;
+        }
+    }
+    };
+    select_views();
+    // A launch of the small-segment kernel of its own pays only for enough segments: when the tcgen05 kernel is
+    // launched anyway and fewer than BLK_SMALL_MIN_PAIRS (default 300: two per SM) pairs of a small segment and a head
+    // exist, they ride along with it (those it cannot take go to the staged kernel).  Attention plans keep their packs.
+    if (allow_small && allow_umma && !p->attn && !p->umma_viewsA.empty()) {
+        int64_t pairs = 0, sk = 0;
+        for (int64_t s = 0; s < S; ++s) {
+            const int64_t m = p->M[s], n = p->N[s], k = p->K[s];
+            if (m > 0 && n > 0 && m <= BLK_SMALL_MAXM && n <= BLK_SMALL_MAXN && (k == 32 || k == 64) && (sk == 0 || sk == k)) {
+                sk = k;
+                pairs += p->H;
+            }
+        }
+        const char* e = std::getenv("BLK_SMALL_MIN_PAIRS");
+        const int64_t min_pairs = e ? std::atoll(e) : 300;
+        if (pairs < min_pairs) {
+            allow_small = false;
+            select_views();
+        }
     }
     // The tcgen05 kernel for a second operand stored (K, D) -- the product of a probability block with the values --
     // takes 16-bit segments whose second operand has D = 64 or 128 columns (one D per plan: the one carrying the
@@ -363,11 +418,12 @@ int blk_build_gemm_schedule(blk_plan* p) {
                                                 (int32_t)(sd.offB / n), (int32_t)(m - tm * BLK_UMMA_BM), (int32_t)k, 0});
             continue;
         }
-        if (p->umma_K != 0 && k == p->umma_K && umma_candidate(s)) {
+        if (allow_umma && umma_views[s] >= 0) {
             const int32_t tms = (int32_t)((m + BLK_UMMA_BM - 1) / BLK_UMMA_BM);
+            const int64_t ra = p->umma_viewsA[umma_views[s] & 255].residue, rb = p->umma_viewsB[umma_views[s] >> 8].residue;
             for (int32_t tm = 0; tm < tms; ++tm)
-                p->umma_items.push_back(BlkUmmaItem{(int32_t)s, tm, (int32_t)(sd.offA / k + (int64_t)tm * BLK_UMMA_BM),
-                                                    (int32_t)(sd.offB / k), sd.offC, (int32_t)m, (int32_t)n});
+                p->umma_items.push_back(BlkUmmaItem{umma_views[s], tm, (int32_t)((sd.offA - ra) / k + (int64_t)tm * BLK_UMMA_BM),
+                                                    (int32_t)((sd.offB - rb) / k), sd.offC, (int32_t)m, (int32_t)n, (int32_t)k, 0});
             continue;
         }
         const int32_t tms = (int32_t)((m + BLK_TILE_BM - 1) / BLK_TILE_BM);
@@ -388,7 +444,8 @@ int blk_build_gemm_schedule(blk_plan* p) {
     auto umma_cost = [two_sweeps](const BlkUmmaItem& a) {
         const int64_t chunks = ((int64_t)a.N + 255) / 256;
         const int64_t rows = std::min(a.M - a.tm * BLK_UMMA_BM, BLK_UMMA_BM);
-        return ((two_sweeps && chunks > 2 ? 2 * chunks : chunks) << 40) + ((int64_t)a.N << 8) + rows;
+        const int64_t kblocks = ((int64_t)a.K + 63) / 64;  // a chunk costs the epilogue (about four k-blocks' worth) plus its k-blocks
+        return ((two_sweeps && chunks > 2 ? 2 * chunks : chunks) * (4 + kblocks) << 36) + ((int64_t)a.N << 8) + rows;
     };
     std::stable_sort(p->umma_items.begin(), p->umma_items.end(),
                      [&](const BlkUmmaItem& a, const BlkUmmaItem& b) { return umma_cost(a) > umma_cost(b); });

@@ -87,16 +87,28 @@ struct BlkSmxWindow {
 static_assert(sizeof(BlkSmxWindow) == 24, "BlkSmxWindow layout");
 constexpr int BLK_SMX_WINDOW_PIECES = 64;  // pieces a window may hold
 
-// Per-CTA tile of the tcgen05 kernel (filled in by blk_gemm_umma.cu's planner).
+// The tcgen05 kernel reads an operand through (K, rows, heads) views of the packed buffer, one tensor map per view.
+// A segment with contraction length K whose offset inside a head strip is r modulo K starts on row (offset - r) / K of
+// the view that begins r elements into the strip, so a batch of several contraction lengths (or of offsets that are
+// not whole rows of one view) needs a handful of views per operand; BLK_UMMA_VIEWS bounds them.
+constexpr int BLK_UMMA_VIEWS = 24;
+struct BlkUmmaView {
+    int64_t K;        // row length = contraction length
+    int64_t residue;  // elements from the start of a head strip to row 0 of the view (< K, a multiple of 8)
+};
+
+// Per-CTA tile of the tcgen05 kernel (filled in by the scheduler).
 struct BlkUmmaItem {
-    int32_t seg;
+    int32_t views;    // view of the first operand | view of the second << 8
     int32_t tm;       // 128-row block inside the segment
-    int32_t rowA;     // first row of that block in the (rows, K) view of the first operand
-    int32_t rowB;     // first row of the segment in the (rows, K) view of the second operand
+    int32_t rowA;     // first row of that block in its view of the first operand
+    int32_t rowB;     // first row of the segment in its view of the second operand
     int64_t offC;     // element offset of the segment's output block
     int32_t M, N;     // extents of the whole segment
+    int32_t K;        // contraction length
+    int32_t pad;
 };
-static_assert(sizeof(BlkUmmaItem) == 32, "BlkUmmaItem layout");
+static_assert(sizeof(BlkUmmaItem) == 40, "BlkUmmaItem layout");
 
 // One work item of the tcgen05 kernel for the product with a (K, D) second operand (P V): a 128-row block of the
 // first operand of one segment.
@@ -156,7 +168,9 @@ struct blk_plan {
     std::vector<BlkSmxChunk> smx_chunks;    // softmax kernel (also second pass of fp32 scores)
     std::vector<BlkSmxWindow> smx_windows;  // pipelined softmax kernels: groups of chunks
     int64_t max_chunks = 0;                 // > 0: the softmax scheduler refuses batches that need more chunks
-    int umma_K = 0;                         // uniform K of the tcgen05 bin
+    int umma_K = 0;                         // K of the tcgen05 bin when it has one view per operand that starts at the
+                                            // strip (the only case the strided entry takes); 0: no such bin; -1: several views
+    std::vector<BlkUmmaView> umma_viewsA, umma_viewsB;  // views of the operands the tcgen05 items refer to
     int small_K = 0;                        // uniform K of the small bin
     int small_pipe = 0;                     // 1: the small segments run as packs on the pipelined kernel
     int attn = 0;                           // attention plan (result = softmax(QK^T) V): 1 every segment in packs,

@@ -61,7 +61,6 @@ struct BlkUmmaParams {
     int64_t Dout;
     int num_items;
     int H;
-    int K;
     int bf16;
     int out_f32;
     int epi;
@@ -162,9 +161,18 @@ cudaError_t blk_launch_softmax_pipe(const BlkSmxPipeParams& p, int dtype, int ba
 cudaError_t blk_launch_gemm_simt(const BlkSimtParams& p, cudaStream_t st);
 cudaError_t blk_launch_scores_small(const BlkSmallParams& p, int dtype_in, int K, int bucket, int sms,
                                     cudaStream_t st);
-cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p, const void* A, const void* B, const BlkOperandLayout& layA,
-                                 const BlkOperandLayout& layB,
-                                 int sms, cudaStream_t st);
+// An operand of the tcgen05 GEMM kernel: the buffer, the length of a head strip, and the views the plan's items refer
+// to.  given != nullptr (strided operands): the one view, which starts at the buffer, has this layout instead of the
+// packed one.
+struct BlkUmmaOperand {
+    const void* base;
+    int64_t D;
+    const BlkUmmaView* views;
+    int num_views;
+    const BlkOperandLayout* given;
+};
+cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p, const BlkUmmaOperand& A, const BlkUmmaOperand& B, int sms,
+                                 cudaStream_t st);
 cudaError_t blk_launch_pv_umma(const BlkPvParams& p, const void* V, int sms, cudaStream_t st);
 cudaError_t blk_launch_attn_umma(const BlkFlashParams& p, const void* q, const void* k, const void* v, int sms,
                                  cudaStream_t st);

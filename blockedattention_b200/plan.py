@@ -166,7 +166,7 @@ class GemmPlan(_Plan):
                         scale: float = 1.0) -> torch.Tensor:
         """Same as :meth:`run` for token-major operands ``mat1 -> (sum m_s, H, d)``, ``mat2 -> (sum n_s, H, d)``
         (the rows of all segments in batch order); the result is the packed head-major ``(H, Dout)`` buffer.
-        Needs a batch the tensor-map kernels take whole: 16-bit, one ``K = d`` that is a multiple of 64."""
+        Needs a batch the tensor-map kernels take whole: 16-bit, one ``K = d`` that is a multiple of 8."""
         if self.device is None:
             raise RuntimeError("this plan was built without a device")
         d = int(self.K[0]) if self.S else 0

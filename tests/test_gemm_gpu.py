@@ -116,13 +116,42 @@ def test_tcgen05_path(cuda_device, dtype, K, mode):
 
 
 def test_tcgen05_mixed_batch_and_negative_scale(cuda_device):
-    # small, tcgen05 and staged-kernel segments in one batch (K = 64 carries the tcgen05 bin; K = 48 and
-    # the odd offsets after it go to the staged kernel)
-    M = [20, 300, 64, 130, 33, 500, 90]; N = [20, 300, 64, 70, 40, 600, 200]; K = [64, 64, 64, 64, 48, 64, 64]
-    p = run_case(cuda_device, M, N, K, 2, BF16, softmax=True, scale=-0.2, what="mixed batch")
+    # small, tcgen05 and staged-kernel segments in one batch: K = 64 and K = 48 go to the tcgen05 kernel (two views per
+    # operand), K = 44 -- rows of 88 bytes, which no tensor map takes -- to the staged kernel.
+    # The small segments get a launch of their own only when asked to (there are too few of them otherwise).
+    M = [20, 300, 64, 130, 33, 500, 90, 70]; N = [20, 300, 64, 70, 40, 600, 200, 50]; K = [64, 64, 64, 64, 48, 64, 44, 64]
+    p = run_case(cuda_device, M, N, K, 2, BF16, softmax=True, scale=-0.2, what="mixed batch",
+                 env={"BLK_SMALL_MIN_PAIRS": "0"})
     s = p.summary
-    assert s["umma_items"] > 0 and s["small_items"] > 0 and s["tile_items"] > 0
+    assert s["umma_items"] > 0 and s["small_items"] == 2 and s["tile_items"] > 0
+    p = run_case(cuda_device, M, N, K, 2, BF16, softmax=True, scale=-0.2, what="mixed batch, small segments riding along")
+    assert p.summary["small_items"] == 0 and p.summary["umma_items"] > s["umma_items"]
     run_case(cuda_device, M, N, K, 2, F16, scale=-1.5, what="mixed batch scores")
+
+
+@pytest.mark.parametrize("out32", [False, True])
+@pytest.mark.parametrize("softmax", [False, True])
+def test_tcgen05_several_contraction_lengths(cuda_device, out32, softmax):
+    # one launch of the tcgen05 kernel for contraction lengths from 16 to 320 (short last k-blocks, k-blocks the tensor
+    # map fills with zeros past K) and offsets that are not whole rows of the segment's own (rows, K) view
+    rs = np.random.RandomState(5)
+    S = 60
+    M = rs.randint(1, 300, size=S); N = rs.randint(1, 700, size=S)
+    K = rs.choice([16, 24, 32, 48, 64, 72, 96, 128, 200, 320], size=S)
+    p = run_case(cuda_device, M, N, K, 3, F16, softmax=softmax, scale=0.07 if softmax else 0.5,
+                 out_dtype=torch.float32 if out32 and not softmax else None, what=f"many K out32={out32} softmax={softmax}")
+    s = p.summary
+    assert s["umma_items"] > 0 and s["launches"] <= 2
+
+
+def test_tcgen05_more_views_than_slots(cuda_device):
+    # more (K, offset modulo K) combinations than tensor-map slots: the lightest go to the staged kernel
+    rs = np.random.RandomState(6)
+    S = 120
+    M = rs.randint(65, 200, size=S); N = rs.randint(65, 200, size=S)
+    K = rs.choice(np.arange(16, 400, 8), size=S)
+    p = run_case(cuda_device, M, N, K, 2, BF16, what="views overflow")
+    assert p.summary["umma_items"] > 0 and p.summary["tile_items"] > 0
 
 
 @pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
@@ -341,12 +370,18 @@ def test_token_major_entry_matches_head_major(cuda_device, dtype, d, lo, hi):
 def test_token_major_entry_refuses_what_it_cannot_take(cuda_device):
     dev = cuda_device
     n = np.array([5, 9, 70])
-    q = torch.randn((int(n.sum()), 2, 32), device=dev).half()       # d = 32: no tensor-map kernel takes it
+    # d = 32 and d = 128 with a few small segments: everything rides on the tcgen05 kernel, which reads token-major rows
+    for d in (32, 128):
+        q = torch.randn((int(n.sum()), 2, d), device=dev).half()
+        qs = q.permute(1, 0, 2).reshape(2, int(n.sum()) * d).contiguous()
+        assert torch.equal(blockAttnScoresTokenMajor(q, q, n), blockAttnScores(qs, qs, n, n, np.full_like(n, d)))
+    q = torch.randn((int(n.sum()), 2, 20), device=dev).half()       # d = 20: rows of 40 bytes, no tensor map takes them
     with pytest.raises(RuntimeError):
         blockAttnScoresTokenMajor(q, q, n)
-    q = torch.randn((int(n.sum()), 2, 128), device=dev).half()      # d = 128 with small segments: register-fed kernel
+    q = torch.randn((int(n.sum()), 2, 64), device=dev)              # fp32 operands: no tensor-map kernel
     with pytest.raises(RuntimeError):
         blockAttnScoresTokenMajor(q, q, n)
+    q = torch.randn((int(n.sum()), 2, 128), device=dev).half()
     with pytest.raises(RuntimeError):
         blockAttnScoresTokenMajor(q[:, :, :64], q[:, :, :64], n)    # not contiguous
 
