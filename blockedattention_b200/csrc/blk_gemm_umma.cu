@@ -124,7 +124,7 @@ __device__ __forceinline__ bool next_work(const BlkUmmaParams& p, uint32_t w, Wo
     const uint32_t item = w / (uint32_t)p.H;
     wk.head = (int)(w - item * (uint32_t)p.H);
     wk.it = p.items[item];
-    wk.nchunks = (wk.it.N + UM_BN - 1) / UM_BN;
+    wk.nchunks = wk.it.nch ? wk.it.nch : (wk.it.N + UM_BN - 1) / UM_BN;  // chunks [it.ch0, it.ch0 + nchunks)
     wk.nkb = (wk.it.K + UM_BK - 1) / UM_BK;
     wk.sweeps = (p.epi == BLK_EPI_SOFTMAX && wk.nchunks > 2) ? 2 : 1;
     return true;
@@ -207,7 +207,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x) {
                 for (int sw = 0; ok && sw < wk.sweeps; ++sw)
-                    for (int ch = 0; ok && ch < wk.nchunks; ++ch)
+                    for (int ch = wk.it.ch0; ok && ch < wk.it.ch0 + wk.nchunks; ++ch)
                         for (int kb = 0; kb < wk.nkb; ++kb) {
                             if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, lim)) { ok = false; break; }
                             const uint32_t sA = smem_u32 + stage * UM_STAGE_BYTES, sB = sA + UM_A_BYTES;
@@ -231,7 +231,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x) {
                 for (int sw = 0; ok && sw < wk.sweeps; ++sw)
-                    for (int ch = 0; ok && ch < wk.nchunks; ++ch) {
+                    for (int ch = wk.it.ch0; ok && ch < wk.it.ch0 + wk.nchunks; ++ch) {
                         const int buf = slot & 1;
                         if (!mbar_wait(tempty_bar(buf), ((slot >> 1) & 1u) ^ 1u, abort_flag, p.status, 2, lim)) { ok = false; break; }
                         tc_fence_after();
@@ -482,7 +482,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
             const bool anyodd = !OUT32 && __any_sync(0xffffffffu, (int)((cbase + (int64_t)myrow * N) & 1));
             volatile float* xm = xch + (seq & 1) * (2 * UM_SPLIT * 128);  // [part][row] maxima, then [UM_SPLIT + part][row] sums
             if (!softmax) {
-                for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
+                for (int ch = wk.it.ch0; ok && ch < wk.it.ch0 + wk.nchunks; ++ch, ++slot) {
                     const int buf = slot & 1;
                     if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 4, lim)) { ok = false; break; }
                     tc_fence_after();

@@ -421,9 +421,17 @@ int blk_build_gemm_schedule(blk_plan* p) {
         if (allow_umma && umma_views[s] >= 0) {
             const int32_t tms = (int32_t)((m + BLK_UMMA_BM - 1) / BLK_UMMA_BM);
             const int64_t ra = p->umma_viewsA[umma_views[s] & 255].residue, rb = p->umma_viewsB[umma_views[s] >> 8].residue;
+            // Scores only: one item per 256-column chunk of a row block when the contraction is long (a k loop of
+            // 8 blocks or more keeps a CTA busy for longer than it takes to start an item), so that a batch of few big
+            // segments still fills the SMs and the CTAs running at one time share a few segments' operands in L2.
+            // With the fused softmax an item is the whole row block.
+            const int32_t chunks = (int32_t)((n + 255) / 256);
+            const bool per_chunk = p->epi != BLK_EPI_SOFTMAX && k >= 512 && chunks > 1;
             for (int32_t tm = 0; tm < tms; ++tm)
-                p->umma_items.push_back(BlkUmmaItem{umma_views[s], tm, (int32_t)((sd.offA - ra) / k + (int64_t)tm * BLK_UMMA_BM),
-                                                    (int32_t)((sd.offB - rb) / k), sd.offC, (int32_t)m, (int32_t)n, (int32_t)k, 0});
+                for (int32_t c = 0; c < (per_chunk ? chunks : 1); ++c)
+                    p->umma_items.push_back(BlkUmmaItem{umma_views[s], tm, (int32_t)((sd.offA - ra) / k + (int64_t)tm * BLK_UMMA_BM),
+                                                        (int32_t)((sd.offB - rb) / k), sd.offC, (int32_t)m, (int32_t)n, (int32_t)k,
+                                                        per_chunk ? c : 0, per_chunk ? 1 : 0, 0});
             continue;
         }
         const int32_t tms = (int32_t)((m + BLK_TILE_BM - 1) / BLK_TILE_BM);
@@ -442,7 +450,7 @@ int blk_build_gemm_schedule(blk_plan* p) {
     // ordering by rows x columns instead left the CTAs 5 % apart on a long-tailed batch.
     const bool two_sweeps = p->epi == BLK_EPI_SOFTMAX;
     auto umma_cost = [two_sweeps](const BlkUmmaItem& a) {
-        const int64_t chunks = ((int64_t)a.N + 255) / 256;
+        const int64_t chunks = a.nch ? a.nch : ((int64_t)a.N + 255) / 256;
         const int64_t rows = std::min(a.M - a.tm * BLK_UMMA_BM, BLK_UMMA_BM);
         const int64_t kblocks = ((int64_t)a.K + 63) / 64;  // a chunk costs the epilogue (about four k-blocks' worth) plus its k-blocks
         return ((two_sweeps && chunks > 2 ? 2 * chunks : chunks) * (4 + kblocks) << 36) + ((int64_t)a.N << 8) + rows;

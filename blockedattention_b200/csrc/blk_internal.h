@@ -106,9 +106,11 @@ struct BlkUmmaItem {
     int64_t offC;     // element offset of the segment's output block
     int32_t M, N;     // extents of the whole segment
     int32_t K;        // contraction length
+    int32_t ch0;      // first 256-column chunk of the item ...
+    int32_t nch;      // ... and how many (0: all the chunks of the row block, which a fused softmax needs)
     int32_t pad;
 };
-static_assert(sizeof(BlkUmmaItem) == 40, "BlkUmmaItem layout");
+static_assert(sizeof(BlkUmmaItem) == 48, "BlkUmmaItem layout");
 
 // One work item of the tcgen05 kernel for the product with a (K, D) second operand (P V): a 128-row block of the
 // first operand of one segment.

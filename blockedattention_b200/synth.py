@@ -157,9 +157,9 @@ def workload(name: str, seed: int = 0, segments: Optional[int] = None) -> Worklo
     if name == "large_k":
         S = segments or 64
         n = _i64(rs.randint(1024, 2049, size=S))
-        K = np.full(S, 2048, np.int64)
+        K = _i64(rs.choice([1024, 2048, 4096], size=S))
         return Workload(name, n, n.copy(), K, 1, torch.float16, torch.float16, 1.0, False, "uniform",
-                        note="64 segments, M=N~U{1024..2048}, K=2048, fp16, GEMM only (compute-bound)")
+                        note="64 segments, M=N~U{1024..2048}, K in {1024,2048,4096}, fp16, GEMM only (compute-bound)")
     raise ValueError(f"unknown workload {name!r}")
 
 
