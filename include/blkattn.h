@@ -129,8 +129,9 @@ BLK_API int blk_gemm_run(const blk_plan_t* plan, const void* mat1, const void* m
  * head-major as always.  Only batches whose every segment runs on a kernel
  * that fetches operands through tensor maps qualify: 16-bit inputs, not
  * transposed, packed offsets, one contraction length d that is a multiple of
- * 64 (and d = 64 where the batch has segments with at most 64 rows and
- * columns); otherwise BLK_ERR_UNSUPPORTED.  No counterpart upstream. */
+ * 8 (with d = 32, a batch with hundreds of segments of at most 64 rows and
+ * columns runs those on a kernel that reads packed strips only and is
+ * refused); otherwise BLK_ERR_UNSUPPORTED.  No counterpart upstream. */
 BLK_API int blk_gemm_run_strided(const blk_plan_t* plan, const void* mat1, int64_t row_stride1, int64_t head_stride1,
                          const void* mat2, int64_t row_stride2, int64_t head_stride2, void* out, float scale,
                          void* cuda_stream);
