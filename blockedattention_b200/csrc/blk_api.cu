@@ -641,6 +641,7 @@ static int gemm_run_impl(const blk_plan* p, const void* mat1, const void* mat2, 
         up.epi = p->epi;
         up.scale = scale;
         up.status = p->d_status;
+        up.long_rows = p->umma_long_rows;
         if (blk_env_flag("BLK_TEST_STALL_PRODUCER")) {  // test hook: see BlkUmmaParams::stall
             up.stall = 1;
             up.spin_limit = 4096;

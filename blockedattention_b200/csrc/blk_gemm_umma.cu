@@ -1,8 +1,8 @@
 // Large-segment kernel of the varlen blocked GEMM on the 5th-generation tensor
 // cores: TMA-fed tcgen05.mma with the accumulator in tensor memory.
 //
-// A persistent CTA (one per SM, 18 warps) walks a static list of work items, an
-// item being a 128-row block of one segment of one head.  Roles:
+// A persistent CTA (one per SM; 22 warps with 16-bit results, 14 with fp32 results) walks a static list of work
+// items, an item being a 128-row block of one segment of one head (or one 256-column chunk of it).  Roles:
 //   warp 0   producer: one lane issues 3-D tiled TMA loads (k, row, head) of a
 //            128 x 64 tile of the first operand and a 256 x 64 tile of the
 //            second into a 3-stage ring of 128-byte-swizzled shared memory;
@@ -10,15 +10,15 @@
 //            tcgen05.mma (M = 128, N up to 256, K = 16 per instruction) into
 //            one of two 256-column accumulators; tcgen05.commit hands shared
 //            memory stages back to the producer and accumulators to the epilogue;
-//   warps 2-9 epilogue arithmetic: a warp may read the 32 accumulator lanes (= rows)
-//            of its quarter; the two warps of a quarter each take 64 of every 128
+//   next 16 (8) warps  epilogue arithmetic: a warp may read the 32 accumulator lanes (= rows)
+//            of its quarter; the four (two) warps of a quarter each take 32 (32) of every 128 (64)
 //            columns of the row and exchange partial row statistics through
 //            shared memory.  A thread reads its row 32 columns at a time
 //            (tcgen05.ld), applies the epilogue and writes the packed words into
-//            one of the quarter's two strips (32 rows x 128 columns each, used
+//            one of the quarter's two strips (32 rows x 128 16-bit or 64 fp32 columns each, used
 //            alternately), at the position the row has in global memory modulo
 //            one 32-bit word;
-//   warps 10-17 stores: one warp per quarter and strip.  It waits for the strip to
+//   last 4 warps  stores: one warp per quarter.  It waits for a strip to
 //            be filled, writes its 32 rows to global memory -- a row piece is 256
 //            contiguous bytes stored as two fully coalesced 128-byte word stores;
 //            an odd first or last element goes out as a 16-bit store -- and hands
@@ -27,8 +27,7 @@
 //            special-function unit idle whenever the memory system pushes back
 //            on its stores, and all warps of a CTA reach that point together;
 //            with separate warps the exponentials of one piece run while the
-//            previous piece drains (both alone and together they take the same
-//            time on this machine).  Wide contiguous row pieces matter as well:
+//            previous piece drains.  Wide contiguous row pieces matter as well:
 //            the same data written as 128-byte pieces with element-wise ragged
 //            edges runs at little more than half the rate.
 //
@@ -69,13 +68,14 @@ constexpr int UM_STAGES = 3;
 constexpr int UM_A_BYTES = UM_BM * UM_BK * 2;  // 16 KB
 constexpr int UM_B_BYTES = UM_BN * UM_BK * 2;  // 32 KB
 constexpr int UM_STAGE_BYTES = UM_A_BYTES + UM_B_BYTES;
-constexpr int UM_SPLIT = 2;                           // arithmetic warps per accumulator-lane quarter
-constexpr int UM_EPI_WARPS = 4 * UM_SPLIT;            // arithmetic warps
-#ifndef UM_STORE_WARPS_N
-#define UM_STORE_WARPS_N 4
-#endif
-constexpr int UM_STORE_WARPS = UM_STORE_WARPS_N;      // 4: one per quarter; 8: one per quarter and strip
-constexpr int UM_THREADS = 64 + 32 * (UM_EPI_WARPS + UM_STORE_WARPS);
+// Arithmetic warps per accumulator-lane quarter (SPLIT, a template parameter of the kernel): four for the fused
+// softmax over rows too long for tensor memory (each converts 32 of every 128 columns: with two warps per scheduler
+// partition the special-function unit idles half the time in the two-sweep scheme), two otherwise -- rows that stay
+// resident, scores only (both a few per cent faster with fewer, fatter warps) and fp32 results (a staged piece is 64
+// columns there, and a warp's share must be whole 32-column loads).
+constexpr int UM_SPLIT_MAX = 4;
+constexpr int UM_STORE_WARPS = 4;                     // one per quarter
+constexpr int um_threads(int split) { return 64 + 32 * (4 * split + UM_STORE_WARPS); }
 constexpr int UM_PIECE = 32;                          // columns per tcgen05.ld
 constexpr int UM_PW = 64;                             // 32-bit words of a staged row piece (128 x 16-bit, 64 x fp32)
 // Strip row pitch in words: odd, so that the 32 row-owning lanes of a store (same word, consecutive rows) hit 32
@@ -94,7 +94,7 @@ struct UmPiece {
 };
 static_assert(sizeof(UmPiece) == 32, "UmPiece layout");
 constexpr int PCOLS16 = UM_PW * 2;                    // columns of a whole 16-bit piece
-constexpr int UM_XCH_BYTES = 2 * 2 * UM_SPLIT * 128 * 4;  // row statistics exchanged between the two halves, double-buffered
+constexpr int UM_XCH_BYTES = 2 * 2 * UM_SPLIT_MAX * 128 * 4;  // row statistics exchanged between the two halves, double-buffered
 constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + 8 * UM_STRIP_BYTES + UM_XCH_BYTES + 8 * 32 + 512;
 static_assert(UM_SMEM_BYTES <= 227 * 1024, "shared memory budget");
 static_assert(UM_STAGES <= 4, "barrier slots");
@@ -146,8 +146,8 @@ __device__ __forceinline__ uint32_t lds_b32(uint32_t addr) {
     return v;
 }
 
-template <typename Tag, bool OUT32>
-__global__ void __launch_bounds__(UM_THREADS, 1)
+template <typename Tag, bool OUT32, int SPLIT>
+__global__ void __launch_bounds__(um_threads(SPLIT), 1)
 blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps) {
     extern __shared__ __align__(1024) unsigned char um_smem_raw[];  // the swizzled tiles need a 1024-byte aligned base
     unsigned char* smem = um_smem_raw;
@@ -155,6 +155,9 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
         if (threadIdx.x == 0) atomicCAS(p.status, 0, 9);
         return;
     }
+    constexpr int UM_SPLIT = SPLIT;
+    static_assert(!OUT32 || SPLIT == 2, "fp32 results: two arithmetic warps per quarter");
+    constexpr int UM_EPI_WARPS = 4 * UM_SPLIT;
     unsigned char* strips = smem + UM_STAGES * UM_STAGE_BYTES;
     float* xch = reinterpret_cast<float*>(strips + 8 * UM_STRIP_BYTES);
     UmPiece* pieces_desc = reinterpret_cast<UmPiece*>(strips + 8 * UM_STRIP_BYTES + UM_XCH_BYTES);  // [quarter][strip]
@@ -183,7 +186,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
         }
         *abort_flag = 0;
         for (int i = 0; i < 4; ++i) mbar_init(bar0 + 8u * (16 + i), UM_SPLIT);   // one arrival per arithmetic warp of the quarter
-        for (int i = 0; i < 8; ++i) mbar_init(bar0 + 8u * (20 + i), UM_SPLIT);   // strip filled: its two arithmetic warps
+        for (int i = 0; i < 8; ++i) mbar_init(bar0 + 8u * (20 + i), UM_SPLIT);   // strip filled: the quarter's arithmetic warps
         for (int i = 0; i < 8; ++i) mbar_init(bar0 + 8u * (28 + i), 1);          // strip drained: its store warp
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -264,10 +267,9 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
         unsigned char* const C = reinterpret_cast<unsigned char*>(p.C);
         constexpr int ES = OUT32 ? 4 : 2;
         for (uint32_t n = 0;; ++n) {
-            // with one store warp per quarter it takes the quarter's pieces in order, piece m from strip m & 1; with
-            // two, each warp owns a strip
-            const int sb = UM_STORE_WARPS == 4 ? (int)(n & 1u) : ((warp - 2 - UM_EPI_WARPS) >> 2);
-            const uint32_t use = UM_STORE_WARPS == 4 ? (n >> 1) : n;   // how often the strip has been used before
+            // the quarter's pieces in order, piece m from strip m & 1
+            const int sb = (int)(n & 1u);
+            const uint32_t use = n >> 1;   // how often the strip has been used before
             const uint32_t strip = blk_smem_u32(strips + (sq * 2 + sb) * UM_STRIP_BYTES);
             const uint32_t filled_bar = bar0 + 8u * (20 + sq * 2 + sb), drained_bar = bar0 + 8u * (28 + sq * 2 + sb);
             const volatile UmPiece* desc = pieces_desc + sq * 2 + sb;
@@ -680,13 +682,13 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <typename Tag, bool OUT32>
+template <typename Tag, bool OUT32, int SPLIT>
 cudaError_t launch(const BlkUmmaParams& p, const UmMaps& maps, int sms, cudaStream_t st) {
-    auto kern = blk_gemm_umma_kernel<Tag, OUT32>;
+    auto kern = blk_gemm_umma_kernel<Tag, OUT32, SPLIT>;
     cudaError_t e = blk_func_smem(reinterpret_cast<const void*>(kern), UM_SMEM_BYTES);
     if (e != cudaSuccess) return e;
     const int64_t total = (int64_t)p.num_items * p.H;
-    const dim3 grid((unsigned)(total < sms ? total : sms)), block(UM_THREADS);
+    const dim3 grid((unsigned)(total < sms ? total : sms)), block(um_threads(SPLIT));
     kern<<<grid, block, UM_SMEM_BYTES, st>>>(p, maps);
     return cudaGetLastError();
 }
@@ -861,6 +863,10 @@ cudaError_t blk_launch_gemm_umma(const BlkUmmaParams& p_in, const BlkUmmaOperand
         victim->stamp = ++g_launch_clock;
         victim->used = true;
     }
-    if (p.bf16) return p.out_f32 ? launch<BlkBf16Tag, true>(p, maps, sms, st) : launch<BlkBf16Tag, false>(p, maps, sms, st);
-    return p.out_f32 ? launch<BlkHalfTag, true>(p, maps, sms, st) : launch<BlkHalfTag, false>(p, maps, sms, st);
+    const bool four = !p.out_f32 && p.epi == BLK_EPI_SOFTMAX && p.long_rows;
+    if (p.bf16)
+        return p.out_f32 ? launch<BlkBf16Tag, true, 2>(p, maps, sms, st)
+                         : (four ? launch<BlkBf16Tag, false, 4>(p, maps, sms, st) : launch<BlkBf16Tag, false, 2>(p, maps, sms, st));
+    return p.out_f32 ? launch<BlkHalfTag, true, 2>(p, maps, sms, st)
+                     : (four ? launch<BlkHalfTag, false, 4>(p, maps, sms, st) : launch<BlkHalfTag, false, 2>(p, maps, sms, st));
 }

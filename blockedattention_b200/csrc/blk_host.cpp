@@ -457,6 +457,9 @@ int blk_build_gemm_schedule(blk_plan* p) {
     };
     std::stable_sort(p->umma_items.begin(), p->umma_items.end(),
                      [&](const BlkUmmaItem& a, const BlkUmmaItem& b) { return umma_cost(a) > umma_cost(b); });
+    p->umma_long_rows = 0;
+    for (const BlkUmmaItem& it : p->umma_items)
+        if (it.N > 512) p->umma_long_rows = 1;
     // longest contractions first for the same reason
     std::stable_sort(p->pv_items.begin(), p->pv_items.end(), [](const BlkPvItem& a, const BlkPvItem& b) { return a.K > b.K; });
     // K = 64 with 16-bit output: the small segments run on the pipelined kernel, grouped into packs of

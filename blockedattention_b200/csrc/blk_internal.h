@@ -172,6 +172,7 @@ struct blk_plan {
     int64_t max_chunks = 0;                 // > 0: the softmax scheduler refuses batches that need more chunks
     int umma_K = 0;                         // K of the tcgen05 bin when it has one view per operand that starts at the
                                             // strip (the only case the strided entry takes); 0: no such bin; -1: several views
+    int umma_long_rows = 0;                 // a tcgen05 item has more than 512 columns
     std::vector<BlkUmmaView> umma_viewsA, umma_viewsB;  // views of the operands the tcgen05 items refer to
     int small_K = 0;                        // uniform K of the small bin
     int small_pipe = 0;                     // 1: the small segments run as packs on the pipelined kernel

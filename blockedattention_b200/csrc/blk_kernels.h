@@ -67,6 +67,7 @@ struct BlkUmmaParams {
     float scale;
     int* status;
     int head_firstA, head_firstB;  // coordinate order of the operands' tensor maps
+    int long_rows;                 // some item has more than 512 columns (a fused softmax takes two sweeps there)
     // Test hook for the bounded waits: stall != 0 makes the producer role issue no copies at all (nothing is ever
     // in flight), so the first wait for operands runs out after spin_limit polls (0: the normal limit), the kernel
     // records BLK_ERR_TIMEOUT's status code and returns.
