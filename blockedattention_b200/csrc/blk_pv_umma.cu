@@ -13,7 +13,7 @@
 // two per column, row = lane).  The values are fetched by tiled TMA exactly as
 // they lie (MN-major second operand, 128-byte swizzle).
 //
-// A persistent CTA (one per SM, 14 warps) walks a static list of work items, an
+// A persistent CTA (one per SM, 22 warps) walks a static list of work items, an
 // item being a 128-row block of the first operand of one segment of one head; it
 // sweeps the contraction index in tiles of 128.  Roles:
 //   warp 0      producer: one lane issues the TMA loads of the value tiles into a ring;
@@ -21,9 +21,11 @@
 //               64-column buffers in tensor memory, O in one of two accumulators
 //               (items alternate); tcgen05.commit frees the value stage and the P
 //               buffer and, after an item's last tile, hands O to the output warps;
-//   warps 2-9   loaders: thread (quarter q, lane) owns row 32 q + lane of the block; the
-//               two warps of a quarter each bring 64 of the 128 columns of a tile;
-//   warps 10-13 output: read O, scale, round and store the rows (a row of the result is
+//   warps 2-17  loaders, two groups of eight, one per P buffer (so a group takes every other
+//               tile and the global loads of two tiles are in flight at a time): thread
+//               (quarter q, lane) owns row 32 q + lane of the block; the two warps of a
+//               quarter in a group each bring 64 of the 128 columns of a tile;
+//   warps 18-21 output: read O, scale, round and store the rows (a row of the result is
 //               D contiguous, 16-byte aligned elements).
 //
 // Columns of a tile past the end of a row (K) and rows past the end of the block
@@ -45,9 +47,13 @@ namespace {
 
 static_assert(BLK_UMMA_BM == 128, "a work item is a block of 128 rows: one accumulator lane per row");
 constexpr int PV_BK = 128;           // contraction elements per tile
-constexpr int PV_LOAD_WARPS = 8;
+constexpr int PV_LOAD_WARPS = 8;     // loader warps of a group: four lane quarters x two halves of a tile's 128 columns
+#ifndef PV_GROUPS_N
+#define PV_GROUPS_N 2
+#endif
+constexpr int PV_GROUPS = PV_GROUPS_N;  // groups of loader warps, one per tensor-memory buffer: their loads are in flight together
 constexpr int PV_OUT_WARPS = 4;
-constexpr int PV_THREADS = 64 + 32 * (PV_LOAD_WARPS + PV_OUT_WARPS);
+constexpr int PV_THREADS = 64 + 32 * (PV_LOAD_WARPS * PV_GROUPS + PV_OUT_WARPS);
 constexpr int PV_BLOCK_BYTES = 128 * 128;  // 128 value rows of one 64-column block: 16 KB
 constexpr int PV_O_COL = 256;              // tensor-memory columns of the two result accumulators: 256 and 384
 
@@ -183,9 +189,10 @@ blk_pv_umma_kernel(const BlkPvParams p, const __grid_constant__ CUtensorMap mapV
                 }
             }
         }
-    } else if (warp < 2 + PV_LOAD_WARPS) {
-        // ---------------- loaders: warps 2..9 ----------------
-        const int q = warp & 3, h = (warp - 2) >> 2;
+    } else if (warp < 2 + PV_LOAD_WARPS * PV_GROUPS) {
+        // ---------------- loaders: warps 2..17, group grp fills buffer grp (every other tile) ----------------
+        const int lw = (warp - 2) % PV_LOAD_WARPS, grp = (warp - 2) / PV_LOAD_WARPS;
+        const int q = warp & 3, h = lw >> 2;
         const int row = q * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         const unsigned char* A = reinterpret_cast<const unsigned char*>(p.A);
@@ -198,6 +205,7 @@ blk_pv_umma_kernel(const BlkPvParams p, const __grid_constant__ CUtensorMap mapV
             // byte address of this lane's row of the block
             const int64_t rowb = ((int64_t)wk.head * p.Dm1 + wk.it.offA + (int64_t)row * K) * 2;
             for (int j = 0; ok && j < wk.T; ++j, ++g) {
+                if (PV_GROUPS == 2 && (int)(g & 1u) != grp) continue;  // the other group's tile
                 const int buf = (int)(g & 1u), vs = (int)(g % VS);
                 const int ncols = min(K - j * PV_BK, PV_BK);
                 const int ksteps = (ncols + 15) >> 4;
@@ -254,7 +262,7 @@ blk_pv_umma_kernel(const BlkPvParams p, const __grid_constant__ CUtensorMap mapV
                     // last tile of the row: clear the value rows between its end and the next multiple of 16
                     if (!mbar_wait(v_full(vs), (g / VS) & 1u, abort_flag, p.status, 46)) { ok = false; break; }
                     const int nz = (16 - (ncols & 15)) * L::NB * 8;  // 16-byte pieces to clear
-                    const int t = (warp - 2) * 32 + lane;
+                    const int t = lw * 32 + lane;
                     if (t < nz) {
                         const int rr = t / (L::NB * 8), rem = t % (L::NB * 8);
                         tc_sts_v4(sV(vs) + (rem >> 3) * PV_BLOCK_BYTES + (ncols + rr) * 128 + (rem & 7) * 16, 0u, 0u, 0u, 0u);
@@ -267,7 +275,7 @@ blk_pv_umma_kernel(const BlkPvParams p, const __grid_constant__ CUtensorMap mapV
             }
         }
     } else {
-        // ---------------- output: warps 10..13 ----------------
+        // ---------------- output: the last four warps ----------------
         const int q = warp & 3;
         const int row = q * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
