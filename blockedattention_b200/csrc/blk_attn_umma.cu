@@ -49,7 +49,14 @@ namespace {
 
 constexpr int FA_BM = BLK_FLASH_BM;  // query rows per work item
 constexpr int FA_BN = 128;           // key / value rows per tile
-constexpr int FA_SOFT_WARPS = 8;
+// Softmax warps per accumulator-lane quarter: each takes 128 / FA_SPLIT key columns of a tile.  Two; four (22 warps of 80
+// registers) measured the same on the long batches and 2 % slower at d = 128 -- this kernel waits on the chain
+// QK^T -> softmax -> PV of a tile, not on the softmax warps' throughput.
+#ifndef FA_SPLIT_N
+#define FA_SPLIT_N 2
+#endif
+constexpr int FA_SPLIT = FA_SPLIT_N;
+constexpr int FA_SOFT_WARPS = 4 * FA_SPLIT;
 constexpr int FA_OUT_WARPS = 4;
 constexpr int FA_THREADS = 64 + 32 * (FA_SOFT_WARPS + FA_OUT_WARPS);
 constexpr int FA_BLOCK_BYTES = 128 * 128;  // 128 rows of one 64-column block: 16 KB
@@ -66,9 +73,9 @@ struct FL {
     static constexpr int K_OFF = OPER_BYTES;
     static constexpr int V_OFF = K_OFF + KS * OPER_BYTES;
     static constexpr int XCH_OFF = V_OFF + VS * OPER_BYTES;
-    static constexpr int XCH_BYTES = 2 * 2 * 128 * 4;       // row maxima: [exchange parity][half][row]
+    static constexpr int XCH_BYTES = 2 * FA_SPLIT * 128 * 4;  // row maxima: [exchange parity][part][row]
     static constexpr int LSUM_OFF = XCH_OFF + XCH_BYTES;
-    static constexpr int LSUM_BYTES = 2 * 2 * 128 * 4;      // row sums for the output warps: [result buffer][half][row]
+    static constexpr int LSUM_BYTES = 2 * FA_SPLIT * 128 * 4; // row sums for the output warps: [result buffer][part][row]
     static constexpr int BAR_OFF = LSUM_OFF + LSUM_BYTES;
     static constexpr int SMEM_BYTES = BAR_OFF + 512;
     static_assert(KS <= 6 && VS <= 6, "barrier slots");
@@ -141,7 +148,7 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             mbar_init(o_free(b), FA_OUT_WARPS);
             mbar_init(l_ready(b), FA_SOFT_WARPS);
         }
-        for (int i = 0; i < 4; ++i) mbar_init(bar0 + 8u * (14 + i), 2);
+        for (int i = 0; i < 4; ++i) mbar_init(bar0 + 8u * (14 + i), FA_SPLIT);
         for (int s = 0; s < KS; ++s) {
             mbar_init(k_full(s), 1);
             mbar_init(k_empty(s), 1);
@@ -279,21 +286,28 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
         const float sl = fabsf(p.scale) * BLK_LOG2E;  // a negative scale is applied by the MMA (negated Q)
         const uint32_t pair_bar = bar0 + 8u * (14 + q);
         uint32_t xc = 0;
-        // value a of this row to the partner warp, the partner's value back
+        constexpr int CW = (FA_BN + 0 * D) / FA_SPLIT;  // key columns of a tile this warp owns: 64 or 32 (written as depending on D so that the branches not taken are not instantiated)
+        // value a of this row to the other warps of the quarter, the maximum of theirs back
         auto exchange = [&](float a, float& other) -> bool {
-            volatile float* x = xch + (xc & 1u) * 256;
+            volatile float* x = xch + (xc & 1u) * (FA_SPLIT * 128);
             x[h * 128 + row] = a;
             __syncwarp();
             if (lane == 0) mbar_arrive(pair_bar);  // release: the warp's values are visible to whoever sees the phase end
             const bool good = mbar_wait(pair_bar, xc & 1u, abort_flag, p.status, 28);
             ++xc;
-            if (good) other = x[(h ^ 1) * 128 + row];
+            if (good) {
+                other = -INFINITY;
+#pragma unroll
+                for (int o = 0; o < FA_SPLIT; ++o)
+                    if (o != h) other = fmaxf(other, x[o * 128 + row]);
+            }
             return good;
         };
         uint32_t g = 0, itc = 0;
         FaWork wk;
         bool ok = true;
-        uint32_t ra[32], rb[32];
+        uint32_t ra[32];
+        [[maybe_unused]] uint32_t rb[CW == 64 ? 32 : 1];
         for (uint32_t w = blockIdx.x; ok && fa_work(p, w, wk); w += gridDim.x, ++itc) {
             const int ob = (int)(itc & 1u);
             float m_run = -INFINITY, l_run = 0.f;
@@ -301,26 +315,27 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 const int buf = (int)(g & 1u), vs = (int)(g % VS);
                 if (!mbar_wait(s_full(buf), (g >> 1) & 1u, abort_flag, p.status, 30)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t scol = lane_addr + (uint32_t)(buf * FA_BN + 64 * h);
+                const uint32_t scol = lane_addr + (uint32_t)(buf * FA_BN + CW * h);
                 tc_ld32_nowait(scol, ra);
-                tc_ld32_nowait(scol + 32, rb);
+                if constexpr (CW == 64) tc_ld32_nowait(scol + 32, rb);
                 tc_ld_wait();
                 const int ncols = min(wk.it.N - j * FA_BN, FA_BN);
-                const int lim = ncols - 64 * h;  // valid columns of this half
-                if (lim < 64) {
+                const int lim = ncols - CW * h;  // valid columns of this warp's share
+                if (lim < CW) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         if (i >= lim) ra[i] = 0xff800000u;  // -inf
-                        if (32 + i >= lim) rb[i] = 0xff800000u;
+                        if constexpr (CW == 64)
+                            if (32 + i >= lim) rb[i] = 0xff800000u;
                     }
                 }
                 float pm = -INFINITY;
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     pm = fmaxf(pm, fmaxf(__uint_as_float(ra[i]), __uint_as_float(ra[i + 1])));
-                    pm = fmaxf(pm, fmaxf(__uint_as_float(rb[i]), __uint_as_float(rb[i + 1])));
+                    if constexpr (CW == 64) pm = fmaxf(pm, fmaxf(__uint_as_float(rb[i]), __uint_as_float(rb[i + 1])));
                 }
-                // after this rendezvous both warps of the quarter have their scores in registers, so the
+                // after this rendezvous all warps of the quarter have their scores in registers, so the
                 // probabilities may overwrite the first 64 columns of the score buffer
                 float other;
                 if (!exchange(pm, other)) { ok = false; break; }
@@ -334,7 +349,7 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                 }
                 const float nm = -m_run * sl;
                 float s4[4] = {0.f, 0.f, 0.f, 0.f};
-                uint32_t pk[32];  // the 64 probabilities, two per word
+                uint32_t pk[CW / 2];  // the probabilities, two per word
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const float e0 = blk_exp2(fmaf(__uint_as_float(ra[i]), sl, nm));
@@ -343,13 +358,15 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                     s4[(i + 1) & 3] += e1;
                     pk[i >> 1] = BlkCvt<Tag>::pack2(e0, e1);
                 }
+                if constexpr (CW == 64) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float e0 = blk_exp2(fmaf(__uint_as_float(rb[i]), sl, nm));
-                    const float e1 = blk_exp2(fmaf(__uint_as_float(rb[i + 1]), sl, nm));
-                    s4[i & 3] += e0;
-                    s4[(i + 1) & 3] += e1;
-                    pk[16 + (i >> 1)] = BlkCvt<Tag>::pack2(e0, e1);
+                    for (int i = 0; i < 32; i += 2) {
+                        const float e0 = blk_exp2(fmaf(__uint_as_float(rb[i]), sl, nm));
+                        const float e1 = blk_exp2(fmaf(__uint_as_float(rb[i + 1]), sl, nm));
+                        s4[i & 3] += e0;
+                        s4[(i + 1) & 3] += e1;
+                        pk[16 + (i >> 1)] = BlkCvt<Tag>::pack2(e0, e1);
+                    }
                 }
                 l_run = l_run * f + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
                 // P V of tile g - 2 (long done: the scores of tile g were computed after it); waited for on every
@@ -359,17 +376,30 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
                     // a row's reference moved: rescale O, at rest once P V of the previous tile is done
                     if (!mbar_wait(pv_done(buf ^ 1), ((g - 1u) >> 1) & 1u, abort_flag, p.status, 34)) { ok = false; break; }
                     tc_fence_after();
+                    // this warp's D / FA_SPLIT columns of the result
+                    constexpr int OC = D / FA_SPLIT;
+                    if constexpr (OC >= 32) {
 #pragma unroll 1
-                    for (int c = 0; c < D / 2; c += 32) {
-                        const uint32_t ocol = lane_addr + (uint32_t)(FA_O_COL + 128 * ob + h * (D / 2) + c);
-                        tc_ld32(ocol, ra);
+                        for (int c = 0; c < OC; c += 32) {
+                            const uint32_t ocol = lane_addr + (uint32_t)(FA_O_COL + 128 * ob + h * OC + c);
+                            tc_ld32(ocol, ra);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * f);
-                        tc_st32(ocol, ra);
+                            for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * f);
+                            tc_st32(ocol, ra);
+                        }
+                    } else {
+                        static_assert(OC == 16 || OC >= 32, "result columns per softmax warp");
+                        uint32_t ro[16];
+                        const uint32_t ocol = lane_addr + (uint32_t)(FA_O_COL + 128 * ob + h * OC);
+                        tc_ld16(ocol, ro);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * f);
+                        tc_st16(ocol, ro);
                     }
                 }
-                // probabilities of this row, key columns [64 h, 64 h + 64): columns [32 h, 32 h + 32) of the score buffer
-                tc_st32(lane_addr + (uint32_t)(buf * FA_BN + 32 * h), pk);
+                // probabilities of this row, key columns [CW h, CW h + CW): columns [CW/2 h, CW/2 h + CW/2) of the score buffer
+                if constexpr (CW == 64) tc_st32(lane_addr + (uint32_t)(buf * FA_BN + 32 * h), pk);
+                else tc_st16(lane_addr + (uint32_t)(buf * FA_BN + 16 * h), pk);
                 tc_wait_st();
                 if (ncols & 15) {
                     // last tile of the segment: clear the value rows between its end and the next multiple of 16
@@ -389,7 +419,7 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             if (!ok) break;
             // row sums to the output warps; the slot is free once they have stored the item two before this one
             if (!mbar_wait(o_free(ob), ((itc >> 1) & 1u) ^ 1u, abort_flag, p.status, 33)) break;
-            lsum[(ob * 2 + h) * 128 + row] = l_run;
+            lsum[(ob * FA_SPLIT + h) * 128 + row] = l_run;
             __syncwarp();
             if (lane == 0) mbar_arrive(l_ready(ob));
         }
@@ -407,7 +437,10 @@ blk_attn_umma_kernel(const BlkFlashParams p, const __grid_constant__ CUtensorMap
             if (!mbar_wait(l_ready(ob), par, abort_flag, p.status, 35)) break;
             if (!mbar_wait(o_ready(ob), par, abort_flag, p.status, 36)) break;
             tc_fence_after();
-            const float inv = __frcp_rn(lsum[(ob * 2) * 128 + row] + lsum[(ob * 2 + 1) * 128 + row]);
+            float lrow = 0.f;
+#pragma unroll
+            for (int o = 0; o < FA_SPLIT; ++o) lrow += lsum[(ob * FA_SPLIT + o) * 128 + row];
+            const float inv = __frcp_rn(lrow);
             // a thread stores its row, 64 bytes at a time
             uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (int64_t)wk.head * p.out_head_stride +
                              (int64_t)(wk.it.rowQ + row) * p.out_row_stride;
