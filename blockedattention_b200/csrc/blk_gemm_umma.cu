@@ -130,6 +130,17 @@ __device__ __forceinline__ bool next_work(const BlkUmmaParams& p, uint32_t w, Wo
     return true;
 }
 
+// Two consecutive items of a CTA's walk pair up when both take the two-sweep softmax over the same number of chunks:
+// then the first sweep of the later one (special-function bound, stores nothing) is interleaved chunk by chunk with the
+// second sweep of the earlier one (bound by the stores).  nx receives the later item.
+__device__ __forceinline__ bool pairs_with_next(const BlkUmmaParams& p, uint32_t w, const Work& wk, Work& nx) {
+#ifdef UM_NO_PAIRING
+    return false;
+#else
+    return wk.sweeps == 2 && next_work(p, w + gridDim.x, nx) && nx.sweeps == 2 && nx.nchunks == wk.nchunks;
+#endif
+}
+
 // Predicated global stores as single instructions (no branch around them).
 __device__ __forceinline__ void stg_b32_if(void* p, uint32_t v, bool ok) {
     asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %2, 0;\n @q st.global.b32 [%0], %1;\n}\n" ::"l"(p), "r"(v), "r"((int)ok)
@@ -208,21 +219,35 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
             uint32_t phase = 0;
             Work wk;
             bool ok = true;
+            // the operand tiles of chunk ch of an item
+            auto load_chunk = [&](const Work& k, int ch) {
+                for (int kb = 0; kb < k.nkb; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, lim)) { ok = false; return; }
+                    const uint32_t sA = smem_u32 + stage * UM_STAGE_BYTES, sB = sA + UM_A_BYTES;
+                    mbar_expect_tx(full_bar(stage), UM_STAGE_BYTES);
+                    // coordinates (k, row, head), or (k, head, row) for a token-major operand
+                    const int rA = k.it.rowA, rB = k.it.rowB + ch * UM_BN;
+                    tma_load_3d(sA, &maps.a[k.it.views & 255], full_bar(stage), kb * UM_BK, p.head_firstA ? k.head : rA,
+                                p.head_firstA ? rA : k.head);
+                    tma_load_3d(sB, &maps.b[k.it.views >> 8], full_bar(stage), kb * UM_BK, p.head_firstB ? k.head : rB,
+                                p.head_firstB ? rB : k.head);
+                    if (++stage == UM_STAGES) { stage = 0; phase ^= 1u; }
+                }
+            };
+            // the order of the chunks is that of the arithmetic warps (see there): first sweep (unless it ran alongside
+            // the previous item), then the storing chunks, each followed by a first-sweep chunk of the next item when
+            // the two items pair up
+            Work nx;
+            bool pre = false;
             for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x) {
-                for (int sw = 0; ok && sw < wk.sweeps; ++sw)
-                    for (int ch = wk.it.ch0; ok && ch < wk.it.ch0 + wk.nchunks; ++ch)
-                        for (int kb = 0; kb < wk.nkb; ++kb) {
-                            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, lim)) { ok = false; break; }
-                            const uint32_t sA = smem_u32 + stage * UM_STAGE_BYTES, sB = sA + UM_A_BYTES;
-                            mbar_expect_tx(full_bar(stage), UM_STAGE_BYTES);
-                            // coordinates (k, row, head), or (k, head, row) for a token-major operand
-                            const int rA = wk.it.rowA, rB = wk.it.rowB + ch * UM_BN;
-                            tma_load_3d(sA, &maps.a[wk.it.views & 255], full_bar(stage), kb * UM_BK, p.head_firstA ? wk.head : rA,
-                                        p.head_firstA ? rA : wk.head);
-                            tma_load_3d(sB, &maps.b[wk.it.views >> 8], full_bar(stage), kb * UM_BK, p.head_firstB ? wk.head : rB,
-                                        p.head_firstB ? rB : wk.head);
-                            if (++stage == UM_STAGES) { stage = 0; phase ^= 1u; }
-                        }
+                const bool pair = pairs_with_next(p, w, wk, nx);
+                if (wk.sweeps == 2 && !pre)
+                    for (int ch = 0; ok && ch < wk.nchunks; ++ch) load_chunk(wk, ch);
+                for (int ch = wk.it.ch0; ok && ch < wk.it.ch0 + wk.nchunks; ++ch) {
+                    load_chunk(wk, ch);
+                    if (ok && pair) load_chunk(nx, ch);
+                }
+                pre = pair;
             }
         }
     } else if (warp == 1) {
@@ -232,33 +257,41 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
             uint32_t phase = 0, slot = 0;
             Work wk;
             bool ok = true;
-            for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x) {
-                for (int sw = 0; ok && sw < wk.sweeps; ++sw)
-                    for (int ch = wk.it.ch0; ok && ch < wk.it.ch0 + wk.nchunks; ++ch) {
-                        const int buf = slot & 1;
-                        if (!mbar_wait(tempty_bar(buf), ((slot >> 1) & 1u) ^ 1u, abort_flag, p.status, 2, lim)) { ok = false; break; }
-                        tc_fence_after();
-                        const int ncols = min(wk.it.N - ch * UM_BN, UM_BN);
-                        const uint32_t idesc = instr_desc(p.bf16, (ncols + 15) & ~15, p.epi == BLK_EPI_SOFTMAX && p.scale < 0.f);
-                        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * UM_BN);
-                        for (int kb = 0; kb < wk.nkb; ++kb) {
-                            if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, lim)) { ok = false; break; }
-                            tc_fence_after();
-                            const uint32_t sA = smem_u32 + stage * UM_STAGE_BYTES, sB = sA + UM_A_BYTES;
-                            // steps of 16 along k in this block: all four, or as many as reach the end of a short last block
-                            const int ksteps = min(UM_BK / 16, (wk.it.K - kb * UM_BK + 15) / 16);
+            // the products of chunk ch of an item into the next accumulator
+            auto mma_chunk = [&](const Work& k, int ch) {
+                const int buf = slot & 1;
+                if (!mbar_wait(tempty_bar(buf), ((slot >> 1) & 1u) ^ 1u, abort_flag, p.status, 2, lim)) { ok = false; return; }
+                tc_fence_after();
+                const int ncols = min(k.it.N - ch * UM_BN, UM_BN);
+                const uint32_t idesc = instr_desc(p.bf16, (ncols + 15) & ~15, p.epi == BLK_EPI_SOFTMAX && p.scale < 0.f);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * UM_BN);
+                for (int kb = 0; kb < k.nkb; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, lim)) { ok = false; return; }
+                    tc_fence_after();
+                    const uint32_t sA = smem_u32 + stage * UM_STAGE_BYTES, sB = sA + UM_A_BYTES;
+                    // steps of 16 along k in this block: all four, or as many as reach the end of a short last block
+                    const int ksteps = min(UM_BK / 16, (k.it.K - kb * UM_BK + 15) / 16);
 #pragma unroll
-                            for (int k = 0; k < UM_BK / 16; ++k)
-                                if (k < ksteps)
-                                    tc_mma_f16(d_tmem, smem_desc_sw128(sA + 32 * k), smem_desc_sw128(sB + 32 * k), idesc,
-                                               (kb | k) != 0);
-                            tc_commit(empty_bar(stage));  // stage reusable once these products have read it
-                            if (++stage == UM_STAGES) { stage = 0; phase ^= 1u; }
-                        }
-                        if (!ok) break;
-                        tc_commit(tfull_bar(buf));
-                        ++slot;
-                    }
+                    for (int j = 0; j < UM_BK / 16; ++j)
+                        if (j < ksteps)
+                            tc_mma_f16(d_tmem, smem_desc_sw128(sA + 32 * j), smem_desc_sw128(sB + 32 * j), idesc, (kb | j) != 0);
+                    tc_commit(empty_bar(stage));  // stage reusable once these products have read it
+                    if (++stage == UM_STAGES) { stage = 0; phase ^= 1u; }
+                }
+                tc_commit(tfull_bar(buf));
+                ++slot;
+            };
+            Work nx;
+            bool pre = false;
+            for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x) {
+                const bool pair = pairs_with_next(p, w, wk, nx);
+                if (wk.sweeps == 2 && !pre)
+                    for (int ch = 0; ok && ch < wk.nchunks; ++ch) mma_chunk(wk, ch);
+                for (int ch = wk.it.ch0; ok && ch < wk.it.ch0 + wk.nchunks; ++ch) {
+                    mma_chunk(wk, ch);
+                    if (ok && pair) mma_chunk(nx, ch);
+                }
+                pre = pair;
             }
         }
     } else if (warp >= 2 + UM_EPI_WARPS) {
@@ -475,14 +508,74 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
                 }
             };
         };
-        for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x, ++seq) {
+        // First sweep of a row too long for tensor memory, one chunk: running (maximum, sum) over this warp's blocks.
+        float mx1 = -INFINITY, sum1 = 0.f;
+        auto first_sweep_chunk = [&](int N, int ch) {
+            uint32_t r[32];
+            const int buf = slot & 1;
+            if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 6, lim)) { ok = false; return; }
+            tc_fence_after();
+            const int ncols = min(N - ch * UM_BN, UM_BN);
+            for (int b0 = h * SH; b0 < ncols; b0 += PC) {
+                const int hi = min(b0 + SH, ncols);
+                for (int c = b0; c < hi; c += UM_PIECE) {
+                    tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c), r);
+                    const bool part = c + 32 > hi;
+                    if (part) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (c + i >= hi) r[i] = 0xff800000u;  // -inf
+                    }
+                    float pm = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) pm = blk_max3(pm, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                    const float mnew = fmaxf(mx1, pm);  // finite: column c of the piece is inside the row
+                    const float nm = -mnew * sl;
+                    float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) s4[i & 3] += blk_exp2(fmaf(__uint_as_float(r[i]), sl, nm));
+                    sum1 = sum1 * blk_exp2((mx1 - mnew) * sl) + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+                    mx1 = mnew;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(buf));
+            ++slot;
+        };
+        // The quarter's warps combine their (maximum, sum) of a finished first sweep; the result is the offset with which
+        // exp2(x * sl + off) = exp2((x - max) * sl) / sum: no multiply after the exponential in the second sweep.
+        float off_next = 0.f;
+        auto first_sweep_done = [&]() {
+            volatile float* xm = xch + (seq++ & 1) * (2 * UM_SPLIT * 128);  // [part][row] maxima, then [UM_SPLIT + part][row] sums
+            xm[h * 128 + myrow] = mx1;
+            xm[(UM_SPLIT + h) * 128 + myrow] = sum1;
+            if (!pair_sync()) { ok = false; return; }
+            // a warp whose share held no column of the row (a last chunk of at most 64 columns) has maximum -inf
+            // and sum 0: its term is skipped
+            float m = -INFINITY;
+#pragma unroll
+            for (int o = 0; o < UM_SPLIT; ++o) m = fmaxf(m, xm[o * 128 + myrow]);
+            float l = 0.f;
+#pragma unroll
+            for (int o = 0; o < UM_SPLIT; ++o) {
+                const float mo = xm[o * 128 + myrow];
+                if (mo != -INFINITY) l += xm[(UM_SPLIT + o) * 128 + myrow] * blk_exp2((mo - m) * sl);
+            }
+            off_next = -m * sl - __log2f(l);
+        };
+        Work nx;
+        bool pre = false;  // this item's first sweep ran alongside the previous item's second
+        for (uint32_t w = blockIdx.x; ok && next_work(p, w, wk); w += gridDim.x) {
+            const bool pair = pairs_with_next(p, w, wk, nx);
+            const bool had_first = pre;
+            pre = pair;
             const int M = wk.it.M - wk.it.tm * UM_BM;  // rows of the segment from this block on
             const int N = wk.it.N;
             const int64_t cbase = (int64_t)wk.head * p.Dout + wk.it.offC + (int64_t)wk.it.tm * UM_BM * N;
             // 16-bit rows that start on an odd element need the half-word shift while staging (chunks and pieces start
             // on even columns, so a row's parity is the same for all of them); the quarter's warps hold the same rows
             const bool anyodd = !OUT32 && __any_sync(0xffffffffu, (int)((cbase + (int64_t)myrow * N) & 1));
-            volatile float* xm = xch + (seq & 1) * (2 * UM_SPLIT * 128);  // [part][row] maxima, then [UM_SPLIT + part][row] sums
             if (!softmax) {
                 for (int ch = wk.it.ch0; ok && ch < wk.it.ch0 + wk.nchunks; ++ch, ++slot) {
                     const int buf = slot & 1;
@@ -500,6 +593,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
                 }
             } else if (wk.sweeps == 1) {
                 // whole row resident: chunk k of the row sits in accumulator (slot + k) & 1
+                volatile float* xm = xch + (seq++ & 1) * (2 * UM_SPLIT * 128);  // [part][row] maxima, then [UM_SPLIT + part][row] sums
                 for (int ch = 0; ok && ch < wk.nchunks; ++ch)
                     if (!mbar_wait(tfull_bar((slot + ch) & 1), ((slot + ch) >> 1) & 1u, abort_flag, p.status, 5, lim)) ok = false;
                 if (!ok) break;
@@ -567,61 +661,18 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
                 }
                 slot += wk.nchunks;
             } else {
-                // two sweeps: running (max, sum) over this warp's blocks, then recompute and stage
-                float mx = -INFINITY, sum = 0.f;
-                uint32_t r[32];
-                for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
-                    const int buf = slot & 1;
-                    if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 6, lim)) { ok = false; break; }
-                    tc_fence_after();
-                    const int ncols = min(N - ch * UM_BN, UM_BN);
-                    for (int b0 = h * SH; b0 < ncols; b0 += PC) {
-                        const int hi = min(b0 + SH, ncols);
-                        for (int c = b0; c < hi; c += UM_PIECE) {
-                            tc_ld32(lane_addr + (uint32_t)(buf * UM_BN + c), r);
-                            const bool part = c + 32 > hi;
-                            if (part) {
-#pragma unroll
-                                for (int i = 0; i < 32; ++i)
-                                    if (c + i >= hi) r[i] = 0xff800000u;  // -inf
-                            }
-                            float pm = -INFINITY;
-#pragma unroll
-                            for (int i = 0; i < 32; i += 2) pm = blk_max3(pm, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-                            const float mnew = fmaxf(mx, pm);  // finite: column c of the piece is inside the row
-                            const float nm = -mnew * sl;
-                            float s4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) s4[i & 3] += blk_exp2(fmaf(__uint_as_float(r[i]), sl, nm));
-                            sum = sum * blk_exp2((mx - mnew) * sl) + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
-                            mx = mnew;
-                        }
-                    }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                // two sweeps: running (max, sum) over this warp's blocks, then recompute and stage; when the next item
+                // pairs with this one, each storing chunk is followed by a first-sweep chunk of the next item, whose
+                // exponentials run while this chunk's pieces drain
+                if (!had_first) {
+                    mx1 = -INFINITY; sum1 = 0.f;
+                    for (int ch = 0; ok && ch < wk.nchunks; ++ch) first_sweep_chunk(N, ch);
+                    if (ok) first_sweep_done();
+                    if (!ok) break;
                 }
-                if (!ok) break;
-                xm[h * 128 + myrow] = mx;
-                xm[(UM_SPLIT + h) * 128 + myrow] = sum;
-                if (!pair_sync()) { ok = false; break; }
-                {
-                    // a warp whose share held no column of the row (a last chunk of at most 64 columns) has maximum -inf
-                    // and sum 0: its term is skipped
-                    float m = -INFINITY;
-#pragma unroll
-                    for (int o = 0; o < UM_SPLIT; ++o) m = fmaxf(m, xm[o * 128 + myrow]);
-                    float l = 0.f;
-#pragma unroll
-                    for (int o = 0; o < UM_SPLIT; ++o) {
-                        const float mo = xm[o * 128 + myrow];
-                        if (mo != -INFINITY) l += xm[(UM_SPLIT + o) * 128 + myrow] * blk_exp2((mo - m) * sl);
-                    }
-                    mx = m;
-                    sum = l;
-                }
-                const float off = -mx * sl - __log2f(sum);  // exp2(x * sl + off) = exp2((x - max) * sl) / sum: no multiply after the exponential
-                for (int ch = 0; ok && ch < wk.nchunks; ++ch, ++slot) {
+                const float off = off_next;
+                if (pair) { mx1 = -INFINITY; sum1 = 0.f; }
+                for (int ch = 0; ok && ch < wk.nchunks; ++ch) {
                     const int buf = slot & 1;
                     if (!mbar_wait(tfull_bar(buf), (slot >> 1) & 1u, abort_flag, p.status, 7, lim)) { ok = false; break; }
                     tc_fence_after();
@@ -635,7 +686,10 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
                                     [&](int c) { return (uint32_t)(buf * UM_BN + (c - ch * UM_BN)); },
                                     pack_with([sl, off](float x) { return blk_exp2(fmaf(x, sl, off)); }), cbase, M, N, anyodd,
                                     release);
+                    ++slot;
+                    if (ok && pair) first_sweep_chunk(nx.it.N, ch);
                 }
+                if (ok && pair) first_sweep_done();
             }
         }
         // tell the quarter's two store warps that nothing follows: one more "piece" per strip that only says stop
