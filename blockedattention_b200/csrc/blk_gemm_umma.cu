@@ -1,7 +1,7 @@
 // Large-segment kernel of the varlen blocked GEMM on the 5th-generation tensor
 // cores: TMA-fed tcgen05.mma with the accumulator in tensor memory.
 //
-// A persistent CTA (one per SM; 22 warps with 16-bit results, 14 with fp32 results) walks a static list of work
+// A persistent CTA (one per SM; 22 warps for the two-sweep fused softmax, 14 otherwise) walks a static list of work
 // items, an item being a 128-row block of one segment of one head (or one 256-column chunk of it).  Roles:
 //   warp 0   producer: one lane issues 3-D tiled TMA loads (k, row, head) of a
 //            128 x 64 tile of the first operand and a 256 x 64 tile of the
@@ -10,9 +10,9 @@
 //            tcgen05.mma (M = 128, N up to 256, K = 16 per instruction) into
 //            one of two 256-column accumulators; tcgen05.commit hands shared
 //            memory stages back to the producer and accumulators to the epilogue;
-//   next 16 (8) warps  epilogue arithmetic: a warp may read the 32 accumulator lanes (= rows)
-//            of its quarter; the four (two) warps of a quarter each take 32 (32) of every 128 (64)
-//            columns of the row and exchange partial row statistics through
+//   next 16 or 8 warps  epilogue arithmetic: a warp may read the 32 accumulator lanes (= rows)
+//            of its quarter; the four or two warps of a quarter (SPLIT) each take an equal share of every
+//            staged piece's columns and exchange partial row statistics through
 //            shared memory.  A thread reads its row 32 columns at a time
 //            (tcgen05.ld), applies the epilogue and writes the packed words into
 //            one of the quarter's two strips (32 rows x 128 16-bit or 64 fp32 columns each, used
@@ -37,7 +37,8 @@
 // the exponential is evaluated once per element and the scores never leave the
 // SM.  Softmax with N > 512: the products are computed twice -- a first sweep
 // over the 256-column chunks keeps only a running (max, sum) per row, a second
-// sweep recomputes each chunk and stores normalised probabilities.
+// sweep recomputes each chunk and stores normalised probabilities; when the CTA's next item is of the same kind and
+// length, its first sweep is interleaved chunk by chunk with this item's second.
 //
 // Rows of the operand views past the end of a segment belong to its neighbour
 // (or are zero-filled past the end of the buffer); they only reach accumulator
@@ -295,7 +296,7 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
             }
         }
     } else if (warp >= 2 + UM_EPI_WARPS) {
-        // ---------------- stores: warps 10..17, one per quarter and strip ----------------
+        // ---------------- stores: the last four warps, one per quarter ----------------
         const int sq = warp & 3;
         unsigned char* const C = reinterpret_cast<unsigned char*>(p.C);
         constexpr int ES = OUT32 ? 4 : 2;
@@ -381,8 +382,8 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
             if (lane == 0) mbar_arrive(drained_bar);
         }
     } else {
-        // ---------------- epilogue arithmetic: warps 2..9 ----------------
-        // lane quarter q = warp % 4 (the 32 accumulator lanes a warp may read); the two warps of a quarter split the
+        // ---------------- epilogue arithmetic: warps 2 .. 2 + 4 SPLIT - 1 ----------------
+        // lane quarter q = warp % 4 (the 32 accumulator lanes a warp may read); the SPLIT warps of a quarter split the
         // columns (share h: the columns c of a chunk with (c mod PC) / SH == h) and exchange their partial row
         // statistics.
         const int q = warp & 3, h = (warp - 2) >> 2;  // h in [0, UM_SPLIT)
@@ -692,7 +693,8 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
                 if (ok && pair) first_sweep_done();
             }
         }
-        // tell the quarter's two store warps that nothing follows: one more "piece" per strip that only says stop
+        // tell the quarter's store warp that nothing follows: one more "piece" that only says stop (posted on both strips;
+        // the store warp leaves at the first)
         for (int t = 0; t < 2; ++t) {
             const int sb = (int)(pieces & 1u);
             const uint32_t filled_bar = bar0 + 8u * (20 + q * 2 + sb), drained_bar = bar0 + 8u * (28 + q * 2 + sb);
