@@ -51,6 +51,20 @@ struct SpIO16<BlkHalfTag> {
         return make_uint4(BlkCvt<BlkHalfTag>::pack2(f[0], f[1]), BlkCvt<BlkHalfTag>::pack2(f[2], f[3]),
                           BlkCvt<BlkHalfTag>::pack2(f[4], f[5]), BlkCvt<BlkHalfTag>::pack2(f[6], f[7]));
     }
+    // running extreme (maximum, or minimum for a negative scale) of a row, taken on the packed pairs as they lie in
+    // memory: one instruction per two elements and no conversion
+    typedef uint32_t X;
+    template <bool NEG> static __device__ __forceinline__ X xinit() { return NEG ? 0x7c007c00u : 0xfc00fc00u; }
+    template <bool NEG> static __device__ __forceinline__ X xacc(X a, const uint4& q) {
+        X r;
+        if (NEG) asm("{\n .reg .b32 t, u;\n min.f16x2 t, %1, %2;\n min.f16x2 u, %3, %4;\n min.f16x2 t, t, u;\n min.f16x2 %0, t, %5;\n}\n" : "=r"(r) : "r"(q.x), "r"(q.y), "r"(q.z), "r"(q.w), "r"(a));
+        else asm("{\n .reg .b32 t, u;\n max.f16x2 t, %1, %2;\n max.f16x2 u, %3, %4;\n max.f16x2 t, t, u;\n max.f16x2 %0, t, %5;\n}\n" : "=r"(r) : "r"(q.x), "r"(q.y), "r"(q.z), "r"(q.w), "r"(a));
+        return r;
+    }
+    template <bool NEG> static __device__ __forceinline__ float xfin(X a) {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&a));
+        return NEG ? fminf(t.x, t.y) : fmaxf(t.x, t.y);
+    }
 };
 template <>
 struct SpIO16<BlkBf16Tag> {
@@ -70,6 +84,18 @@ struct SpIO16<BlkBf16Tag> {
         return make_uint4(BlkCvt<BlkBf16Tag>::pack2(f[0], f[1]), BlkCvt<BlkBf16Tag>::pack2(f[2], f[3]),
                           BlkCvt<BlkBf16Tag>::pack2(f[4], f[5]), BlkCvt<BlkBf16Tag>::pack2(f[6], f[7]));
     }
+    typedef uint32_t X;
+    template <bool NEG> static __device__ __forceinline__ X xinit() { return NEG ? 0x7f807f80u : 0xff80ff80u; }
+    template <bool NEG> static __device__ __forceinline__ X xacc(X a, const uint4& q) {
+        X r;
+        if (NEG) asm("{\n .reg .b32 t, u;\n min.bf16x2 t, %1, %2;\n min.bf16x2 u, %3, %4;\n min.bf16x2 t, t, u;\n min.bf16x2 %0, t, %5;\n}\n" : "=r"(r) : "r"(q.x), "r"(q.y), "r"(q.z), "r"(q.w), "r"(a));
+        else asm("{\n .reg .b32 t, u;\n max.bf16x2 t, %1, %2;\n max.bf16x2 u, %3, %4;\n max.bf16x2 t, t, u;\n max.bf16x2 %0, t, %5;\n}\n" : "=r"(r) : "r"(q.x), "r"(q.y), "r"(q.z), "r"(q.w), "r"(a));
+        return r;
+    }
+    template <bool NEG> static __device__ __forceinline__ float xfin(X a) {
+        const float lo = __uint_as_float(a << 16), hi = __uint_as_float(a & 0xffff0000u);
+        return NEG ? fminf(lo, hi) : fmaxf(lo, hi);
+    }
 };
 struct SpIO32 {
     typedef float E;
@@ -82,6 +108,13 @@ struct SpIO32 {
     static __device__ __forceinline__ uint4 pack(const float (&f)[4]) {
         return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
     }
+    typedef float X;
+    template <bool NEG> static __device__ __forceinline__ X xinit() { return NEG ? INFINITY : -INFINITY; }
+    template <bool NEG> static __device__ __forceinline__ X xacc(X a, const uint4& q) {
+        const float x = __uint_as_float(q.x), y = __uint_as_float(q.y), z = __uint_as_float(q.z), w = __uint_as_float(q.w);
+        return NEG ? fminf(fminf(a, x), fminf(fminf(y, z), w)) : fmaxf(fmaxf(a, x), fmaxf(fmaxf(y, z), w));
+    }
+    template <bool NEG> static __device__ __forceinline__ float xfin(X a) { return a; }
 };
 
 __device__ __forceinline__ float sp_max(float v, int G) {
@@ -203,22 +236,19 @@ __device__ __forceinline__ void fwd_rows_vec(typename IO::E* piece, int rows, in
         if (rs.xi >= 0) rs.row[rs.xi] = IO::st(x * inv);
     }
 }
-// forward, any column count that fits the window: three passes over the row, exponential evaluated twice
-template <typename IO, int NW>
-__device__ __forceinline__ void fwd_rows_vec_streamed(typename IO::E* piece, int rows, int cols, float sl, int warp,
-                                                      int lane) {
+// forward, any column count that fits the window: three passes over the row, exponential evaluated twice.  The first
+// pass takes the extreme of the raw packed elements; the third folds the normalisation into the exponent.
+template <typename IO, int NW, bool NEG>
+__device__ __forceinline__ void fwd_rows_vec_streamed_impl(typename IO::E* piece, int rows, int cols, float sl, int warp,
+                                                           int lane) {
     constexpr int VE = IO::VE;
     for (int r = warp; r < rows; r += NW) {
         RowSplit<IO> rs(piece + (size_t)r * cols, cols, lane);
         const float x = rs.xi >= 0 ? IO::ld(rs.row[rs.xi]) * sl : -INFINITY;
         float f[VE];
-        float mx = x;
-        for (int vi = lane; vi < rs.nv; vi += 32) {
-            IO::unpack(rs.body[vi], f);
-#pragma unroll
-            for (int e = 0; e < VE; ++e) mx = fmaxf(mx, f[e] * sl);
-        }
-        mx = sp_max(mx, 32);
+        typename IO::X ex = IO::template xinit<NEG>();
+        for (int vi = lane; vi < rs.nv; vi += 32) ex = IO::template xacc<NEG>(ex, rs.body[vi]);
+        const float mx = sp_max(fmaxf(x, IO::template xfin<NEG>(ex) * sl), 32);
         float sum = blk_exp2(x - mx);
         for (int vi = lane; vi < rs.nv; vi += 32) {
             IO::unpack(rs.body[vi], f);
@@ -226,15 +256,21 @@ __device__ __forceinline__ void fwd_rows_vec_streamed(typename IO::E* piece, int
             for (int e = 0; e < VE; ++e) sum += blk_exp2(fmaf(f[e], sl, -mx));
         }
         sum = sp_sum(sum, 32);
-        const float inv = 1.f / sum;
+        const float off = -mx - __log2f(sum);  // exp2(x * sl + off) = exp2(x * sl - max) / sum
         for (int vi = lane; vi < rs.nv; vi += 32) {
             IO::unpack(rs.body[vi], f);
 #pragma unroll
-            for (int e = 0; e < VE; ++e) f[e] = blk_exp2(fmaf(f[e], sl, -mx)) * inv;
+            for (int e = 0; e < VE; ++e) f[e] = blk_exp2(fmaf(f[e], sl, off));
             rs.body[vi] = IO::pack(f);
         }
-        if (rs.xi >= 0) rs.row[rs.xi] = IO::st(blk_exp2(x - mx) * inv);
+        if (rs.xi >= 0) rs.row[rs.xi] = IO::st(blk_exp2(x + off));
     }
+}
+template <typename IO, int NW>
+__device__ __forceinline__ void fwd_rows_vec_streamed(typename IO::E* piece, int rows, int cols, float sl, int warp,
+                                                      int lane) {
+    if (sl < 0.f) fwd_rows_vec_streamed_impl<IO, NW, true>(piece, rows, cols, sl, warp, lane);
+    else fwd_rows_vec_streamed_impl<IO, NW, false>(piece, rows, cols, sl, warp, lane);
 }
 // backward over whole vectors, two passes (dot product, then the result over the gradient)
 template <typename IO, int NW>
