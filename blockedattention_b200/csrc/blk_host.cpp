@@ -583,7 +583,7 @@ int blk_build_softmax_schedule(blk_plan* p) {
         }
         if (count > cap) {
             blk_set_error("softmax plan: this batch needs more than " + std::to_string(cap) +
-                          " chunks of 16 KB (a row longer than 16 KB is one chunk)");
+                          " chunks of 12 KB (a row longer than 12 KB is one chunk)");
             return BLK_ERR_UNSUPPORTED;
         }
     }

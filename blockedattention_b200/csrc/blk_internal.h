@@ -146,7 +146,10 @@ constexpr int BLK_SMALL_BUCKETS = 2;  // N <= 32, N <= 64
 constexpr int BLK_PACK_ROWS = 192;    // rows of each operand a pack may hold
 constexpr int BLK_PACK_ROWS_ATTN = 128;  // same for the attention variant, whose slots hold a third operand
 constexpr int BLK_PACK_BLOCKS = 16;   // segments a pack may hold
-constexpr int BLK_SMX_WINDOW_BYTES = 16384;
+// Shared-memory window of the softmax kernels: 12 KB lets eight CTAs of the pipelined forward kernel (two windows each)
+// and four of the backward kernel (four) share an SM; with 16 KB and six / three the CTA-wide barriers of a window were
+// hidden less well (5 to 10 % slower on every buffer but the longest rows).
+constexpr int BLK_SMX_WINDOW_BYTES = 12288;
 constexpr int BLK_UMMA_BM = 128;
 constexpr int BLK_FLASH_BM = 128;
 constexpr int BLK_NOALLOC_MAX_CHUNKS = 65536;  // entries of the built-in chunk table of blk_softmax_noalloc

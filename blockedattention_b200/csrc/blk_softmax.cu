@@ -1,7 +1,7 @@
 // Varlen row softmax over a packed (H, D) buffer: out = softmax_rows(scale * src).
 //
 // A CTA owns a chunk of consecutive rows of one segment of one head whose
-// bytes fit a 16 KB shared-memory window.  Rows of a packed segment start at
+// bytes fit a 12 KB shared-memory window.  Rows of a packed segment start at
 // arbitrary element offsets, so the CTA moves the chunk as a flat byte range:
 // 16-byte vectors for every vector that lies wholly inside the chunk, single
 // elements for the (at most two) ragged edge vectors.  Global traffic is thus

@@ -1,7 +1,7 @@
 // Pipelined varlen row softmax, forward and backward, over a packed (H, D) buffer.
 //
 // The host groups consecutive row pieces (blk_softmax.cu's chunks) whose bytes are contiguous in memory into
-// windows of at most 16 KB -- many small segments, or a few rows of a wide one.  A persistent CTA walks windows
+// windows of at most 12 KB -- many small segments, or a few rows of a wide one.  A persistent CTA walks windows
 // w = blockIdx.x, + gridDim.x, ... of the (window, head) list with two shared-memory stages:
 //   * one thread fetches the next window with a bulk asynchronous copy (cp.async.bulk, completion on the
 //     stage's mbarrier) of the 16-byte aligned range that covers it -- no thread waits for a load it issued;
@@ -391,7 +391,7 @@ __device__ __forceinline__ float sp_cta_reduce(float v, bool is_max, float* red,
 
 // BWD = false: in0 = src, result = softmax; BWD = true: in0 = forward result, in1 = its gradient.
 template <typename IO, bool BWD>
-__global__ void __launch_bounds__(SP_THREADS, BWD ? 3 : 6) blk_softmax_pipe_kernel(const BlkSmxPipeParams p) {
+__global__ void __launch_bounds__(SP_THREADS, BWD ? 4 : 8) blk_softmax_pipe_kernel(const BlkSmxPipeParams p) {
     typedef typename IO::E E;
     constexpr int ES = (int)sizeof(E);
     constexpr int NIN = BWD ? 2 : 1;
@@ -519,7 +519,7 @@ cudaError_t blk_launch_softmax_pipe(const BlkSmxPipeParams& p, int dtype, int ba
         const int smem = 2 * nin * SP_BUF;
         cudaError_t e = blk_func_smem(reinterpret_cast<const void*>(kern), smem);
         if (e != cudaSuccess) return e;
-        const int64_t resident = (int64_t)sms * (nin == 1 ? 6 : 3);
+        const int64_t resident = (int64_t)sms * (nin == 1 ? 8 : 4);
         const dim3 grid((unsigned)(total < resident ? total : resident)), block(SP_THREADS);
         kern<<<grid, block, smem, st>>>(p);
         return cudaGetLastError();

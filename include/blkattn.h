@@ -203,8 +203,8 @@ BLK_API int blk_softmax_backward_run(const blk_plan_t* plan, const void* out, co
  * plan: rows and cols are host lists (packed offsets), and the chunk table a
  * plan would upload into allocated memory goes into a fixed 1 MB array that
  * every GPU loading the library carries until exit.  Limit: the batch may need
- * at most 65536 chunks (a chunk covers up to 16 KB of one head's rows; a row
- * longer than 16 KB is one chunk) -- larger batches get BLK_ERR_UNSUPPORTED,
+ * at most 65536 chunks (a chunk covers up to 12 KB of one head's rows; a row
+ * longer than 12 KB is one chunk) -- larger batches get BLK_ERR_UNSUPPORTED,
  * decided from the lists before anything is built, and should use the plan
  * entry points.  The call performs no cudaMalloc/cudaFree: it copies the table
  * with cudaMemcpyAsync from ordinary host memory (the runtime stages that copy

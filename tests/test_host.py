@@ -175,7 +175,8 @@ def test_schedule_rejects_bad_input():
 
 def test_softmax_schedule_chunks():
     p = SoftmaxPlan([127] * 3, [2047] * 3, 7, torch.float16)
-    assert p.summary["softmax_chunks"] == 3 * 32 and p.D == 3 * 127 * 2047
+    # rows of 4094 bytes: three fit a 12 KB window, so 127 rows make 43 chunks
+    assert p.summary["softmax_chunks"] == 3 * 43 and p.D == 3 * 127 * 2047
     p = SoftmaxPlan([3, 0, 2], [20000, 5, 0], 1, torch.float32)   # rows longer than the window: one chunk per row
     assert p.summary["softmax_chunks"] == 3
     p = SoftmaxPlan([], [], 4, torch.bfloat16)
