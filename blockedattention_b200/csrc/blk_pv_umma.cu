@@ -52,6 +52,9 @@ constexpr int PV_LOAD_WARPS = 8;     // loader warps of a group: four lane quart
 #define PV_GROUPS_N 2
 #endif
 constexpr int PV_GROUPS = PV_GROUPS_N;  // groups of loader warps, one per tensor-memory buffer: their loads are in flight together
+                                        // (two: 13 % faster than one; three measured the same as two)
+constexpr int PV_PBUFS = PV_GROUPS > 2 ? PV_GROUPS : 2;  // buffers of the first operand in tensor memory, 64 columns each
+static_assert(PV_PBUFS <= 4, "the first-operand buffers lie below the result accumulators (column 256)");
 constexpr int PV_OUT_WARPS = 4;
 constexpr int PV_THREADS = 64 + 32 * (PV_LOAD_WARPS * PV_GROUPS + PV_OUT_WARPS);
 constexpr int PV_BLOCK_BYTES = 128 * 128;  // 128 value rows of one 64-column block: 16 KB
@@ -103,25 +106,27 @@ blk_pv_umma_kernel(const BlkPvParams p, const __grid_constant__ CUtensorMap mapV
         return;
     }
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
-    // barriers: 0.. p_full[2], 2.. p_free[2], 4.. o_ready[2], 6.. o_free[2], 8.. v_full[VS], 14.. v_empty[VS]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 21);
+    // barriers: 0.. p_full[4], 4.. p_free[4], 8.. o_ready[2], 10.. o_free[2], 12.. v_full[VS], 18.. v_empty[VS]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 25);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_u32 = blk_smem_u32(smem);
     const uint32_t bar0 = blk_smem_u32(bars);
     auto p_full = [&](int b) { return bar0 + 8u * (0 + b); };
-    auto p_free = [&](int b) { return bar0 + 8u * (2 + b); };
-    auto o_ready = [&](int b) { return bar0 + 8u * (4 + b); };
-    auto o_free = [&](int b) { return bar0 + 8u * (6 + b); };
-    auto v_full = [&](int s) { return bar0 + 8u * (8 + s); };
-    auto v_empty = [&](int s) { return bar0 + 8u * (14 + s); };
+    auto p_free = [&](int b) { return bar0 + 8u * (4 + b); };
+    auto o_ready = [&](int b) { return bar0 + 8u * (8 + b); };
+    auto o_free = [&](int b) { return bar0 + 8u * (10 + b); };
+    auto v_full = [&](int s) { return bar0 + 8u * (12 + s); };
+    auto v_empty = [&](int s) { return bar0 + 8u * (18 + s); };
     auto sV = [&](int s) { return smem_u32 + L::V_OFF + s * L::OPER_BYTES; };
 
     if (threadIdx.x == 0) {
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < PV_PBUFS; ++b) {
             mbar_init(p_full(b), PV_LOAD_WARPS);
             mbar_init(p_free(b), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
             mbar_init(o_ready(b), 1);
             mbar_init(o_free(b), PV_OUT_WARPS);
         }
@@ -171,8 +176,8 @@ blk_pv_umma_kernel(const BlkPvParams p, const __grid_constant__ CUtensorMap mapV
                 const int ob = (int)(itc & 1u);
                 if (!mbar_wait(o_free(ob), ((itc >> 1) & 1u) ^ 1u, abort_flag, p.status, 42)) break;
                 for (int j = 0; j < wk.T; ++j, ++g) {
-                    const int vs = (int)(g % VS), buf = (int)(g & 1u);
-                    if (!mbar_wait(p_full(buf), (g >> 1) & 1u, abort_flag, p.status, 43)) { ok = false; break; }
+                    const int vs = (int)(g % VS), buf = (int)(g % PV_PBUFS);
+                    if (!mbar_wait(p_full(buf), (g / PV_PBUFS) & 1u, abort_flag, p.status, 43)) { ok = false; break; }
                     if (!mbar_wait(v_full(vs), (g / VS) & 1u, abort_flag, p.status, 44)) { ok = false; break; }
                     tc_fence_after();
                     const int ncols = min(wk.it.K - j * PV_BK, PV_BK);
@@ -205,8 +210,8 @@ blk_pv_umma_kernel(const BlkPvParams p, const __grid_constant__ CUtensorMap mapV
             // byte address of this lane's row of the block
             const int64_t rowb = ((int64_t)wk.head * p.Dm1 + wk.it.offA + (int64_t)row * K) * 2;
             for (int j = 0; ok && j < wk.T; ++j, ++g) {
-                if (PV_GROUPS == 2 && (int)(g & 1u) != grp) continue;  // the other group's tile
-                const int buf = (int)(g & 1u), vs = (int)(g % VS);
+                if (PV_GROUPS > 1 && (int)(g % PV_GROUPS) != grp) continue;  // another group's tile
+                const int buf = (int)(g % PV_PBUFS), vs = (int)(g % VS);
                 const int ncols = min(K - j * PV_BK, PV_BK);
                 const int ksteps = (ncols + 15) >> 4;
                 const int nv = row_ok ? max(0, min(ncols - 64 * h, 64)) : 0;   // elements of this lane's 64 that exist
@@ -250,7 +255,7 @@ blk_pv_umma_kernel(const BlkPvParams p, const __grid_constant__ CUtensorMap mapV
                         else if (2 * i + 1 >= nv) pk[i] &= 0xffffu;
                     }
                 }
-                if (!mbar_wait(p_free(buf), ((g >> 1) & 1u) ^ 1u, abort_flag, p.status, 45)) { ok = false; break; }
+                if (!mbar_wait(p_free(buf), ((g / PV_PBUFS) & 1u) ^ 1u, abort_flag, p.status, 45)) { ok = false; break; }
                 tc_fence_after();
                 // this row's elements [64 h, 64 h + 64) of the tile: columns [32 h, 32 h + 32) of the buffer (only the
                 // columns the products of this tile read)
