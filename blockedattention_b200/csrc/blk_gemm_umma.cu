@@ -338,6 +338,42 @@ blk_gemm_umma_kernel(const BlkUmmaParams p, const __grid_constant__ UmMaps maps)
                         t += (uint32_t)N;
                     }
                 }
+            } else if (OUT32 && pcols == UM_PW && rows == 32) {
+                // the same for a whole piece of fp32 results: row k is the 64 words from word g0 + k N on
+                uint32_t* wp = reinterpret_cast<uint32_t*>(C) + g0 + lane;
+#pragma unroll 2
+                for (int kb = 0; kb < 32; kb += 4) {
+                    uint32_t v[4][2];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) v[k][i] = lds_b32(rbase + (uint32_t)(kb + k) * (UM_STRIP_PITCHW * 4) + 128u * i);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        asm volatile("st.global.b32 [%0], %1;\n" ::"l"(wp), "r"(v[k][0]) : "memory");
+                        asm volatile("st.global.b32 [%0], %1;\n" ::"l"(wp + 32), "r"(v[k][1]) : "memory");
+                        wp += N;
+                    }
+                }
+            } else if constexpr (OUT32) {
+                // a partial piece of fp32 results (fewer rows or columns): the same walk with the bounds as predicates
+                uint32_t* wp = reinterpret_cast<uint32_t*>(C) + g0 + lane;
+#pragma unroll 2
+                for (int kb = 0; kb < 32; kb += 4) {
+                    if (kb >= rows) break;
+                    uint32_t v[4][2];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) v[k][i] = lds_b32(rbase + (uint32_t)(kb + k) * (UM_STRIP_PITCHW * 4) + 128u * i);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const bool row_ok = kb + k < rows;
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) stg_b32_if(wp + 32 * i, v[k][i], row_ok && lane + 32 * i < pcols);
+                        wp += N;
+                    }
+                }
             } else
 #pragma unroll 2
             for (int kb = 0; kb < 32; kb += 4) {
