@@ -149,6 +149,53 @@ def test_schedule_bins_and_work():
     p = GemmPlan(w.M, w.N, w.K, w.H, w.dtype, torch.float32)
     assert p.summary["launches"] >= 1 and p.work[0] == pytest.approx(w.flops())
 
+
+def _with_env(env, fn):
+    old = {k: os.environ.get(k) for k in env}
+    os.environ.update(env)
+    try:
+        return fn()
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+
+
+def test_tcgen05_bin_takes_mixed_contraction_lengths():
+    # six contraction lengths, offsets that are no whole rows of a segment's own (rows, K) view: 24 views per operand
+    # cover all of them, every segment goes to the tcgen05 kernel (the handful of small ones ride along), one launch
+    w = workload("general_gemm")
+    s = GemmPlan(w.M, w.N, w.K, w.H, w.dtype, torch.float32).summary
+    assert s["umma_items"] == int(np.ceil(w.M / 128).sum()) and s["tile_items"] == 0 and s["small_items"] == 0
+    assert s["launches"] == 1
+    # with the ride-along rule off the small segments of the small kernel's K get their own launches
+    s0 = _with_env({"BLK_SMALL_MIN_PAIRS": "0"}, lambda: GemmPlan(w.M, w.N, w.K, w.H, w.dtype, torch.float32).summary)
+    assert s0["small_items"] > 0 and s0["umma_items"] + s0["small_items"] <= s["umma_items"] and s0["launches"] > 1
+    # a batch of small segments only keeps its small-segment launch: there is no tcgen05 launch to ride along with
+    sm = GemmPlan([20, 30, 64], [20, 30, 64], [64, 64, 64], 2, torch.float16, softmax=True).summary
+    assert sm["umma_items"] == 0 and sm["small_items"] == 3
+    # more (K, offset) combinations than view slots: the lightest fall back to the staged kernel
+    rs = np.random.RandomState(6)
+    M = rs.randint(65, 200, size=120); N = rs.randint(65, 200, size=120); K = rs.choice(np.arange(16, 400, 8), size=120)
+    s = GemmPlan(M, N, K, 2, torch.bfloat16).summary
+    assert s["umma_items"] > 0 and s["tile_items"] > 0
+    # K that is no multiple of 8: rows of the views would not be 16-byte multiples
+    s = GemmPlan([200, 200], [300, 300], [36, 100], 1, torch.float16).summary
+    assert s["umma_items"] == 0 and s["tile_items"] > 0
+
+
+def test_tcgen05_items_per_tile_for_long_contractions():
+    # scores only and K >= 512: one item per 128 x 256 tile; with the fused softmax, or a shorter K, one per row block
+    w = workload("large_k")
+    s = GemmPlan(w.M, w.N, w.K, w.H, w.dtype).summary
+    assert s["umma_items"] == int((np.ceil(w.M / 128) * np.ceil(w.N / 256)).sum()) and s["launches"] == 1
+    s = GemmPlan(w.M, w.N, w.K, w.H, w.dtype, softmax=True).summary
+    assert s["umma_items"] == int(np.ceil(w.M / 128).sum())
+    s = GemmPlan([300, 700], [900, 100], [256, 256], 2, torch.bfloat16).summary
+    assert s["umma_items"] == 3 + 6
+
     w = workload("cpu_plumbing")
     p = GemmPlan(w.M, w.N, w.K, w.H, torch.float32, softmax=True)
     s = p.summary
