@@ -92,6 +92,10 @@ def _runs(owner: np.ndarray):
     return out
 
 
+# gather_output sends run by run up to this many runs per rank and all-gathers beyond
+GATHER_MAX_RUNS_PER_RANK = 4
+
+
 def gather_output(local, block_elems, owner, H: int, group=None, out=None):
     """Every rank ends with the whole packed head-major result.
 
@@ -101,10 +105,13 @@ def gather_output(local, block_elems, owner, H: int, group=None, out=None):
     ``(H, sum(block_elems))`` with segment s of head h at ``h * D + offset[s]``, ``offset = cumsum(block_elems)``
     -- the layout a single process produces (upstream csrc/cuda/spBlkGEMM.cu:453-455).
 
-    One grouped set of point-to-point transfers (``torch.distributed.batch_isend_irecv``: NCCL send/recv between
-    ``ncclGroupStart`` and ``ncclGroupEnd`` on GPUs, gloo on CPU).  A rank's strips have unequal lengths and are not
-    contiguous in the result, so this is H transfers per run of consecutive segments with one owner, received in
-    place: no staging buffer, no equal-size padding.  The upstream project is single-GPU; no counterpart there."""
+    Ownership in a few runs of consecutive segments (contiguous ranges): one grouped set of point-to-point transfers
+    (``torch.distributed.batch_isend_irecv``: NCCL send/recv between ``ncclGroupStart`` and ``ncclGroupEnd`` on GPUs,
+    gloo on CPU).  A rank's strips have unequal lengths and are not contiguous in the result, so this is H transfers
+    per run, received in place: no staging buffer, no equal-size padding.  Ownership scattered over many runs (the
+    longest-processing-time assignment): thousands of point-to-point transfers in one group are not something to rely
+    on, so the ranks all-gather their packed strips, padded to the longest, and every rank copies the runs into place
+    itself.  The upstream project is single-GPU; no counterpart there."""
     import torch
     import torch.distributed as dist
     owner = np.asarray(owner)
@@ -117,9 +124,24 @@ def gather_output(local, block_elems, owner, H: int, group=None, out=None):
     mine = int(be[owner == rank].sum())
     if local.shape != (H, mine):
         raise RuntimeError(f"local result has shape {tuple(local.shape)}, this rank owns ({H}, {mine})")
-    peers = [r for r in range(dist.get_world_size(group)) if r != rank]
+    world = dist.get_world_size(group)
+    runs = [(r, s, e) for r, s, e in _runs(owner) if off[e] > off[s]]
+    if len(runs) > GATHER_MAX_RUNS_PER_RANK * world:
+        per_rank = [int(be[owner == r].sum()) for r in range(world)]
+        longest = max(per_rank)
+        padded = local if mine == longest else torch.cat(
+            [local, torch.zeros((H, longest - mine), dtype=local.dtype, device=local.device)], dim=1)
+        parts = [torch.empty((H, longest), dtype=local.dtype, device=local.device) for _ in range(world)]
+        dist.all_gather(parts, padded.contiguous(), group=group)
+        pos = [0] * world
+        for r, s, e in runs:
+            lo, hi = int(off[s]), int(off[e])
+            out[:, lo:hi].copy_(parts[r][:, pos[r]:pos[r] + (hi - lo)])
+            pos[r] += hi - lo
+        return out
+    peers = [r for r in range(world) if r != rank]
     ops, lpos = [], 0
-    for r, s, e in _runs(owner):
+    for r, s, e in runs:
         lo, hi = int(off[s]), int(off[e])
         if hi == lo:
             continue

@@ -61,8 +61,16 @@ def _worker(rank, world, port, out_dir):
         ql2 = torch.cat([q[:, a1[s]:a1[s + 1]] for s in idx], dim=1)
         kl2 = torch.cat([k[:, a2[s]:a2[s + 1]] for s in idx], dim=1)
         mine2 = Or.block_scores(ql2, kl2, w.M[idx], w.N[idx], w.K[idx], scale=w.scale)
-        got2 = P.gather_output(mine2, w.M * w.N, owner2, w.H)
+        got2 = P.gather_output(mine2, w.M * w.N, owner2, w.H)   # 20 runs: the all-gather path, unequal strips padded
         assert torch.equal(got2, ref)
+        # a few runs that are not one range per rank: still point to point
+        owner3 = (np.arange(w.S) // 24 % world).astype(np.int32)
+        assert len(list(P._runs(owner3))) <= P.GATHER_MAX_RUNS_PER_RANK * world
+        idx = np.nonzero(owner3 == rank)[0]
+        ql3 = torch.cat([q[:, a1[s]:a1[s + 1]] for s in idx], dim=1)
+        kl3 = torch.cat([k[:, a2[s]:a2[s + 1]] for s in idx], dim=1)
+        mine3 = Or.block_scores(ql3, kl3, w.M[idx], w.N[idx], w.K[idx], scale=w.scale)
+        assert torch.equal(P.gather_output(mine3, w.M * w.N, owner3, w.H), ref)
         # a heavy-tailed batch sends shard() to the fallback
         heavy = np.array([4, 4, 4, 4, 2000, 4, 4, 1500], np.int64)
         o3, i3 = P.shard(heavy, heavy, np.full(8, 64), 1, world, max_imbalance=1.0)
