@@ -273,53 +273,80 @@ int blk_build_gemm_schedule(blk_plan* p) {
     // its K that starts at its offset modulo K.  It takes the 16-bit segments that are not for the small-segment
     // kernels (too big, or a K other than theirs) whose K and offsets are multiples of 8 elements (16-byte rows for the tensor maps) and whose views are
     // among the BLK_UMMA_VIEWS per operand that carry the most work.
+    // Per segment, once: whether the kernel could take it at all, its multiply-adds, and the number of its (K, residue)
+    // key among the distinct keys of each operand (a batch has a handful of them: flat tables, linear search).
+    typedef std::pair<int64_t, int64_t> Key;  // (K, residue)
+    std::vector<Key> keysA, keysB;
+    std::vector<int32_t> keyA(allow_umma ? (size_t)S : 0, -1), keyB(allow_umma ? (size_t)S : 0, -1);
+    std::vector<double> seg_work(allow_umma ? (size_t)S : 0, 0.0);
+    double all_work = 0;
+    if (allow_umma) {
+        auto key_of = [](std::vector<Key>& keys, int64_t k, int64_t r) {
+            for (size_t i = keys.size(); i-- > 0;)  // the last keys added are the likeliest
+                if (keys[i].first == k && keys[i].second == r) return (int32_t)i;
+            keys.push_back(Key(k, r));
+            return (int32_t)(keys.size() - 1);
+        };
+        for (int64_t s = 0; s < S; ++s) {
+            const int64_t m = p->M[s], n = p->N[s], k = p->K[s];
+            seg_work[s] = (double)m * (double)n * (double)k;
+            all_work += seg_work[s];
+            if (m > 0 && n > 0 && k >= 16 && k % 8 == 0 && p->a1[s] % 8 == 0 && p->a2[s] % 8 == 0 && p->Dm1 / k < INT32_MAX &&
+                p->Dm2 / k < INT32_MAX) {
+                keyA[s] = key_of(keysA, k, p->a1[s] % k);
+                keyB[s] = key_of(keysB, k, p->a2[s] % k);
+            }
+        }
+    }
+    // a capable segment is a candidate unless the small-segment kernels take it
     auto umma_candidate = [&](int64_t s) {
         const int64_t m = p->M[s], n = p->N[s], k = p->K[s];
-        return allow_umma && m > 0 && n > 0 && k >= 16 && k % 8 == 0 &&
-               (m > BLK_SMALL_MAXM || n > BLK_SMALL_MAXN || (k != 32 && k != 64) || !allow_small) &&
-               p->a1[s] % 8 == 0 && p->a2[s] % 8 == 0 && p->Dm1 / k < INT32_MAX && p->Dm2 / k < INT32_MAX;
+        return allow_umma && keyA[s] >= 0 &&
+               (m > BLK_SMALL_MAXM || n > BLK_SMALL_MAXN || (k != 32 && k != 64) || !allow_small);
     };
     std::vector<int32_t> umma_views(allow_umma ? (size_t)S : 0, -1);  // per segment: view of A | view of B << 8, or -1
     auto select_views = [&]() {
-    p->umma_K = 0;
-    p->umma_viewsA.clear();
-    p->umma_viewsB.clear();
-    std::fill(umma_views.begin(), umma_views.end(), -1);
-    if (allow_umma) {
-        typedef std::pair<int64_t, int64_t> Key;  // (K, residue)
-        std::map<Key, double> workA, workB;
-        double all = 0;
+        p->umma_K = 0;
+        p->umma_viewsA.clear();
+        p->umma_viewsB.clear();
+        std::fill(umma_views.begin(), umma_views.end(), -1);
+        if (!allow_umma) return;
+        std::vector<double> workA(keysA.size(), 0.0), workB(keysB.size(), 0.0);
+        std::vector<char> usedA(keysA.size(), 0), usedB(keysB.size(), 0);
         for (int64_t s = 0; s < S; ++s) {
-            const double wk = (double)p->M[s] * (double)p->N[s] * (double)p->K[s];
-            all += wk;
             if (!umma_candidate(s)) continue;
-            workA[Key(p->K[s], p->a1[s] % p->K[s])] += wk;
-            workB[Key(p->K[s], p->a2[s] % p->K[s])] += wk;
+            workA[keyA[s]] += seg_work[s];
+            workB[keyB[s]] += seg_work[s];
+            usedA[keyA[s]] = usedB[keyB[s]] = 1;
         }
-        auto pick = [](const std::map<Key, double>& work, std::vector<BlkUmmaView>* out) {
-            std::vector<std::pair<double, Key>> v;
-            for (const auto& kv : work) v.push_back(std::make_pair(kv.second, kv.first));
-            std::stable_sort(v.begin(), v.end(), [](const std::pair<double, Key>& x, const std::pair<double, Key>& y) { return x.first > y.first; });
-            for (size_t i = 0; i < v.size() && i < (size_t)BLK_UMMA_VIEWS; ++i) out->push_back(BlkUmmaView{v[i].second.first, v[i].second.second});
+        // the BLK_UMMA_VIEWS keys with the most work, ties in the order of (K, residue); slot[key] = view or -1
+        auto pick = [](const std::vector<Key>& keys, const std::vector<double>& work, const std::vector<char>& used,
+                       std::vector<BlkUmmaView>* out, std::vector<int32_t>* slot) {
+            std::vector<int32_t> order;
+            for (size_t i = 0; i < keys.size(); ++i)
+                if (used[i]) order.push_back((int32_t)i);
+            std::sort(order.begin(), order.end(), [&](int32_t x, int32_t y) { return keys[x] < keys[y]; });
+            std::stable_sort(order.begin(), order.end(), [&](int32_t x, int32_t y) { return work[x] > work[y]; });
+            slot->assign(keys.size(), -1);
+            for (size_t i = 0; i < order.size() && i < (size_t)BLK_UMMA_VIEWS; ++i) {
+                out->push_back(BlkUmmaView{keys[order[i]].first, keys[order[i]].second});
+                (*slot)[order[i]] = (int32_t)i;
+            }
         };
-        pick(workA, &p->umma_viewsA);
-        pick(workB, &p->umma_viewsB);
-        auto find = [](const std::vector<BlkUmmaView>& views, int64_t k, int64_t r) {
-            for (size_t i = 0; i < views.size(); ++i)
-                if (views[i].K == k && views[i].residue == r) return (int)i;
-            return -1;
-        };
+        std::vector<int32_t> slotA, slotB;
+        pick(keysA, workA, usedA, &p->umma_viewsA, &slotA);
+        pick(keysB, workB, usedB, &p->umma_viewsB, &slotB);
         double taken = 0;
         for (int64_t s = 0; s < S; ++s) {
             if (!umma_candidate(s)) continue;
-            const int va = find(p->umma_viewsA, p->K[s], p->a1[s] % p->K[s]), vb = find(p->umma_viewsB, p->K[s], p->a2[s] % p->K[s]);
+            const int va = slotA[keyA[s]], vb = slotB[keyB[s]];
             if (va < 0 || vb < 0) continue;
             umma_views[s] = va | (vb << 8);
-            taken += (double)p->M[s] * (double)p->N[s] * (double)p->K[s];
+            taken += seg_work[s];
         }
         // A separate launch pays only if it takes a real share of the batch: when the segments it could take
         // carry under a tenth of all multiply-adds, they stay with the staged kernel.
-        if (taken == 0 || (taken < 0.1 * all && !blk_env_flag("BLK_FORCE_UMMA"))) {
+        if (taken == 0 || (taken < 0.1 * all_work && !blk_env_flag("BLK_FORCE_UMMA"))) {
             std::fill(umma_views.begin(), umma_views.end(), -1);
             p->umma_viewsA.clear();
             p->umma_viewsB.clear();
@@ -329,7 +356,6 @@ int blk_build_gemm_schedule(blk_plan* p) {
         } else {
             p->umma_K = -1;
         }
-    }
     };
     select_views();
     // A launch of the small-segment kernel of its own pays only for enough segments: when the tcgen05 kernel is
@@ -455,8 +481,15 @@ int blk_build_gemm_schedule(blk_plan* p) {
         const int64_t kblocks = ((int64_t)a.K + 63) / 64;  // a chunk costs the epilogue (about four k-blocks' worth) plus its k-blocks
         return ((two_sweeps && chunks > 2 ? 2 * chunks : chunks) * (4 + kblocks) << 36) + ((int64_t)a.N << 8) + rows;
     };
-    std::stable_sort(p->umma_items.begin(), p->umma_items.end(),
-                     [&](const BlkUmmaItem& a, const BlkUmmaItem& b) { return umma_cost(a) > umma_cost(b); });
+    {
+        // the cost of an item is computed once, the (cost, position) pairs are sorted and the items moved into that order
+        std::vector<std::pair<int64_t, int32_t>> order(p->umma_items.size());
+        for (size_t i = 0; i < order.size(); ++i) order[i] = std::make_pair(-umma_cost(p->umma_items[i]), (int32_t)i);
+        std::sort(order.begin(), order.end());  // descending cost, ties in the order of generation (a stable sort)
+        std::vector<BlkUmmaItem> sorted(order.size());
+        for (size_t i = 0; i < order.size(); ++i) sorted[i] = p->umma_items[order[i].second];
+        p->umma_items.swap(sorted);
+    }
     p->umma_long_rows = 0;
     for (const BlkUmmaItem& it : p->umma_items)
         if (it.N > 512) p->umma_long_rows = 1;
