@@ -280,7 +280,12 @@ int blk_build_gemm_schedule(blk_plan* p) {
     std::vector<int32_t> keyA(allow_umma ? (size_t)S : 0, -1), keyB(allow_umma ? (size_t)S : 0, -1);
     std::vector<double> seg_work(allow_umma ? (size_t)S : 0, 0.0);
     double all_work = 0;
-    if (allow_umma) {
+    // segments the small-segment kernels would take get their keys only if they end up riding along (below): a batch
+    // of thousands of small graphs does not pay for keys it never uses
+    auto small_shaped = [&](int64_t s) {
+        return p->M[s] <= BLK_SMALL_MAXM && p->N[s] <= BLK_SMALL_MAXN && (p->K[s] == 32 || p->K[s] == 64);
+    };
+    auto make_keys = [&](bool small_ones) {
         auto key_of = [](std::vector<Key>& keys, int64_t k, int64_t r) {
             for (size_t i = keys.size(); i-- > 0;)  // the last keys added are the likeliest
                 if (keys[i].first == k && keys[i].second == r) return (int32_t)i;
@@ -289,14 +294,23 @@ int blk_build_gemm_schedule(blk_plan* p) {
         };
         for (int64_t s = 0; s < S; ++s) {
             const int64_t m = p->M[s], n = p->N[s], k = p->K[s];
-            seg_work[s] = (double)m * (double)n * (double)k;
-            all_work += seg_work[s];
-            if (m > 0 && n > 0 && k >= 16 && k % 8 == 0 && p->a1[s] % 8 == 0 && p->a2[s] % 8 == 0 && p->Dm1 / k < INT32_MAX &&
-                p->Dm2 / k < INT32_MAX) {
-                keyA[s] = key_of(keysA, k, p->a1[s] % k);
-                keyB[s] = key_of(keysB, k, p->a2[s] % k);
+            if (!small_ones) {
+                seg_work[s] = (double)m * (double)n * (double)k;
+                all_work += seg_work[s];
+            }
+            if (small_shaped(s) != small_ones) continue;
+            // (rows of a view must fit 32 bits: D / k < INT32_MAX, written without the division)
+            if (m > 0 && n > 0 && k >= 16 && k % 8 == 0 && p->a1[s] % 8 == 0 && p->a2[s] % 8 == 0 &&
+                p->Dm1 < (int64_t)INT32_MAX * k && p->Dm2 < (int64_t)INT32_MAX * k) {
+                const bool pow2 = (k & (k - 1)) == 0;
+                keyA[s] = key_of(keysA, k, pow2 ? (p->a1[s] & (k - 1)) : p->a1[s] % k);
+                keyB[s] = key_of(keysB, k, pow2 ? (p->a2[s] & (k - 1)) : p->a2[s] % k);
             }
         }
+    };
+    if (allow_umma) {
+        make_keys(false);
+        if (!allow_small) make_keys(true);
     }
     // a capable segment is a candidate unless the small-segment kernels take it
     auto umma_candidate = [&](int64_t s) {
@@ -374,6 +388,7 @@ int blk_build_gemm_schedule(blk_plan* p) {
         const int64_t min_pairs = e ? std::atoll(e) : 300;
         if (pairs < min_pairs) {
             allow_small = false;
+            make_keys(true);
             select_views();
         }
     }
