@@ -105,11 +105,7 @@ bool grid_ok(int64_t items, int64_t H, const char* what) {
     return true;
 }
 
-size_t small_count(const blk_plan* p) {
-    size_t n = 0;
-    for (const auto& v : p->small_items) n += v.size();
-    return n;
-}
+size_t small_count(const blk_plan* p) { return (size_t)p->small_segments; }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -408,7 +404,7 @@ static int attention_plan_impl(blk_plan_t** plan, const int64_t* M, const int64_
         p->umma_items.clear();
         p->simt_items.clear();
         if (!packs) {
-            p->packs.clear(); p->pack_blocks.clear(); p->small_pipe = 0;
+            p->packs.clear(); p->pack_blocks.clear(); p->small_pipe = 0; p->small_segments = 0;
             for (auto& v : p->small_items) v.clear();
         }
         if (rc == BLK_OK && !any_length && nonempty > 0 && !(small && packs)) {

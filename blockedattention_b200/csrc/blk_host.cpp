@@ -448,9 +448,7 @@ int blk_build_gemm_schedule(blk_plan* p) {
                               (p->small_K == 0 || p->small_K == (int)k);
         if (small_ok) {
             p->small_K = (int)k;
-            small_segs.push_back(s);
-            p->small_items[n <= 32 ? 0 : 1].push_back(
-                BlkSmallItem{sd.offA, sd.offB, sd.offC, (int32_t)m, (int32_t)n});
+            small_segs.push_back(s);  // packs or per-warp items: decided below, once the whole bin is known
             continue;
         }
         if (p->pv_D != 0 && pv_candidate(s, p->pv_D)) {
@@ -521,13 +519,15 @@ int blk_build_gemm_schedule(blk_plan* p) {
     if (p->small_K == 64 && p->dtype_out != BLK_F32 && rows_ok && !blk_env_flag("BLK_DISABLE_PIPE") && !small_segs.empty()) {
         p->small_pipe = 1;
         const int pack_rows = p->attn ? BLK_PACK_ROWS_ATTN : BLK_PACK_ROWS;
-        // packs in batch order with their blocks in one flat array, then emitted heaviest first
+        // First the packs in batch order (extents, cost and the first segment of each), then the block table written
+        // once, pack by pack, heaviest pack first: persistent CTAs take packs with a fixed stride.
         std::vector<BlkPack> pk;
-        std::vector<double> cost;
-        std::vector<BlkPackBlock> flat;
+        std::vector<std::pair<double, int32_t>> order;  // (-cost, pack)
+        std::vector<int32_t> first_seg;                 // index into small_segs
         pk.reserve(small_segs.size() / 4 + 1);
-        cost.reserve(small_segs.size() / 4 + 1);
-        flat.reserve(small_segs.size() * 2);
+        order.reserve(small_segs.size() / 4 + 1);
+        first_seg.reserve(small_segs.size() / 4 + 2);
+        size_t nblocks = 0;
         for (size_t q = 0; q < small_segs.size(); ++q) {
             const BlkSeg& sd = p->segs[small_segs[q]];
             const int32_t mblocks = (sd.M + 15) / 16;  // one block per 16 first-operand rows of the segment
@@ -539,52 +539,67 @@ int blk_build_gemm_schedule(blk_plan* p) {
                          t.nblocks + mblocks <= BLK_PACK_BLOCKS;
             }
             if (!extend) {
-                pk.push_back(BlkPack{sd.offA, sd.offB, 0, 0, (int32_t)flat.size(), 0});
-                cost.push_back(0.0);
+                pk.push_back(BlkPack{sd.offA, sd.offB, 0, 0, 0, 0});
+                order.push_back(std::make_pair(-0.0, (int32_t)order.size()));
+                first_seg.push_back((int32_t)q);
             }
             BlkPack& t = pk.back();
-            for (int32_t mb = 0; mb < mblocks; ++mb)
-                // output of the block: M x N scores, or for an attention plan M x 64 result rows
-                flat.push_back(BlkPackBlock{sd.offC + (int64_t)mb * 16 * (p->attn ? 64 : sd.N), t.rowsA + 16 * mb, t.rowsB,
-                                            std::min<int32_t>(16, sd.M - 16 * mb), sd.N, 0, 0});
             t.rowsA += sd.M;
             t.rowsB += sd.N;
             t.nblocks += mblocks;
-            cost.back() += (double)sd.M * sd.N + (double)(sd.M + sd.N) * 64;
+            nblocks += (size_t)mblocks;
+            order.back().first -= (double)sd.M * sd.N + (double)(sd.M + sd.N) * 64;
         }
-        // heaviest packs first: persistent CTAs take packs with a fixed stride
-        std::vector<int32_t> order(pk.size());
-        std::iota(order.begin(), order.end(), 0);
-        std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return cost[a] > cost[b]; });
-        p->packs.reserve(pk.size());
-        p->pack_blocks.reserve(flat.size() + BLK_PACK_BLOCKS);
-        for (int32_t i : order) {
-            BlkPack t = pk[i];
-            BlkPackBlock* first = flat.data() + t.first_block;
-            // consumers claim blocks in table order: widest first (at most 16 blocks: insertion sort, stable)
-            for (int32_t a = 1; a < t.nblocks; ++a) {
-                const BlkPackBlock key = first[a];
-                int32_t b = a - 1;
-                while (b >= 0 && first[b].N < key.N) { first[b + 1] = first[b]; --b; }
-                first[b + 1] = key;
+        first_seg.push_back((int32_t)small_segs.size());
+        std::sort(order.begin(), order.end());  // descending cost, equal costs in batch order
+        p->packs.resize(pk.size());
+        // the block table is read in 16-record pieces: 16 records of slack (zeros) behind the last pack
+        p->pack_blocks.assign(nblocks + BLK_PACK_BLOCKS, BlkPackBlock{0, 0, 0, 0, 0, 0, 0});
+        BlkPackBlock* dst = p->pack_blocks.data();
+        const BlkSeg* const segs = p->segs.data();
+        const int64_t* const small = small_segs.data();
+        const bool attn = p->attn != 0;
+        for (size_t i = 0; i < order.size(); ++i) {
+            const int32_t pi = order[i].second;
+            BlkPack t = pk[pi];
+            t.first_block = (int32_t)(dst - p->pack_blocks.data());
+            // consumers claim blocks in table order: widest segment first, equal widths in batch order (at most
+            // BLK_PACK_BLOCKS segments, every one has a block: insertion sort)
+            struct Member { int32_t N, q, rowA, rowB; } member[BLK_PACK_BLOCKS];
+            int32_t rowsA = 0, rowsB = 0, members = 0;
+            for (int32_t q = first_seg[pi]; q < first_seg[pi + 1]; ++q) {
+                const BlkSeg& sd = segs[small[q]];
+                int32_t at = members++;
+                for (; at > 0 && member[at - 1].N < sd.N; --at) member[at] = member[at - 1];
+                member[at] = Member{sd.N, q, rowsA, rowsB};
+                rowsA += sd.M;
+                rowsB += sd.N;
             }
-            t.first_block = (int32_t)p->pack_blocks.size();
-            for (int32_t a = 0; a < t.nblocks; ++a) {
-                first[a].nblocks = t.nblocks;
-                p->pack_blocks.push_back(first[a]);
+            BlkPackBlock* out = dst;
+            for (int32_t e = 0; e < members; ++e) {
+                const BlkSeg& sd = segs[small[member[e].q]];
+                // output of a block: 16 x N scores, or for an attention plan 16 x 64 result rows
+                const int64_t step = 16 * (int64_t)(attn ? 64 : sd.N);
+                for (int32_t mb = 0; mb * 16 < sd.M; ++mb)
+                    *out++ = BlkPackBlock{sd.offC + mb * step, member[e].rowA + 16 * mb, member[e].rowB,
+                                          std::min<int32_t>(16, sd.M - 16 * mb), sd.N, t.nblocks, 0};
             }
-            p->packs.push_back(t);
+            dst += t.nblocks;
+            p->packs[i] = t;
         }
-        // the block table is read in 16-record pieces: keep 16 records of slack behind the last pack
-        for (int q = 0; q < BLK_PACK_BLOCKS; ++q) p->pack_blocks.push_back(BlkPackBlock{0, 0, 0, 0, 0, 0, 0});
+    } else {
+        // One warp per (segment, head).  Persistent warps take the items in list order with a fixed stride: heaviest
+        // first evens the tails.
+        for (int64_t s : small_segs) {
+            const BlkSeg& sd = p->segs[s];
+            p->small_items[sd.N <= 32 ? 0 : 1].push_back(BlkSmallItem{sd.offA, sd.offB, sd.offC, sd.M, sd.N});
+        }
+        for (auto& v : p->small_items)
+            std::stable_sort(v.begin(), v.end(), [](const BlkSmallItem& a, const BlkSmallItem& b) {
+                return (int64_t)a.M * a.N + (int64_t)(a.M + a.N) * 64 > (int64_t)b.M * b.N + (int64_t)(b.M + b.N) * 64;
+            });
     }
-    // Persistent warps take small items in list order with a fixed stride: heaviest first evens the tails
-    // (the pack kernel does not read these lists).
-    if (!p->small_pipe)
-    for (auto& v : p->small_items)
-        std::stable_sort(v.begin(), v.end(), [](const BlkSmallItem& a, const BlkSmallItem& b) {
-            return (int64_t)a.M * a.N + (int64_t)(a.M + a.N) * 64 > (int64_t)b.M * b.N + (int64_t)(b.M + b.N) * 64;
-        });
+    p->small_segments = (int64_t)small_segs.size();
     // fp32 inputs with the softmax epilogue: SIMT GEMM, then the softmax kernel in place.
     if (p->dtype_in == BLK_F32 && p->epi == BLK_EPI_SOFTMAX) {
         blk_plan tmp;

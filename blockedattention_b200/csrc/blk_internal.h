@@ -166,7 +166,7 @@ struct blk_plan {
     std::vector<BlkSeg> segs;
     std::vector<BlkTileItem> tile_items;    // staged mma.sync kernel (16-bit inputs)
     std::vector<BlkTileItem> simt_items;    // fp32 SIMT kernel
-    std::vector<BlkSmallItem> small_items[BLK_SMALL_BUCKETS];  // packed small-segment kernel, by column count
+    std::vector<BlkSmallItem> small_items[BLK_SMALL_BUCKETS];  // packed small-segment kernel, by column count (empty when small_pipe)
     std::vector<BlkUmmaItem> umma_items;    // tcgen05 kernel
     std::vector<BlkPvItem> pv_items;        // tcgen05 kernel for transposed second operands of 64 or 128 columns
     int pv_D = 0;                           // columns of that second operand
@@ -178,6 +178,7 @@ struct blk_plan {
     int umma_long_rows = 0;                 // a tcgen05 item has more than 512 columns
     std::vector<BlkUmmaView> umma_viewsA, umma_viewsB;  // views of the operands the tcgen05 items refer to
     int small_K = 0;                        // uniform K of the small bin
+    int64_t small_segments = 0;             // segments of the small bin (as packs when small_pipe, else one item each)
     int small_pipe = 0;                     // 1: the small segments run as packs on the pipelined kernel
     int attn = 0;                           // attention plan (result = softmax(QK^T) V): 1 every segment in packs,
                                             // 2 every segment on the tcgen05 attention kernel
