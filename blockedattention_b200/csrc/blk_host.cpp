@@ -225,6 +225,56 @@ static int access_class(int64_t H, int64_t D, int64_t off, int64_t pitch, int es
     return 0;
 }
 
+// Stable ascending order of (key, payload) records by their 64-bit keys: counting sort byte by byte, skipping the
+// bytes on which all keys agree.  A comparison sort of a few thousand work items spends its time in mispredicted
+// branches; this takes a fifth of it.
+static void sort_by_key(std::vector<std::pair<uint64_t, int32_t>>& v) {
+    uint64_t any = 0, all = ~(uint64_t)0;
+    for (const auto& e : v) { any |= e.first; all &= e.first; }
+    const uint64_t differ = any ^ all;
+    std::vector<std::pair<uint64_t, int32_t>> tmp(v.size());
+    for (int shift = 0; shift < 64; shift += 8) {
+        if (((differ >> shift) & 255) == 0) continue;
+        size_t start[256] = {0};
+        for (const auto& e : v) ++start[(e.first >> shift) & 255];
+        size_t at = 0;
+        for (size_t& c : start) { const size_t n = c; c = at; at += n; }
+        for (const auto& e : v) tmp[start[(e.first >> shift) & 255]++] = e;
+        v.swap(tmp);
+    }
+}
+
+// The distinct (K, residue) keys of an operand, numbered in the order of first appearance, behind a small
+// open-addressing table (a batch of mixed contraction lengths has dozens of keys, looked up twice per segment).
+struct BlkKeyTable {
+    std::vector<std::pair<int64_t, int64_t>> keys;
+    std::vector<int32_t> slots;  // key number or -1; a power of two, at most half full
+    static size_t hash(int64_t k, int64_t r) {
+        return (size_t)(((uint64_t)k * 0x9E3779B97F4A7C15ull) ^ ((uint64_t)r * 0xC2B2AE3D27D4EB4Full)) >> 20;
+    }
+    void place(int32_t i) {
+        size_t h = hash(keys[i].first, keys[i].second) & (slots.size() - 1);
+        while (slots[h] >= 0) h = (h + 1) & (slots.size() - 1);
+        slots[h] = i;
+    }
+    int32_t number_of(int64_t k, int64_t r) {
+        if (slots.empty()) slots.assign(64, -1);
+        for (size_t h = hash(k, r) & (slots.size() - 1);; h = (h + 1) & (slots.size() - 1)) {
+            const int32_t i = slots[h];
+            if (i < 0) break;
+            if (keys[i].first == k && keys[i].second == r) return i;
+        }
+        keys.push_back(std::make_pair(k, r));
+        if (keys.size() * 2 > slots.size()) {
+            slots.assign(slots.size() * 2, -1);
+            for (size_t i = 0; i < keys.size(); ++i) place((int32_t)i);
+        } else {
+            place((int32_t)keys.size() - 1);
+        }
+        return (int32_t)keys.size() - 1;
+    }
+};
+
 static int validate_offsets(const char* what, const std::vector<int64_t>& acc, const std::vector<int64_t>& need,
                             int64_t S) {
     if (acc[0] < 0) {
@@ -274,9 +324,10 @@ int blk_build_gemm_schedule(blk_plan* p) {
     // kernels (too big, or a K other than theirs) whose K and offsets are multiples of 8 elements (16-byte rows for the tensor maps) and whose views are
     // among the BLK_UMMA_VIEWS per operand that carry the most work.
     // Per segment, once: whether the kernel could take it at all, its multiply-adds, and the number of its (K, residue)
-    // key among the distinct keys of each operand (a batch has a handful of them: flat tables, linear search).
+    // key among the distinct keys of each operand (BlkKeyTable).
     typedef std::pair<int64_t, int64_t> Key;  // (K, residue)
-    std::vector<Key> keysA, keysB;
+    BlkKeyTable tableA, tableB;
+    const std::vector<Key>&keysA = tableA.keys, &keysB = tableB.keys;
     std::vector<int32_t> keyA(allow_umma ? (size_t)S : 0, -1), keyB(allow_umma ? (size_t)S : 0, -1);
     std::vector<double> seg_work(allow_umma ? (size_t)S : 0, 0.0);
     double all_work = 0;
@@ -286,12 +337,6 @@ int blk_build_gemm_schedule(blk_plan* p) {
         return p->M[s] <= BLK_SMALL_MAXM && p->N[s] <= BLK_SMALL_MAXN && (p->K[s] == 32 || p->K[s] == 64);
     };
     auto make_keys = [&](bool small_ones) {
-        auto key_of = [](std::vector<Key>& keys, int64_t k, int64_t r) {
-            for (size_t i = keys.size(); i-- > 0;)  // the last keys added are the likeliest
-                if (keys[i].first == k && keys[i].second == r) return (int32_t)i;
-            keys.push_back(Key(k, r));
-            return (int32_t)(keys.size() - 1);
-        };
         for (int64_t s = 0; s < S; ++s) {
             const int64_t m = p->M[s], n = p->N[s], k = p->K[s];
             if (!small_ones) {
@@ -303,8 +348,8 @@ int blk_build_gemm_schedule(blk_plan* p) {
             if (m > 0 && n > 0 && k >= 16 && k % 8 == 0 && p->a1[s] % 8 == 0 && p->a2[s] % 8 == 0 &&
                 p->Dm1 < (int64_t)INT32_MAX * k && p->Dm2 < (int64_t)INT32_MAX * k) {
                 const bool pow2 = (k & (k - 1)) == 0;
-                keyA[s] = key_of(keysA, k, pow2 ? (p->a1[s] & (k - 1)) : p->a1[s] % k);
-                keyB[s] = key_of(keysB, k, pow2 ? (p->a2[s] & (k - 1)) : p->a2[s] % k);
+                keyA[s] = tableA.number_of(k, pow2 ? (p->a1[s] & (k - 1)) : p->a1[s] % k);
+                keyB[s] = tableB.number_of(k, pow2 ? (p->a2[s] & (k - 1)) : p->a2[s] % k);
             }
         }
     };
@@ -319,8 +364,10 @@ int blk_build_gemm_schedule(blk_plan* p) {
                (m > BLK_SMALL_MAXM || n > BLK_SMALL_MAXN || (k != 32 && k != 64) || !allow_small);
     };
     std::vector<int32_t> umma_views(allow_umma ? (size_t)S : 0, -1);  // per segment: view of A | view of B << 8, or -1
+    size_t umma_segments = 0;  // segments with views
     auto select_views = [&]() {
         p->umma_K = 0;
+        umma_segments = 0;
         p->umma_viewsA.clear();
         p->umma_viewsB.clear();
         std::fill(umma_views.begin(), umma_views.end(), -1);
@@ -357,6 +404,7 @@ int blk_build_gemm_schedule(blk_plan* p) {
             if (va < 0 || vb < 0) continue;
             umma_views[s] = va | (vb << 8);
             taken += seg_work[s];
+            ++umma_segments;
         }
         // A separate launch pays only if it takes a real share of the batch: when the segments it could take
         // carry under a tenth of all multiply-adds, they stay with the staged kernel.
@@ -364,6 +412,7 @@ int blk_build_gemm_schedule(blk_plan* p) {
             std::fill(umma_views.begin(), umma_views.end(), -1);
             p->umma_viewsA.clear();
             p->umma_viewsB.clear();
+            umma_segments = 0;
         } else if (p->umma_viewsA.size() == 1 && p->umma_viewsB.size() == 1 && p->umma_viewsA[0].residue == 0 &&
                    p->umma_viewsB[0].residue == 0) {
             p->umma_K = (int)p->umma_viewsA[0].K;
@@ -415,6 +464,7 @@ int blk_build_gemm_schedule(blk_plan* p) {
         if (best > 0 && (best >= 0.1 * all || blk_env_flag("BLK_FORCE_UMMA"))) p->pv_D = w128 >= w64 ? 128 : 64;
     }
     p->segs.resize(S);
+    p->umma_items.reserve(umma_segments + umma_segments / 2);  // an item per 128-row block (or tile): a first guess
     p->flops = p->bytes = 0;
     std::vector<int64_t> small_segs;  // segments of the small bin, in batch order
     for (int64_t s = 0; s < S; ++s) {
@@ -492,16 +542,29 @@ int blk_build_gemm_schedule(blk_plan* p) {
         const int64_t chunks = a.nch ? a.nch : ((int64_t)a.N + 255) / 256;
         const int64_t rows = std::min(a.M - a.tm * BLK_UMMA_BM, BLK_UMMA_BM);
         const int64_t kblocks = ((int64_t)a.K + 63) / 64;  // a chunk costs the epilogue (about four k-blocks' worth) plus its k-blocks
-        return ((two_sweeps && chunks > 2 ? 2 * chunks : chunks) * (4 + kblocks) << 36) + ((int64_t)a.N << 8) + rows;
+        const int64_t work = std::min<int64_t>((two_sweeps && chunks > 2 ? 2 * chunks : chunks) * (4 + kblocks), (1 << 27) - 1);
+        return (work << 36) + ((int64_t)a.N << 8) + rows;  // below 2^63: the ordering key is its complement
     };
     {
         // the cost of an item is computed once, the (cost, position) pairs are sorted and the items moved into that order
-        std::vector<std::pair<int64_t, int32_t>> order(p->umma_items.size());
-        for (size_t i = 0; i < order.size(); ++i) order[i] = std::make_pair(-umma_cost(p->umma_items[i]), (int32_t)i);
-        std::sort(order.begin(), order.end());  // descending cost, ties in the order of generation (a stable sort)
-        std::vector<BlkUmmaItem> sorted(order.size());
-        for (size_t i = 0; i < order.size(); ++i) sorted[i] = p->umma_items[order[i].second];
-        p->umma_items.swap(sorted);
+        std::vector<std::pair<uint64_t, int32_t>> order(p->umma_items.size());
+        for (size_t i = 0; i < order.size(); ++i)
+            order[i] = std::make_pair(~(uint64_t)umma_cost(p->umma_items[i]), (int32_t)i);
+        sort_by_key(order);  // descending cost, ties in the order of generation (a stable sort)
+        // in place, cycle by cycle: position i receives the item that was at order[i].second
+        BlkUmmaItem* const items = p->umma_items.data();
+        for (size_t i = 0; i < order.size(); ++i) {
+            if (order[i].second == (int32_t)i) continue;
+            const BlkUmmaItem first = items[i];
+            size_t to = i;
+            for (;;) {
+                const size_t from = (size_t)order[to].second;
+                order[to].second = (int32_t)to;  // done
+                if (from == i) { items[to] = first; break; }
+                items[to] = items[from];
+                to = from;
+            }
+        }
     }
     p->umma_long_rows = 0;
     for (const BlkUmmaItem& it : p->umma_items)
