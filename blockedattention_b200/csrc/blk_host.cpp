@@ -698,9 +698,9 @@ int blk_build_softmax_schedule(blk_plan* p) {
     p->bytes = 0;
     const int64_t window = BLK_SMX_WINDOW_BYTES / es;  // elements
     // Count the chunks before making them: a batch of very many long rows must be refused, not materialised.
+    int64_t count = 0;
     {
         const int64_t cap = p->max_chunks > 0 ? p->max_chunks : (int64_t)0x7fffffff / std::max<int64_t>(p->H, 1);
-        int64_t count = 0;
         for (int64_t s = 0; s < S && count <= cap; ++s) {
             const int64_t rows = p->M[s], cols = p->N[s];
             if (rows == 0 || cols == 0) continue;
@@ -713,40 +713,42 @@ int blk_build_softmax_schedule(blk_plan* p) {
             return BLK_ERR_UNSUPPORTED;
         }
     }
+    // Chunks, and in the same pass the windows of the pipelined kernels: consecutive chunks that are contiguous in
+    // memory, up to the window size.
+    p->smx_chunks.resize((size_t)count);
+    p->smx_windows.clear();
+    p->smx_windows.reserve((size_t)count / 2 + 16);
+    BlkSmxChunk* const chunks = p->smx_chunks.data();
+    int64_t c = 0;
+    int64_t open_end = -1;  // element offset one past the last piece of the window being filled (-1: none)
+    auto add_chunk = [&](int64_t off, int64_t rows, int64_t cols) {
+        chunks[c] = BlkSmxChunk{off, (int32_t)rows, (int32_t)cols};
+        const int64_t ne = rows * cols, nb = ne * es;
+        bool extend = false;
+        if (open_end == off && nb <= BLK_SMX_WINDOW_BYTES) {
+            const BlkSmxWindow& wd = p->smx_windows.back();
+            extend = wd.nbytes + nb <= BLK_SMX_WINDOW_BYTES && wd.npieces < BLK_SMX_WINDOW_PIECES;
+        }
+        if (extend) {
+            BlkSmxWindow& wd = p->smx_windows.back();
+            wd.nbytes += (int32_t)nb;
+            wd.npieces += 1;
+            open_end += ne;
+        } else {
+            // a one-row piece longer than the window keeps its own window; its byte count only has to exceed the
+            // window size for the kernel to stream it (and no later piece continues such a window)
+            const int64_t capped = std::min<int64_t>(nb, (int64_t)BLK_SMX_WINDOW_BYTES + 1);
+            p->smx_windows.push_back(BlkSmxWindow{off, (int32_t)capped, (int32_t)c, 1, 0});
+            open_end = nb <= BLK_SMX_WINDOW_BYTES ? off + ne : -1;
+        }
+        ++c;
+    };
     for (int64_t s = 0; s < S; ++s) {
         const int64_t rows = p->M[s], cols = p->N[s];
         p->bytes += 2.0 * (double)p->H * (double)rows * (double)cols * es;
         if (rows == 0 || cols == 0) continue;
-        if (cols > window) {
-            for (int64_t r = 0; r < rows; ++r)
-                p->smx_chunks.push_back(BlkSmxChunk{p->a1[s] + r * cols, 1, (int32_t)cols});
-        } else {
-            const int64_t rpc = window / cols;
-            for (int64_t r = 0; r < rows; r += rpc)
-                p->smx_chunks.push_back(
-                    BlkSmxChunk{p->a1[s] + r * cols, (int32_t)std::min(rpc, rows - r), (int32_t)cols});
-        }
-    }
-    // Windows of the pipelined kernels: consecutive chunks that are contiguous in memory, up to the window size.
-    p->smx_windows.clear();
-    for (size_t c = 0; c < p->smx_chunks.size(); ++c) {
-        const BlkSmxChunk& ch = p->smx_chunks[c];
-        const int64_t nb = (int64_t)ch.rows * ch.cols * es;
-        bool extend = false;
-        if (!p->smx_windows.empty() && nb <= BLK_SMX_WINDOW_BYTES) {
-            const BlkSmxWindow& wd = p->smx_windows.back();
-            extend = wd.nbytes + nb <= BLK_SMX_WINDOW_BYTES && wd.npieces < BLK_SMX_WINDOW_PIECES &&
-                     wd.off + wd.nbytes / es == ch.off;
-        }
-        if (extend) {
-            p->smx_windows.back().nbytes += (int32_t)nb;
-            p->smx_windows.back().npieces += 1;
-        } else {
-            // a one-row piece longer than the window keeps its own window; its byte count only has to exceed the
-            // window size for the kernel to stream it
-            const int64_t capped = std::min<int64_t>(nb, (int64_t)BLK_SMX_WINDOW_BYTES + 1);
-            p->smx_windows.push_back(BlkSmxWindow{ch.off, (int32_t)capped, (int32_t)c, 1, 0});
-        }
+        const int64_t rpc = cols > window ? 1 : window / cols;
+        for (int64_t r = 0; r < rows; r += rpc) add_chunk(p->a1[s] + r * cols, std::min(rpc, rows - r), cols);
     }
     return BLK_OK;
 }
