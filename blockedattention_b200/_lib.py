@@ -52,6 +52,7 @@ SIGNATURES = {
     "blk_plan_extents": (C.c_int, [_vp, _i64p, _i64p, _i64p]),
     "blk_plan_offsets": (C.c_int, [_vp, _i64p, _i64p, _i64p]),
     "blk_plan_summary": (C.c_int, [_vp, _i64p]),
+    "blk_plan_table": (C.c_int, [_vp, C.c_int, _vp, C.c_int64, _i64p, _i64p]),
     "blk_plan_work": (C.c_int, [_vp, _f64p, _f64p]),
     "blk_plan_check": (C.c_int, [_vp, _vp]),
 }

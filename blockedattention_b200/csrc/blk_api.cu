@@ -284,6 +284,46 @@ extern "C" int blk_plan_summary(const blk_plan_t* p, int64_t counts[8]) {
     return BLK_OK;
 }
 
+extern "C" int blk_plan_table(const blk_plan_t* p, int table, void* dst, int64_t capacity, int64_t* bytes,
+                              int64_t* record_bytes) {
+    if (!p || !bytes) {
+        blk_set_error("blk_plan_table: null argument");
+        return BLK_ERR_INVALID;
+    }
+    const void* src = nullptr;
+    size_t n = 0, rec = 0;
+    auto take = [&](const auto& v) { src = v.data(); rec = sizeof(v[0]); n = v.size() * rec; };
+    switch (table) {
+        case BLK_TABLE_SEGMENTS: take(p->segs); break;
+        case BLK_TABLE_TILE_ITEMS: take(p->tile_items); break;
+        case BLK_TABLE_SIMT_ITEMS: take(p->simt_items); break;
+        case BLK_TABLE_SMALL_ITEMS_32: take(p->small_items[0]); break;
+        case BLK_TABLE_SMALL_ITEMS_64: take(p->small_items[1]); break;
+        case BLK_TABLE_UMMA_ITEMS: take(p->umma_items); break;
+        case BLK_TABLE_PV_ITEMS: take(p->pv_items); break;
+        case BLK_TABLE_PACKS: take(p->packs); break;
+        case BLK_TABLE_PACK_BLOCKS: take(p->pack_blocks); break;
+        case BLK_TABLE_SMX_CHUNKS: take(p->smx_chunks); break;
+        case BLK_TABLE_SMX_WINDOWS: take(p->smx_windows); break;
+        case BLK_TABLE_FLASH_ITEMS: take(p->flash_items); break;
+        case BLK_TABLE_UMMA_VIEWS_A: take(p->umma_viewsA); break;
+        case BLK_TABLE_UMMA_VIEWS_B: take(p->umma_viewsB); break;
+        default:
+            blk_set_error("blk_plan_table: no table " + std::to_string(table));
+            return BLK_ERR_INVALID;
+    }
+    *bytes = (int64_t)n;
+    if (record_bytes) *record_bytes = (int64_t)rec;
+    if (dst) {
+        if (capacity < (int64_t)n) {
+            blk_set_error("blk_plan_table: the table has " + std::to_string(n) + " bytes, the buffer " + std::to_string(capacity));
+            return BLK_ERR_INVALID;
+        }
+        if (n) std::memcpy(dst, src, n);
+    }
+    return BLK_OK;
+}
+
 extern "C" int blk_plan_work(const blk_plan_t* p, double* flops, double* bytes) {
     if (!p) {
         blk_set_error("blk_plan_work: plan is null");

@@ -40,6 +40,37 @@ def _stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+def _rec(*fields):
+    return np.dtype([tuple(f) for f in fields])
+
+
+_TILE_ITEM = _rec(("seg", "<i4"), ("tm", "<i4"), ("tn", "<i4"), ("ntn", "<i4"))
+_SMALL_ITEM = _rec(("offA", "<i8"), ("offB", "<i8"), ("offC", "<i8"), ("M", "<i4"), ("N", "<i4"))
+_VIEW = _rec(("K", "<i8"), ("residue", "<i8"))
+# name -> (blk_table_t value, record layout): mirrors of the schedule records of csrc/blk_internal.h
+TABLES = {
+    "segments": (0, _rec(("offA", "<i8"), ("offB", "<i8"), ("offC", "<i8"), ("M", "<i4"), ("N", "<i4"), ("K", "<i4"),
+                         ("clsIn", "u1"), ("clsOut", "u1"), ("pad", "u1", (2,)))),
+    "tile_items": (1, _TILE_ITEM),
+    "simt_items": (2, _TILE_ITEM),
+    "small_items_32": (3, _SMALL_ITEM),
+    "small_items_64": (4, _SMALL_ITEM),
+    "umma_items": (5, _rec(("views", "<i4"), ("tm", "<i4"), ("rowA", "<i4"), ("rowB", "<i4"), ("offC", "<i8"),
+                           ("M", "<i4"), ("N", "<i4"), ("K", "<i4"), ("ch0", "<i4"), ("nch", "<i4"), ("pad", "<i4"))),
+    "pv_items": (6, _rec(("offA", "<i8"), ("offC", "<i8"), ("rowB", "<i4"), ("M", "<i4"), ("K", "<i4"), ("pad", "<i4"))),
+    "packs": (7, _rec(("offA", "<i8"), ("offB", "<i8"), ("rowsA", "<i4"), ("rowsB", "<i4"), ("first_block", "<i4"),
+                      ("nblocks", "<i4"))),
+    "pack_blocks": (8, _rec(("offC", "<i8"), ("rowA", "<i4"), ("rowB", "<i4"), ("M", "<i4"), ("N", "<i4"),
+                            ("nblocks", "<i4"), ("pad", "<i4"))),
+    "softmax_chunks": (9, _rec(("off", "<i8"), ("rows", "<i4"), ("cols", "<i4"))),
+    "softmax_windows": (10, _rec(("off", "<i8"), ("nbytes", "<i4"), ("first_piece", "<i4"), ("npieces", "<i4"),
+                                 ("pad", "<i4"))),
+    "flash_items": (11, _rec(("rowQ", "<i4"), ("rowKV", "<i4"), ("M", "<i4"), ("N", "<i4"))),
+    "umma_views_a": (12, _VIEW),
+    "umma_views_b": (13, _VIEW),
+}
+
+
 class _Plan:
     def __init__(self):
         self._h = C.c_void_p()
@@ -67,6 +98,20 @@ class _Plan:
         L.check(L.lib.blk_plan_summary(self._h, arr))
         keys = ["segments", "small_items", "tile_items", "umma_items", "softmax_chunks", "launches", "simt_items", "packs"]
         return {k: int(arr[i]) for i, k in enumerate(keys)}
+
+    def table(self, name: str) -> np.ndarray:
+        """One of the schedule's tables as a numpy record array (a copy), for tests and debugging; ``name`` is a key
+        of ``TABLES``.  The record layouts are the library's own and follow its version."""
+        which, dtype = TABLES[name]
+        n, rec = C.c_int64(), C.c_int64()
+        L.check(L.lib.blk_plan_table(self._h, which, None, 0, C.byref(n), C.byref(rec)))
+        if rec.value != dtype.itemsize:
+            raise RuntimeError(f"table {name}: the library's records have {rec.value} bytes, this module expects "
+                               f"{dtype.itemsize}")
+        out = np.empty(n.value // dtype.itemsize, dtype)
+        if n.value:
+            L.check(L.lib.blk_plan_table(self._h, which, out.ctypes.data_as(C.c_void_p), n.value, C.byref(n), None))
+        return out
 
     @property
     def work(self):

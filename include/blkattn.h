@@ -240,6 +240,29 @@ BLK_API int blk_plan_offsets(const blk_plan_t* plan, int64_t* accum1, int64_t* a
  * small-segment kernel (0 unless it was enabled). */
 BLK_API int blk_plan_summary(const blk_plan_t* plan, int64_t counts[8]);
 
+/* The schedule itself, for tests and debugging: copies the host copy of one of the plan's tables into dst
+ * (capacity bytes; dst may be NULL to ask for the size only), *bytes = size of the table, *record_bytes = size of
+ * one record.  The record layouts are the library's own (csrc/blk_internal.h) and may change between versions; no
+ * run-time caller needs them. */
+typedef enum {
+    BLK_TABLE_SEGMENTS = 0,      /* BlkSeg: one per segment, batch order */
+    BLK_TABLE_TILE_ITEMS = 1,    /* BlkTileItem: staged mma.sync kernel */
+    BLK_TABLE_SIMT_ITEMS = 2,    /* BlkTileItem: fp32 SIMT kernel */
+    BLK_TABLE_SMALL_ITEMS_32 = 3,/* BlkSmallItem: per-warp small-segment kernel, at most 32 columns */
+    BLK_TABLE_SMALL_ITEMS_64 = 4,/* BlkSmallItem: ... 33 to 64 columns */
+    BLK_TABLE_UMMA_ITEMS = 5,    /* BlkUmmaItem: tcgen05 kernel, in the order the CTAs take them */
+    BLK_TABLE_PV_ITEMS = 6,      /* BlkPvItem: tcgen05 kernel for (K, D) second operands */
+    BLK_TABLE_PACKS = 7,         /* BlkPack: pipelined small-segment kernel */
+    BLK_TABLE_PACK_BLOCKS = 8,   /* BlkPackBlock */
+    BLK_TABLE_SMX_CHUNKS = 9,    /* BlkSmxChunk */
+    BLK_TABLE_SMX_WINDOWS = 10,  /* BlkSmxWindow */
+    BLK_TABLE_FLASH_ITEMS = 11,  /* BlkFlashItem: tcgen05 attention kernel */
+    BLK_TABLE_UMMA_VIEWS_A = 12, /* BlkUmmaView: views of the first operand the tcgen05 items refer to */
+    BLK_TABLE_UMMA_VIEWS_B = 13  /* BlkUmmaView: ... of the second operand */
+} blk_table_t;
+BLK_API int blk_plan_table(const blk_plan_t* plan, int table, void* dst, int64_t capacity, int64_t* bytes,
+                           int64_t* record_bytes);
+
 /* Algorithmic work of one run over all heads: flops = 2 H sum(M N K) (0 for a
  * softmax plan), bytes = inputs read once + outputs written once. */
 BLK_API int blk_plan_work(const blk_plan_t* plan, double* flops, double* bytes);
