@@ -66,7 +66,10 @@ def _gemm_cover(plan, M, N, ao):
         # offC is the block's first result row; the item holds min(M, 128) rows of the segment's D columns
         s = max(k for k in seg_of.values() if ao[k] <= it["offC"])
         rows = min(int(it["M"]), 128)
-        assert (it["offC"] - ao[s]) % N[s] == 0
+        tm, rem = divmod(int(it["offC"] - ao[s]), 128 * int(N[s]))
+        assert rem == 0 and it["M"] == M[s] - 128 * tm and it["K"] == segs[s]["K"]
+        assert it["offA"] == segs[s]["offA"] + tm * 128 * int(it["K"])   # first operand: rows of K elements
+        assert int(it["rowB"]) * int(N[s]) == segs[s]["offB"]            # second operand: (rows, D) view of the strip
         cover[int(it["offC"]):int(it["offC"]) + rows * int(N[s])] += 1
     packs, blocks = plan.table("packs"), plan.table("pack_blocks")
     for pk in packs:
