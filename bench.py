@@ -349,6 +349,30 @@ class Runner:
             self.plan_pv.check()
 
 
+def cold_plan_ms(w, run, dev, reps: int = 5):
+    """Median wall time of creating the plan(s) of one step from the lists: host schedule, one pooled allocation and
+    one upload each, synchronised on both sides."""
+    import torch
+    from blockedattention_b200.plan import AttentionPlan, GemmPlan
+    if run.softmax_only:
+        return None
+    ts = []
+    for _ in range(reps):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        if run.fused_attn:
+            p = AttentionPlan(w.M, w.N, w.H, w.dtype, device=dev, d=int(w.K[0]) if w.S else 64)
+        else:
+            p = GemmPlan(w.M, w.N, w.K, w.H, w.dtype, w.out_dtype, False, False, w.softmax, device=dev)
+        q = None
+        if run.plan_pv is not None:
+            q = GemmPlan(w.M, np.full_like(w.N, w.d_v), w.N, w.H, w.out_dtype, w.out_dtype, False, True, False, device=dev)
+        torch.cuda.synchronize()
+        ts.append((time.perf_counter() - t0) * 1e3)
+        del p, q
+    return float(np.median(ts))
+
+
 def timed_region(fn, steps: int, warmup: int, min_ms: float, barrier, allmax):
     """W warm-up steps, then `repeats` x `steps` steps between two events; returns (ms per step on this rank,
     repeats).  `repeats` is the same on every rank and makes the region last at least min_ms."""
@@ -676,11 +700,15 @@ def main():
                     rc = Runner(wc, dev, 2, seed=args.seed + 7)
                     ms_c, rep_c = timed_region(rc.step, max(3, min(args.steps, 20)), 3, args.min_ms, barrier, allmax)
                     rc.check()
-                    configs.append({"workload": name, "note": wc.note, "ms_per_step": ms_c, "repeats": rep_c,
-                                    "value": wc.flops() / (ms_c * 1e-3) / 1e12, "unit": "TFLOP/s",
-                                    "roofline": roofline_of(wc, ms_c, peaks, rc.kernel_name(), rc.launches_per_step,
-                                                            traffic, 1),
-                                    "launches_per_step": rc.launches_per_step, "plan": rc.plan.summary})
+                    rec = {"workload": name, "note": wc.note, "ms_per_step": ms_c, "repeats": rep_c,
+                           "value": wc.flops() / (ms_c * 1e-3) / 1e12, "unit": "TFLOP/s",
+                           "roofline": roofline_of(wc, ms_c, peaks, rc.kernel_name(), rc.launches_per_step, traffic, 1),
+                           "launches_per_step": rc.launches_per_step, "plan": rc.plan.summary}
+                    try:  # what a new set of lists costs on the host before the first launch
+                        rec["plan_ms"] = cold_plan_ms(wc, rc, dev)
+                    except Exception as exc:
+                        rec["plan_ms_error"] = f"{type(exc).__name__}: {exc}"
+                    configs.append(rec)
                     del rc
                 except Exception as exc:  # a sub-record must not take the headline down with it
                     configs.append({"workload": name, "error": f"{type(exc).__name__}: {exc}"})
