@@ -2,14 +2,40 @@
 // include/blkattn.h.  Thin by design -- argument checks, one upload of the
 // schedule at plan creation, kernel launches on the caller's stream.
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
 
 #include "blk_internal.h"
 #include "blk_kernels.h"
+
+// A named range around every plan creation and every run, for timelines of tools that collect NVTX (header-only:
+// without such a tool attached a range is a call through a pointer to an empty function).  BLK_NVTX=0 in the
+// environment leaves them out.
+namespace {
+struct BlkRange {
+    bool on;
+    explicit BlkRange(const char* name) : on(enabled()) {
+        if (on) nvtxRangePushA(name);
+    }
+    ~BlkRange() {
+        if (on) nvtxRangePop();
+    }
+    BlkRange(const BlkRange&) = delete;
+    BlkRange& operator=(const BlkRange&) = delete;
+    static bool enabled() {
+        static const bool v = [] {
+            const char* e = std::getenv("BLK_NVTX");
+            return !(e && e[0] == '0' && e[1] == 0);
+        }();
+        return v;
+    }
+};
+}  // namespace
 
 namespace {
 
@@ -115,6 +141,7 @@ extern "C" int blk_gemm_plan_create(blk_plan_t** plan, const int64_t* M, const i
                                     const int64_t* accum1, const int64_t* accum2, const int64_t* accumOut, int64_t S,
                                     int64_t H, int dtype_in, int dtype_out, int transpose1, int transpose2,
                                     int epilogue, int device) {
+    BlkRange range("blk_gemm_plan_create");
     if (!plan) {
         blk_set_error("blk_gemm_plan_create: plan is null");
         return BLK_ERR_INVALID;
@@ -185,6 +212,7 @@ extern "C" int blk_gemm_plan_create(blk_plan_t** plan, const int64_t* M, const i
 
 extern "C" int blk_softmax_plan_create(blk_plan_t** plan, const int64_t* rows, const int64_t* cols,
                                        const int64_t* accum, int64_t S, int64_t H, int dtype, int device) {
+    BlkRange range("blk_softmax_plan_create");
     if (!plan) {
         blk_set_error("blk_softmax_plan_create: plan is null");
         return BLK_ERR_INVALID;
@@ -376,6 +404,7 @@ static int build_flash_items(blk_plan* p, bool skip_small) {
 
 static int attention_plan_impl(blk_plan_t** plan, const int64_t* M, const int64_t* N, int64_t S, int64_t H,
                                int64_t head_dim, bool any_length, int dtype, int device) {
+    BlkRange range("blk_attention_plan_create");
     if (!plan) {
         blk_set_error("blk_attention_plan_create: plan is null");
         return BLK_ERR_INVALID;
@@ -511,6 +540,7 @@ extern "C" int blk_attention_run_strided(const blk_plan_t* p, const void* q, con
 
 static int attention_run_impl(const blk_plan* p, const void* q, const void* k, const void* v, void* out,
                               int64_t row_stride, int64_t head_stride, float scale, void* cuda_stream) {
+    BlkRange range("blk_attention_run");
     if (!p || p->kind != 0 || !p->attn) {
         blk_set_error("blk_attention_run: not an attention plan");
         return BLK_ERR_INVALID;
@@ -578,6 +608,7 @@ static int attention_run_impl(const blk_plan* p, const void* q, const void* k, c
 // packed head-major strips, whose row view depends on the contraction length of the kernel that reads them).
 static int gemm_run_impl(const blk_plan* p, const void* mat1, const void* mat2, void* out, float scale,
                          const BlkOperandLayout* layA, const BlkOperandLayout* layB, void* cuda_stream) {
+    BlkRange range("blk_gemm_run");
     if (p && p->attn) {
         blk_set_error("blk_gemm_run: this is an attention plan, run it with blk_attention_run");
         return BLK_ERR_INVALID;
@@ -765,6 +796,7 @@ extern "C" int blk_gemm_run_strided(const blk_plan_t* p, const void* mat1, int64
 }
 
 extern "C" int blk_softmax_run(const blk_plan_t* p, const void* src, void* out, float scale, void* cuda_stream) {
+    BlkRange range("blk_softmax_run");
     if (!p || p->kind != 1) {
         blk_set_error("blk_softmax_run: not a softmax plan");
         return BLK_ERR_INVALID;
@@ -800,6 +832,7 @@ extern "C" int blk_softmax_run(const blk_plan_t* p, const void* src, void* out, 
 
 extern "C" int blk_softmax_backward_run(const blk_plan_t* p, const void* out, const void* grad_out, void* grad_src,
                                         float scale, void* cuda_stream) {
+    BlkRange range("blk_softmax_backward_run");
     if (!p || p->kind != 1) {
         blk_set_error("blk_softmax_backward_run: not a softmax plan");
         return BLK_ERR_INVALID;
